@@ -1,0 +1,161 @@
+/*
+ * b200loss.h — C ABI of libb200loss.so: fused per-pixel losses for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes only.  All pointers named
+ * "logits", "labels", "losses", "grad*", "out", "jacc" and "workspace" are DEVICE
+ * pointers owned by the caller; the library never allocates, frees or keeps a
+ * pointer after it returns.
+ * Work is enqueued on `stream` (a cudaStream_t passed as void*) and the call
+ * returns without synchronising.  Return value: 0 on success, otherwise one of
+ * the B200_ERR_* codes; b200_last_error() gives the message of the calling
+ * thread's last failure.  Nothing throws across this boundary.
+ *
+ * Shapes follow the reference project (CoinCheung/pytorch-loss): logits are
+ * [N, C, M] row-major with M = product of the trailing (spatial) dims, labels
+ * are int64 [N, M] (focal: same dtype and shape as the logits).
+ *
+ * dtype codes: B200_F32 (float), B200_F16 (__half).  Arithmetic is always fp32.
+ *
+ * Reduction record ("out", 32 bytes, 8-byte aligned), written by the forward
+ * kernels when `out` is non-NULL:
+ *     double sum;     // sum of the per-pixel losses of valid pixels
+ *     double count;   // number of valid (non-ignored) pixels / elements
+ *     float  mean;    // (float)(sum / count)      (NaN when count == 0)
+ *     float  sum32;   // (float)sum
+ *     float  pad[2];
+ *
+ * Workspace: every op that reduces needs `b200_reduce_workspace_bytes()` bytes
+ * of device memory whose first 64 bytes are ZERO before its first use; the
+ * kernels leave them zero again, so one zero-initialised buffer per stream can
+ * be reused forever.  Two calls that overlap on the GPU must not share one.
+ * Byte 4..7 of the workspace is a status word: non-zero after a kernel gave up
+ * a bounded wait (see b200_read_status).
+ */
+#ifndef B200LOSS_H_
+#define B200LOSS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK               0
+#define B200_ERR_ARG          1   /* null pointer, bad size, bad dtype, misaligned buffer */
+#define B200_ERR_UNSUPPORTED  2   /* shape outside what the kernels cover */
+#define B200_ERR_LAUNCH       3   /* CUDA runtime reported an error at launch */
+#define B200_ERR_STATUS       4   /* device status word set (a bounded wait ran out) */
+#define B200_ERR_WORKSPACE    5   /* workspace too small */
+
+#define B200_F32 0
+#define B200_F16 1
+
+/* Version of this ABI (bumped on any signature change). */
+int b200_abi_version(void);
+
+/* Message of the calling thread's last failed call ("" if none). */
+const char *b200_last_error(void);
+
+/* Bytes of workspace the reducing forward kernels need (constant). */
+size_t b200_reduce_workspace_bytes(void);
+
+/* Synchronises `stream`, reads the workspace's status word, clears it, and returns
+ * B200_OK or B200_ERR_STATUS.  For tests and debugging; never needed for results. */
+int b200_read_status(void *workspace, void *stream);
+
+/* ------------------------------------------------------------------ focal ---
+ * Sigmoid focal loss, elementwise over E elements.
+ * Replaces focal_cpp.focalloss_forward / focalloss_backward /
+ * focalloss_forward_backward (reference csrc/focal_kernel.cu:301-341; math at
+ * :30-118).  `labels` has the dtype of `logits` (soft labels allowed).
+ *
+ * forward:  losses (E elements, dtype) may be NULL; out (reduction record) may be
+ *           NULL; at least one must be given.  workspace is required iff out != NULL.
+ * backward: grad_logits[i] = dloss_i/dlogit_i * g, where g is
+ *             grad_mode 0: 1
+ *             grad_mode 1: *(const float*)grad_out            (one device scalar)
+ *             grad_mode 2: ((const dtype*)grad_out)[i]        (elementwise)
+ *           and, when denom != NULL, additionally divided by ((const double*)denom)[0]
+ *           read on the device (the element count for reduction='mean', e.g. the
+ *           `count` field of the reduction record, possibly all-reduced).
+ * forward_backward: writes losses and unscaled gradients in one pass.
+ */
+int b200_focal_forward(const void *logits, const void *labels, void *losses, void *out,
+                       void *workspace, size_t workspace_bytes, int64_t E, int dtype,
+                       float gamma, float alpha, void *stream);
+int b200_focal_backward(const void *logits, const void *labels, const void *grad_out,
+                        int grad_mode, const void *denom, void *grad_logits, int64_t E,
+                        int dtype, float gamma, float alpha, void *stream);
+int b200_focal_forward_backward(const void *logits, const void *labels, void *losses,
+                                void *grad_logits, int64_t E, int dtype, float gamma,
+                                float alpha, void *stream);
+
+/* -------------------------------------------------- label-smooth softmax CE ---
+ * Replaces lsr_cpp.lsr_forward / lsr_backward (reference csrc/lsr_kernel.cu:296-322;
+ * math at :66-185) including the ATen log_softmax/softmax calls and the Python-side
+ * `grad.mul_(grad_output.unsqueeze(1))`, `(labels != ignore).sum()` and
+ * `losses.sum()` passes (reference pytorch_loss/label_smooth.py:144,169-170).
+ *
+ * forward:  losses ([N, M], dtype) may be NULL; out may be NULL; one must be given.
+ * backward: grad_logits [N, C, M] = (sumy * softmax - y) * g, zero at ignored
+ *           pixels, with g:
+ *             grad_mode 0: 1
+ *             grad_mode 1: *(const float*)grad_out
+ *             grad_mode 2: ((const dtype*)grad_out)[n*M + m]   (per pixel)
+ *           and, when denom != NULL, additionally divided by ((const double*)denom)[0]
+ *           read on the device (the valid-pixel count, possibly all-reduced).
+ */
+int b200_lsr_forward(const void *logits, const int64_t *labels, void *losses, void *out,
+                     void *workspace, size_t workspace_bytes, int64_t N, int64_t C,
+                     int64_t M, int dtype, int64_t ignore_index, float smooth, void *stream);
+int b200_lsr_backward(const void *logits, const int64_t *labels, const void *grad_out,
+                      int grad_mode, const void *denom, void *grad_logits, int64_t N,
+                      int64_t C, int64_t M, int dtype, int64_t ignore_index, float smooth,
+                      void *stream);
+
+/* ------------------------------------------------------ large-margin softmax ---
+ * Replaces large_margin_cpp.l_margin_forward / l_margin_backward /
+ * l_margin_forward_backward (reference csrc/large_margin_kernel.cu:796-838; math at
+ * :388-481) and the Python-side scaling / counting passes (reference
+ * large_margin_softmax.py:167,191,221-226).  Same argument conventions as LSR.
+ */
+int b200_lmargin_forward(const void *logits, const int64_t *labels, void *losses, void *out,
+                         void *workspace, size_t workspace_bytes, int64_t N, int64_t C,
+                         int64_t M, int dtype, int64_t ignore_index, float lam, void *stream);
+int b200_lmargin_backward(const void *logits, const int64_t *labels, const void *grad_out,
+                          int grad_mode, const void *denom, void *grad_logits, int64_t N,
+                          int64_t C, int64_t M, int dtype, int64_t ignore_index, float lam,
+                          void *stream);
+
+/* ------------------------------------------------------------ Lovasz softmax ---
+ * Replaces lovasz_softmax_cpp.lovasz_softmax_forward / lovasz_softmax_backward
+ * (reference csrc/lovasz_softmax.cu:778-802; pipeline at :495-773, scan in
+ * csrc/cumsum.hpp:113-150).
+ *
+ * Groups: per_image == 0 -> one group holding all N*M pixels (the reference's
+ * behaviour); per_image != 0 -> every image is its own group.  G = number of groups,
+ * L = pixels per group.  Segments are (group, class) pairs.
+ *
+ * forward:  loss  float[G*C]      per-segment Lovasz loss
+ *           jacc  float[G*C*L]    Jaccard-gradient of every pixel, segment-major,
+ *                                 pixel order inside the group (what backward needs)
+ *           workspace: b200_lovasz_workspace_bytes(...) bytes, 256-byte aligned; no
+ *           zero-initialisation required.
+ * backward: grad float32 [G*C] upstream gradient per segment;
+ *           grad_logits [N, C, M] (dtype).
+ */
+size_t b200_lovasz_workspace_bytes(int64_t N, int64_t C, int64_t M, int per_image);
+int b200_lovasz_forward(const void *logits, const int64_t *labels, float *loss, float *jacc,
+                        void *workspace, size_t workspace_bytes, int64_t N, int64_t C,
+                        int64_t M, int dtype, int64_t ignore_index, int per_image,
+                        void *stream);
+int b200_lovasz_backward(const float *grad, const void *logits, const int64_t *labels,
+                         const float *jacc, void *grad_logits, int64_t N, int64_t C,
+                         int64_t M, int dtype, int64_t ignore_index, int per_image,
+                         void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200LOSS_H_ */

@@ -1,0 +1,123 @@
+// Host-side plumbing of libb200loss: per-thread error string, launch checks,
+// device queries and the tensor-map encoder (looked up in the driver at run time
+// so the library links against the CUDA runtime only).
+#include "common.cuh"
+
+#include <string.h>
+
+namespace b200 {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int launch_status(const char *what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return B200_OK;
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return B200_ERR_LAUNCH;
+}
+
+int sm_count() {
+    static thread_local int cached_dev = -1, cached_sms = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached_dev = dev;
+        cached_sms = n;
+    }
+    return cached_sms;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        tried = true;
+    }
+    return fn;
+}
+
+bool encode_tensor_map(CUtensorMap *map, int dtype, const void *base, int rank,
+                       const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return false;
+    }
+    cuuint64_t gdim[5];
+    cuuint64_t gstr[5];
+    cuuint32_t bdim[5];
+    cuuint32_t estr[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bdim[i] = box[i];
+        estr[i] = 1;
+        if (i > 0) gstr[i - 1] = strides_bytes[i];
+    }
+    CUtensorMapDataType dt;
+    switch (dtype) {
+        case B200_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+        case B200_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+        default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT32; break;   // raw 32-bit words
+    }
+    const CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void *>(base), gdim,
+                          gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+        return false;
+    }
+    return true;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_abi_version(void) { return 1; }
+
+const char *b200_last_error(void) { return b200::g_error; }
+
+size_t b200_reduce_workspace_bytes(void) { return b200::kReduceWorkspaceBytes; }
+
+int b200_read_status(void *workspace, void *stream) {
+    if (!workspace) {
+        b200::set_error("b200_read_status: workspace is NULL");
+        return B200_ERR_ARG;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned status = 0;
+    unsigned *word = reinterpret_cast<unsigned *>(workspace) + 1;
+    if (cudaMemcpyAsync(&status, word, sizeof(status), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess) {
+        return b200::launch_status("b200_read_status");
+    }
+    if (status == 0) return B200_OK;
+    cudaMemsetAsync(word, 0, sizeof(unsigned), s);
+    cudaStreamSynchronize(s);
+    b200::set_error("device status word = 0x%x: a kernel gave up a bounded wait", status);
+    return B200_ERR_STATUS;
+}
+
+}  // extern "C"

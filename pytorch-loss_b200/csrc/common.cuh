@@ -1,0 +1,262 @@
+// Shared device/host helpers of libb200loss: error reporting, dtype access,
+// warp/block reductions, the deterministic grid reduction that ends every
+// reducing forward kernel, and thin wrappers over the sm_100a bulk-async (TMA)
+// and mbarrier PTX used to stage tiles in shared memory.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/b200loss.h"
+
+namespace b200 {
+
+// ----------------------------------------------------------------- host side
+
+void set_error(const char *fmt, ...);
+int launch_status(const char *what);   // cudaGetLastError -> B200_OK / B200_ERR_LAUNCH
+int sm_count();                         // SMs of the current device (cached per device)
+
+// Workspace layout shared by all reducing kernels.
+//   [0]   uint32  ticket   (must be zero between kernels; kernels reset it)
+//   [4]   uint32  status   (non-zero: a bounded wait gave up)
+//   [64]  double2 partials[kMaxPartials]
+constexpr int kMaxPartials = 65536;
+constexpr size_t kPartialsOffset = 64;
+constexpr size_t kReduceWorkspaceBytes = kPartialsOffset + size_t(kMaxPartials) * 16;
+
+struct ReduceRecord {       // the 32-byte "out" record of the C ABI
+    double sum;
+    double count;
+    float mean;
+    float sum32;
+    float pad[2];
+};
+
+// --------------------------------------------------------------- dtype access
+
+template <typename T> struct Vec16;   // 16-byte vector of T
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    float v[4];
+};
+template <> struct Vec16<__half> {
+    static constexpr int N = 8;
+    __half v[8];
+};
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+
+// Streaming 16-byte global access (read-once data: keep it out of L1).
+template <typename V> __device__ __forceinline__ V ld_stream16(const void *p) {
+    static_assert(sizeof(V) == 16, "16-byte vector expected");
+    int4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return *reinterpret_cast<V *>(&r);
+}
+template <typename V> __device__ __forceinline__ void st_stream16(void *p, const V &v) {
+    static_assert(sizeof(V) == 16, "16-byte vector expected");
+    const int4 r = *reinterpret_cast<const int4 *>(&v);
+    asm volatile("st.global.cs.v4.s32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(r.x), "r"(r.y), "r"(r.z),
+                 "r"(r.w)
+                 : "memory");
+}
+
+// ------------------------------------------------------------ math (fp32 core)
+
+// e^x for x <= 0 in softmax sums: ex2.approx on x*log2(e).  Relative error of a
+// term is below 2^-21 for the arguments that contribute to a sum (|x| < 16).
+__device__ __forceinline__ float exp_fast(float x) { return __expf(x); }
+
+// --------------------------------------------------------------- reductions
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum of (loss, count) pairs in double; result valid in thread 0.
+// `sh` must hold 64 doubles.  All threads of the block must call it.
+__device__ __forceinline__ void block_sum2(double &a, double &b, double *sh) {
+    a = warp_sum(a);
+    b = warp_sum(b);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) {
+        sh[warp] = a;
+        sh[32 + warp] = b;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        a = lane < nwarp ? sh[lane] : 0.0;
+        b = lane < nwarp ? sh[32 + lane] : 0.0;
+        a = warp_sum(a);
+        b = warp_sum(b);
+    }
+}
+
+// Final step of a reducing forward kernel.  Every block calls it once with its
+// partial (sum, count).  The block that takes the last ticket adds all partials
+// in a fixed order, writes the record and re-arms the ticket: deterministic,
+// no spinning, no second launch.  blockDim.x must be a multiple of 32, <= 1024.
+__device__ __forceinline__ void grid_reduce_finish(double sum, double cnt, void *workspace,
+                                                   ReduceRecord *out, double *sh) {
+    block_sum2(sum, cnt, sh);
+    unsigned *ticket = reinterpret_cast<unsigned *>(workspace);
+    double2 *partials =
+        reinterpret_cast<double2 *>(reinterpret_cast<char *>(workspace) + kPartialsOffset);
+    __shared__ unsigned s_last;
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = make_double2(sum, cnt);
+        __threadfence();
+        const unsigned t = atomicAdd(ticket, 1u);
+        s_last = (t == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    double a = 0.0, b = 0.0;
+    for (unsigned i = threadIdx.x; i < gridDim.x; i += blockDim.x) {
+        const double2 p = __ldcg(&partials[i]);
+        a += p.x;
+        b += p.y;
+    }
+    block_sum2(a, b, sh);
+    if (threadIdx.x == 0) {
+        out->sum = a;
+        out->count = b;
+        out->mean = static_cast<float>(a / b);
+        out->sum32 = static_cast<float>(a);
+        out->pad[0] = 0.f;
+        out->pad[1] = 0.f;
+        *ticket = 0u;
+    }
+}
+
+// ------------------------------------------------- mbarrier + bulk-async (TMA)
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kMbarSpinLimit polls (each poll itself blocks for a
+// hardware-defined short time), records it in the status word and reports false.
+constexpr uint32_t kMbarSpinLimit = 1u << 20;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
+                                                  unsigned *status_word) {
+    for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (status_word) atomicOr(status_word, 1u);
+    // second, shorter bounded wait so copies still in flight land before the CTA exits
+    for (uint32_t i = 0; i < (kMbarSpinLimit >> 4); ++i) {
+        if (mbar_try_wait(bar, parity)) break;
+    }
+    return false;
+}
+
+// 2-D / 3-D tiled loads global -> shared, completion on an mbarrier (no multicast).
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y,
+                                            uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z,
+                                            uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
+}
+// Tiled stores shared -> global (bulk-group completion).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),
+                 "r"(x), "r"(y), "r"(smem_u32(src))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int x, int y, int z,
+                                             const void *src) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(map),
+        "r"(x), "r"(y), "r"(z), "r"(smem_u32(src))
+        : "memory");
+}
+// Untiled bulk copies (16-byte aligned addresses, size a multiple of 16).
+__device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, uint32_t bytes,
+                                             uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void *dst, const void *src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                 "r"(smem_u32(src)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// Host: encode a tiled tensor map over a row-major array.  `dims`/`strides_bytes`
+// are innermost-first; strides_bytes[0] is implied (element size).  Returns false
+// (with the error string set) if the driver entry point is missing or refuses.
+bool encode_tensor_map(CUtensorMap *map, int dtype, const void *base, int rank,
+                       const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box);
+
+}  // namespace b200

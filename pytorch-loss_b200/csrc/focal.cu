@@ -1,0 +1,281 @@
+// Sigmoid focal loss for sm_100a: one streaming kernel family.
+//
+// Math follows the reference's elementwise kernels (csrc/focal_kernel.cu:30-118):
+//   p = sigmoid(x), log p = x >= 0 ? -log1p(e^-x) : x - log1p(e^x), log(1-p) = log p - x
+//   ce = y*a*log p + (1-y)*(1-a)*log(1-p);  coeff = -|y-p|^g;  loss = coeff*ce
+//   d_ce = y*a - p*(1 - y - a + 2*y*a);  d_coeff = g*|y-p|^(g-1)*p*(1-p), negated if y < p
+//   grad = d_coeff*ce + d_ce*coeff
+// One exp and one log1p per element serve both branches (e = e^-|x|).
+//
+// Data movement: 16-byte loads/stores, two vectors in flight per thread per array,
+// persistent grid of kBlocksPerSM blocks per SM; the 'mean'/'sum' forward writes no
+// per-element loss at all (8 B/element), the backward recomputes (12 B/element).
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kBlocksPerSM = 4;
+
+enum FocalMode { kFwd = 0, kBwd = 1, kFwdBwd = 2 };
+
+struct FocalParams {
+    const void *logits;
+    const void *labels;
+    void *losses;        // may be null (kFwd with reduce only)
+    void *grads;         // kBwd / kFwdBwd
+    const void *grad_out;
+    int grad_mode;       // 0 none, 1 device float scalar, 2 elementwise (dtype)
+    const double *denom; // optional device divisor
+    void *workspace;     // reduce
+    ReduceRecord *out;   // reduce
+    int64_t E;
+    float gamma, alpha;
+};
+
+template <bool GAMMA2>
+__device__ __forceinline__ void focal_core(float x, float y, float gamma, float alpha, float &loss,
+                                           float &grad, bool want_grad) {
+    const float e = expf(-fabsf(x));
+    const float inv = 1.f / (1.f + e);
+    const float p = x >= 0.f ? inv : e * inv;
+    const float l1p = log1pf(e);
+    const float log_p = x >= 0.f ? -l1p : x - l1p;
+    const float ce = y * alpha * log_p + (1.f - y) * (1.f - alpha) * (log_p - x);
+    const float d = fabsf(y - p);
+    const float coeff = GAMMA2 ? -(d * d) : -powf(d, gamma);
+    loss = coeff * ce;
+    if (want_grad) {
+        const float d_ce = y * alpha - p * (1.f - y - alpha + 2.f * y * alpha);
+        float d_coeff = (GAMMA2 ? 2.f * d : gamma * powf(d, gamma - 1.f)) * p * (1.f - p);
+        if (y < p) d_coeff = -d_coeff;
+        grad = d_coeff * ce + d_ce * coeff;
+    }
+}
+
+template <typename T, int MODE, bool GAMMA2, bool REDUCE>
+__global__ void __launch_bounds__(kThreads) focal_kernel(const FocalParams prm) {
+    using V = Vec16<T>;
+    constexpr int VN = V::N;
+    const T *__restrict__ logits = static_cast<const T *>(prm.logits);
+    const T *__restrict__ labels = static_cast<const T *>(prm.labels);
+    T *__restrict__ losses = static_cast<T *>(prm.losses);
+    T *__restrict__ grads = static_cast<T *>(prm.grads);
+    const T *__restrict__ gout = static_cast<const T *>(prm.grad_out);
+    const float gamma = prm.gamma, alpha = prm.alpha;
+    constexpr bool kGrad = MODE != kFwd;
+    constexpr bool kLoss = MODE != kBwd;
+
+    float gscale = 1.f;
+    if (MODE == kBwd && prm.grad_mode == 1) gscale = *static_cast<const float *>(prm.grad_out);
+    if (MODE == kBwd && prm.denom) gscale = static_cast<float>(double(gscale) / *prm.denom);
+    const bool per_elem = (MODE == kBwd) && prm.grad_mode == 2;
+
+    double acc = 0.0;
+    const int64_t nvec = prm.E / VN;
+    const int64_t stride = int64_t(gridDim.x) * kThreads;
+    int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x;
+
+    auto do_vec = [&](int64_t vi, const V &xv, const V &yv) {
+        V lv, gv, sv;
+        if (per_elem) sv = ld_stream16<V>(gout + vi * VN);
+        float part = 0.f;
+#pragma unroll
+        for (int k = 0; k < VN; ++k) {
+            float loss, grad = 0.f;
+            focal_core<GAMMA2>(to_f32(xv.v[k]), to_f32(yv.v[k]), gamma, alpha, loss, grad, kGrad);
+            if (kLoss) {
+                part += loss;
+                lv.v[k] = from_f32<T>(loss);
+            }
+            if (kGrad) {
+                const float s = per_elem ? gscale * to_f32(sv.v[k]) : gscale;
+                gv.v[k] = from_f32<T>(MODE == kBwd ? grad * s : grad);
+            }
+        }
+        if (kLoss && losses) st_stream16(losses + vi * VN, lv);
+        if (kGrad) st_stream16(grads + vi * VN, gv);
+        if (REDUCE) acc += double(part);
+    };
+
+    // two vectors per array in flight per thread
+    for (; i + stride < nvec; i += 2 * stride) {
+        const V x0 = ld_stream16<V>(logits + i * VN);
+        const V y0 = ld_stream16<V>(labels + i * VN);
+        const V x1 = ld_stream16<V>(logits + (i + stride) * VN);
+        const V y1 = ld_stream16<V>(labels + (i + stride) * VN);
+        do_vec(i, x0, y0);
+        do_vec(i + stride, x1, y1);
+    }
+    if (i < nvec) {
+        const V x0 = ld_stream16<V>(logits + i * VN);
+        const V y0 = ld_stream16<V>(labels + i * VN);
+        do_vec(i, x0, y0);
+    }
+    // scalar tail (E not a multiple of the vector width)
+    if (blockIdx.x == 0) {
+        for (int64_t j = nvec * VN + threadIdx.x; j < prm.E; j += kThreads) {
+            float loss, grad = 0.f;
+            focal_core<GAMMA2>(to_f32(logits[j]), to_f32(labels[j]), gamma, alpha, loss, grad, kGrad);
+            if (kLoss && losses) losses[j] = from_f32<T>(loss);
+            if (kGrad) {
+                const float s = per_elem ? gscale * to_f32(gout[j]) : gscale;
+                grads[j] = from_f32<T>(MODE == kBwd ? grad * s : grad);
+            }
+            if (REDUCE) acc += double(loss);
+        }
+    }
+    if (REDUCE) {
+        __shared__ double sh[64];
+        const double cnt = (blockIdx.x == 0 && threadIdx.x == 0) ? double(prm.E) : 0.0;
+        grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh);
+    }
+}
+
+// Scalar-only variant for buffers that are not 16-byte aligned.
+template <typename T, int MODE, bool REDUCE>
+__global__ void __launch_bounds__(kThreads) focal_kernel_unaligned(const FocalParams prm) {
+    const T *logits = static_cast<const T *>(prm.logits);
+    const T *labels = static_cast<const T *>(prm.labels);
+    T *losses = static_cast<T *>(prm.losses);
+    T *grads = static_cast<T *>(prm.grads);
+    const T *gout = static_cast<const T *>(prm.grad_out);
+    constexpr bool kGrad = MODE != kFwd;
+    constexpr bool kLoss = MODE != kBwd;
+    float gscale = 1.f;
+    if (MODE == kBwd && prm.grad_mode == 1) gscale = *static_cast<const float *>(prm.grad_out);
+    if (MODE == kBwd && prm.denom) gscale = static_cast<float>(double(gscale) / *prm.denom);
+    const bool per_elem = (MODE == kBwd) && prm.grad_mode == 2;
+    double acc = 0.0;
+    for (int64_t j = int64_t(blockIdx.x) * kThreads + threadIdx.x; j < prm.E;
+         j += int64_t(gridDim.x) * kThreads) {
+        float loss, grad = 0.f;
+        focal_core<false>(to_f32(logits[j]), to_f32(labels[j]), prm.gamma, prm.alpha, loss, grad, kGrad);
+        if (kLoss && losses) losses[j] = from_f32<T>(loss);
+        if (kGrad) {
+            const float s = per_elem ? gscale * to_f32(gout[j]) : gscale;
+            grads[j] = from_f32<T>(MODE == kBwd ? grad * s : grad);
+        }
+        if (REDUCE) acc += double(loss);
+    }
+    if (REDUCE) {
+        __shared__ double sh[64];
+        const double cnt = (blockIdx.x == 0 && threadIdx.x == 0) ? double(prm.E) : 0.0;
+        grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh);
+    }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T, int MODE, bool REDUCE>
+int launch_focal(const FocalParams &prm, cudaStream_t stream) {
+    const int vn = Vec16<T>::N;
+    int64_t want = (prm.E / vn + kThreads - 1) / kThreads;
+    const int64_t cap = int64_t(sm_count()) * kBlocksPerSM;
+    if (want > cap) want = cap;
+    if (want < 1) want = 1;
+    const dim3 grid(static_cast<unsigned>(want));
+    const bool al = aligned16(prm.logits) && aligned16(prm.labels) &&
+                    (!prm.losses || aligned16(prm.losses)) && (!prm.grads || aligned16(prm.grads)) &&
+                    (prm.grad_mode != 2 || aligned16(prm.grad_out));
+    if (!al) {
+        focal_kernel_unaligned<T, MODE, REDUCE><<<grid, kThreads, 0, stream>>>(prm);
+    } else if (prm.gamma == 2.f) {
+        focal_kernel<T, MODE, true, REDUCE><<<grid, kThreads, 0, stream>>>(prm);
+    } else {
+        focal_kernel<T, MODE, false, REDUCE><<<grid, kThreads, 0, stream>>>(prm);
+    }
+    return launch_status("focal kernel launch");
+}
+
+template <int MODE, bool REDUCE>
+int dispatch_focal(const FocalParams &prm, int dtype, cudaStream_t stream) {
+    if (dtype == B200_F32) return launch_focal<float, MODE, REDUCE>(prm, stream);
+    if (dtype == B200_F16) return launch_focal<__half, MODE, REDUCE>(prm, stream);
+    set_error("focal: unknown dtype code %d", dtype);
+    return B200_ERR_ARG;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_focal_forward(const void *logits, const void *labels, void *losses, void *out,
+                                  void *workspace, size_t workspace_bytes, int64_t E, int dtype,
+                                  float gamma, float alpha, void *stream) {
+    if (E < 0 || (!losses && !out)) {
+        set_error("b200_focal_forward: need E >= 0 and at least one of losses/out");
+        return B200_ERR_ARG;
+    }
+    if (E > 0 && (!logits || !labels)) {
+        set_error("b200_focal_forward: null input pointer");
+        return B200_ERR_ARG;
+    }
+    if (out && (!workspace || workspace_bytes < kReduceWorkspaceBytes)) {
+        set_error("b200_focal_forward: workspace of %zu bytes required, got %zu",
+                  kReduceWorkspaceBytes, workspace ? workspace_bytes : size_t(0));
+        return B200_ERR_WORKSPACE;
+    }
+    if (E == 0 && !out) return B200_OK;
+    FocalParams prm{};
+    prm.logits = logits;
+    prm.labels = labels;
+    prm.losses = losses;
+    prm.workspace = workspace;
+    prm.out = static_cast<ReduceRecord *>(out);
+    prm.E = E;
+    prm.gamma = gamma;
+    prm.alpha = alpha;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return out ? dispatch_focal<kFwd, true>(prm, dtype, s) : dispatch_focal<kFwd, false>(prm, dtype, s);
+}
+
+extern "C" int b200_focal_backward(const void *logits, const void *labels, const void *grad_out,
+                                   int grad_mode, const void *denom, void *grad_logits, int64_t E,
+                                   int dtype, float gamma, float alpha, void *stream) {
+    if (E < 0 || grad_mode < 0 || grad_mode > 2 || (grad_mode != 0 && !grad_out)) {
+        set_error("b200_focal_backward: bad E / grad_mode / grad_out");
+        return B200_ERR_ARG;
+    }
+    if (E == 0) return B200_OK;
+    if (!logits || !labels || !grad_logits) {
+        set_error("b200_focal_backward: null pointer");
+        return B200_ERR_ARG;
+    }
+    FocalParams prm{};
+    prm.logits = logits;
+    prm.labels = labels;
+    prm.grads = grad_logits;
+    prm.grad_out = grad_out;
+    prm.grad_mode = grad_mode;
+    prm.denom = static_cast<const double *>(denom);
+    prm.E = E;
+    prm.gamma = gamma;
+    prm.alpha = alpha;
+    return dispatch_focal<kBwd, false>(prm, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_focal_forward_backward(const void *logits, const void *labels, void *losses,
+                                           void *grad_logits, int64_t E, int dtype, float gamma,
+                                           float alpha, void *stream) {
+    if (E < 0) {
+        set_error("b200_focal_forward_backward: E < 0");
+        return B200_ERR_ARG;
+    }
+    if (E == 0) return B200_OK;
+    if (!logits || !labels || !losses || !grad_logits) {
+        set_error("b200_focal_forward_backward: null pointer");
+        return B200_ERR_ARG;
+    }
+    FocalParams prm{};
+    prm.logits = logits;
+    prm.labels = labels;
+    prm.losses = losses;
+    prm.grads = grad_logits;
+    prm.E = E;
+    prm.gamma = gamma;
+    prm.alpha = alpha;
+    return dispatch_focal<kFwdBwd, false>(prm, dtype, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,94 @@
+"""Host logic shared by the two softmax-family losses (label-smooth CE and large-margin
+softmax): argument checks, the per-pixel forward/backward calls and the fused
+'mean'/'sum' autograd Function.  `kind` selects the C-ABI entry points."""
+import torch
+import torch.amp as amp
+
+from . import _cabi
+from . import _sharding
+
+_ENTRY = {
+    "lsr": ("b200_lsr_forward", "b200_lsr_backward"),
+    "lmargin": ("b200_lmargin_forward", "b200_lmargin_backward"),
+}
+
+
+def _prep(logits, labels):
+    dev = _cabi.require_cuda(logits, labels)
+    n, c, m = _cabi.split_shape(logits, labels)
+    return dev, logits.contiguous(), labels.contiguous(), n, c, m, _cabi.dtype_code(logits)
+
+
+def forward_per_pixel(kind, logits, labels, ignore_index, hyper):
+    """Per-pixel losses [N, *spatial] in the logits' dtype, zeros at ignored pixels."""
+    dev, logits, labels, n, c, m, dt = _prep(logits, labels)
+    lib = _cabi.load_library()
+    losses = torch.empty(labels.shape, dtype=logits.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _cabi.check(getattr(lib, _ENTRY[kind][0])(
+            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), None, None, 0,
+            n, c, m, dt, int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+    return losses, logits, labels
+
+
+def forward_reduced(kind, logits, labels, ignore_index, hyper, want_losses=False):
+    """Runs the reducing forward; returns (record, per-pixel losses or None, logits, labels)."""
+    dev, logits, labels, n, c, m, dt = _prep(logits, labels)
+    lib = _cabi.load_library()
+    rec = _cabi.new_record(dev)
+    ws = _cabi.reduce_workspace(dev)
+    losses = torch.empty(labels.shape, dtype=logits.dtype, device=dev) if want_losses else None
+    with torch.cuda.device(dev):
+        _cabi.check(getattr(lib, _ENTRY[kind][0])(
+            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), _cabi.ptr(rec), _cabi.ptr(ws),
+            ws.numel(), n, c, m, dt, int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+    return rec, losses, logits, labels
+
+
+def backward(kind, logits, labels, grad_output, denom, ignore_index, hyper):
+    """d(loss)/d(logits); the upstream gradient (None = ones, a broadcast scalar, or one
+    value per pixel) and the optional device-resident divisor are applied in the kernel."""
+    dev = logits.device
+    n, c, m = _cabi.split_shape(logits)
+    lib = _cabi.load_library()
+    grads = torch.empty_like(logits)
+    if grad_output is None:
+        mode, g = 0, None
+    else:
+        mode, g = _cabi.grad_mode_of(grad_output, labels.shape)
+        if mode == 2:
+            g = g.to(logits.dtype)
+    with torch.cuda.device(dev):
+        _cabi.check(getattr(lib, _ENTRY[kind][1])(
+            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(g), mode,
+            None if denom is None else _cabi._vp(denom.data_ptr()), _cabi.ptr(grads),
+            n, c, m, _cabi.dtype_code(logits), int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+    return grads
+
+
+class ReducedLossFunc(torch.autograd.Function):
+    """'mean' / 'sum' over valid pixels as ONE reducing forward kernel (no per-pixel loss
+    tensor, no separate count or sum pass) and ONE backward kernel that recomputes the
+    softmax and applies grad_output / n_valid read from device memory.  With a process
+    group the [sum, count] pair is all-reduced first, so the result is the loss of the
+    concatenated batch.  Returns a 0-dim float32 loss."""
+
+    @staticmethod
+    @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
+    def forward(ctx, logits, labels, kind, hyper, ignore_index, mean, group):
+        rec, _, logits, labels = forward_reduced(kind, logits, labels, ignore_index, hyper)
+        sum_count = rec[:4].view(torch.float64)
+        if _sharding.group_is_active(group):
+            _sharding.allreduce_sum_count(sum_count, group)
+            loss = _sharding.combine_mean(sum_count) if mean else sum_count[0].to(torch.float32)
+        else:
+            loss = rec[4] if mean else rec[5]
+        ctx.variables = logits, labels, kind, hyper, ignore_index, (sum_count[1:] if mean else None)
+        return loss
+
+    @staticmethod
+    @amp.custom_bwd(device_type='cuda')
+    def backward(ctx, grad_output):
+        logits, labels, kind, hyper, ignore_index, denom = ctx.variables
+        grads = backward(kind, logits, labels, grad_output, denom, ignore_index, hyper)
+        return grads, None, None, None, None, None, None

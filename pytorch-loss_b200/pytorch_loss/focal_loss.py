@@ -1,0 +1,154 @@
+"""Sigmoid focal loss on the B200 CUDA library.
+
+Drop-in for the reference's V3 classes (focal_loss.py:129-200): `FocalLossV3`,
+`FocalSigmoidLossFuncV3`, `FocalSigmoidLossFuncV3FB` keep their names, arguments and
+return shapes.  What differs is underneath: with reduction 'mean' or 'sum' the module
+runs one forward kernel that reads logits and labels once and emits only the sum (no
+per-element loss tensor, no separate `.mean()` pass), and one backward kernel that
+recomputes the sigmoid and writes the already-scaled gradient.
+"""
+import torch
+import torch.nn as nn
+import torch.amp as amp
+
+from . import _cabi
+from . import _sharding
+
+
+def _prep(logits, labels):
+    dev = _cabi.require_cuda(logits, labels)
+    if labels.dtype != logits.dtype:
+        raise RuntimeError("focal loss: labels must have the dtype of logits (%s), got %s"
+                           % (logits.dtype, labels.dtype))
+    if labels.shape != logits.shape:
+        raise RuntimeError("focal loss: labels shape %s != logits shape %s"
+                           % (tuple(labels.shape), tuple(logits.shape)))
+    return dev, logits.contiguous(), labels.contiguous(), _cabi.dtype_code(logits)
+
+
+def _focal_backward(logits, labels, grad_output, denom, alpha, gamma):
+    """grad wrt logits, scaled by the upstream gradient (and 1/denom) inside the kernel."""
+    dev = logits.device
+    lib = _cabi.load_library()
+    grads = torch.empty_like(logits)
+    if grad_output is None:
+        mode, g = 0, None
+    else:
+        mode, g = _cabi.grad_mode_of(grad_output, logits.shape)
+        if mode == 2:
+            g = g.to(logits.dtype)
+    with torch.cuda.device(dev):
+        _cabi.check(lib.b200_focal_backward(
+            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(g), mode,
+            None if denom is None else _cabi._vp(denom.data_ptr()),
+            _cabi.ptr(grads), logits.numel(), _cabi.dtype_code(logits),
+            float(gamma), float(alpha), _cabi.stream_ptr(dev)))
+    return grads
+
+
+class FocalSigmoidLossFuncV3(torch.autograd.Function):
+    """Per-element focal loss; backward recomputes from logits and labels
+    (reference focal_loss.py:129-149)."""
+
+    @staticmethod
+    @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
+    def forward(ctx, logits, labels, alpha, gamma):
+        dev, logits, labels, dt = _prep(logits, labels)
+        lib = _cabi.load_library()
+        losses = torch.empty_like(logits)
+        with torch.cuda.device(dev):
+            _cabi.check(lib.b200_focal_forward(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), None, None, 0,
+                logits.numel(), dt, float(gamma), float(alpha), _cabi.stream_ptr(dev)))
+        ctx.variables = logits, labels, alpha, gamma
+        return losses
+
+    @staticmethod
+    @amp.custom_bwd(device_type='cuda')
+    def backward(ctx, grad_output):
+        logits, labels, alpha, gamma = ctx.variables
+        return _focal_backward(logits, labels, grad_output, None, alpha, gamma), None, None, None
+
+
+class FocalSigmoidLossFuncV3FB(torch.autograd.Function):
+    """Loss and unscaled gradient from one pass; the gradient is kept for backward
+    (reference focal_loss.py:152-171)."""
+
+    @staticmethod
+    @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
+    def forward(ctx, logits, labels, alpha, gamma):
+        dev, logits, labels, dt = _prep(logits, labels)
+        lib = _cabi.load_library()
+        losses = torch.empty_like(logits)
+        grads = torch.empty_like(logits)
+        with torch.cuda.device(dev):
+            _cabi.check(lib.b200_focal_forward_backward(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), _cabi.ptr(grads),
+                logits.numel(), dt, float(gamma), float(alpha), _cabi.stream_ptr(dev)))
+        ctx.variables = grads
+        return losses
+
+    @staticmethod
+    @amp.custom_bwd(device_type='cuda')
+    def backward(ctx, grad_output):
+        grads = ctx.variables
+        return grads * grad_output, None, None, None
+
+
+class _FocalReducedFunc(torch.autograd.Function):
+    """'mean' / 'sum' focal loss as one reducing kernel + one recomputing backward.
+    Returns a 0-dim float32 loss."""
+
+    @staticmethod
+    @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
+    def forward(ctx, logits, labels, alpha, gamma, mean, group):
+        dev, logits, labels, dt = _prep(logits, labels)
+        lib = _cabi.load_library()
+        rec = _cabi.new_record(dev)
+        ws = _cabi.reduce_workspace(dev)
+        with torch.cuda.device(dev):
+            _cabi.check(lib.b200_focal_forward(
+                _cabi.ptr(logits), _cabi.ptr(labels), None, _cabi.ptr(rec), _cabi.ptr(ws),
+                ws.numel(), logits.numel(), dt, float(gamma), float(alpha), _cabi.stream_ptr(dev)))
+        sum_count = rec[:4].view(torch.float64)
+        if _sharding.group_is_active(group):
+            _sharding.allreduce_sum_count(sum_count, group)
+            loss = _sharding.combine_mean(sum_count) if mean else sum_count[0].to(torch.float32)
+        else:
+            loss = rec[4] if mean else rec[5]
+        ctx.variables = logits, labels, alpha, gamma, (sum_count[1:] if mean else None)
+        return loss
+
+    @staticmethod
+    @amp.custom_bwd(device_type='cuda')
+    def backward(ctx, grad_output):
+        logits, labels, alpha, gamma, denom = ctx.variables
+        grads = _focal_backward(logits, labels, grad_output, denom, alpha, gamma)
+        return grads, None, None, None, None, None
+
+
+class FocalLossV3(nn.Module):
+    """Sigmoid focal loss, usage as nn.BCEWithLogitsLoss (reference focal_loss.py:174-200):
+
+        >>> criteria = FocalLossV3()
+        >>> logits = torch.randn(8, 19, 384, 384).cuda()
+        >>> lbs = torch.randint(0, 2, (8, 19, 384, 384)).float().cuda()
+        >>> loss = criteria(logits, lbs)
+
+    `process_group` (keyword only, not in the reference): pass a torch.distributed group
+    (or True for the default group) to make 'mean'/'sum' global over a batch that is
+    sharded across ranks; the default None keeps the loss local to this process.
+    """
+
+    def __init__(self, alpha=0.25, gamma=2, reduction='mean', *, process_group=None):
+        super(FocalLossV3, self).__init__()
+        self.alpha = alpha
+        self.gamma = gamma
+        self.reduction = reduction
+        self.process_group = process_group
+
+    def forward(self, logits, label):
+        if self.reduction == 'mean' or self.reduction == 'sum':
+            return _FocalReducedFunc.apply(logits, label, self.alpha, self.gamma,
+                                           self.reduction == 'mean', self.process_group)
+        return FocalSigmoidLossFuncV3.apply(logits, label, self.alpha, self.gamma)

@@ -1,0 +1,104 @@
+"""FocalLossV3 (CUDA, through the C ABI) against the CPU oracle and the golden files."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_grad_close, assert_loss_close, run_module, TOL_F16
+
+pytestmark = pytest.mark.gpu
+
+
+def _mods():
+    import pytorch_loss
+    from oracle import losses as O
+    return pytorch_loss, O
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 7, 5), (16, 1, 64, 64), (1, 1, 1), (3, 5, 1023), (2, 2, 4096, 33)])
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+@pytest.mark.parametrize("gamma", [2, 1.5])
+def test_focal_matches_oracle(shape, reduction, gamma):
+    P, O = _mods()
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(shape, generator=g) * 3 ** 0.5
+    labels = (torch.rand(shape, generator=g) < 0.1).float()
+    want_loss, want_grad = O.focal_loss(logits, labels, 0.25, gamma, reduction)
+    loss, grad = run_module(P.FocalLossV3(0.25, gamma, reduction), logits.cuda(), labels.cuda())
+    assert_loss_close(loss, want_loss, atol=1e-6 if reduction == "none" else 1e-7)
+    assert_grad_close(grad, want_grad)
+
+
+def test_focal_soft_labels_and_extremes():
+    P, O = _mods()
+    g = torch.Generator().manual_seed(12)
+    logits = torch.randn(4, 3, 50, generator=g) * 10
+    logits[0, 0, :6] = torch.tensor([-100., 100., -30., 30., 0., -0.])
+    labels = torch.sigmoid(torch.randn(4, 3, 50, generator=g))
+    want_loss, want_grad = O.focal_loss(logits, labels, 0.4, 2.0, "sum")
+    loss, grad = run_module(P.FocalLossV3(0.4, 2.0, "sum"), logits.cuda(), labels.cuda())
+    assert_loss_close(loss, want_loss)
+    assert_grad_close(grad, want_grad)
+
+
+def test_focal_golden(golden_dir):
+    P, _ = _mods()
+    z = np.load(os.path.join(golden_dir, "focal.npz"))
+    for i in range(int(z["n_cases"])):
+        al, ga = z[f"c{i}_hyper"]
+        red = str(z[f"c{i}_reduction"])
+        logits, labels = torch.from_numpy(z[f"c{i}_logits"]), torch.from_numpy(z[f"c{i}_labels"])
+        loss, grad = run_module(P.FocalLossV3(float(al), float(ga), red), logits.cuda(), labels.cuda())
+        assert_loss_close(loss, torch.from_numpy(z[f"c{i}_loss_v2"]), atol=1e-6, what=f"golden c{i} loss")
+        assert_grad_close(grad, torch.from_numpy(z[f"c{i}_grad_v2"]), what=f"golden c{i} grad")
+
+
+def test_focal_functions_match_reference_contract():
+    """The two public autograd Functions: per-element loss, gradient scaled by grad_output."""
+    P, O = _mods()
+    g = torch.Generator().manual_seed(13)
+    logits = torch.randn(3, 2, 17, generator=g)
+    labels = (torch.rand(3, 2, 17, generator=g) < 0.3).float()
+    up = torch.randn(3, 2, 17, generator=g)
+    want_loss, want_grad = O.focal_loss(logits, labels, 0.25, 2.0, "none")
+    for fn in (P.FocalSigmoidLossFuncV3, P.FocalSigmoidLossFuncV3FB):
+        x = logits.cuda().requires_grad_(True)
+        loss = fn.apply(x, labels.cuda(), 0.25, 2.0)
+        loss.backward(up.cuda())
+        assert_loss_close(loss, want_loss, atol=1e-6)
+        assert_grad_close(x.grad, want_grad * up)
+
+
+def test_focal_fp16_io():
+    P, O = _mods()
+    g = torch.Generator().manual_seed(14)
+    logits = (torch.randn(2, 4, 31, 8, generator=g) * 2).half()
+    labels = (torch.rand(2, 4, 31, 8, generator=g) < 0.2).half()
+    want_loss, want_grad = O.focal_loss(logits.float(), labels.float(), 0.25, 2.0, "mean")
+    loss, grad = run_module(P.FocalLossV3(), logits.cuda(), labels.cuda())
+    assert grad.dtype == torch.float16
+    assert_loss_close(loss, want_loss, rtol=TOL_F16)
+    assert_grad_close(grad, want_grad, atol=TOL_F16 * float(want_grad.abs().max()), rtol=TOL_F16)
+
+
+def test_focal_rejects_cpu_and_bad_dtype():
+    P, _ = _mods()
+    crit = P.FocalLossV3()
+    with pytest.raises(RuntimeError):
+        crit(torch.randn(2, 3), torch.zeros(2, 3))
+    with pytest.raises(RuntimeError):
+        crit(torch.randn(2, 3).cuda(), torch.zeros(2, 3, dtype=torch.int64).cuda())
+
+
+def test_focal_deterministic_and_workspace_rearmed():
+    P, _ = _mods()
+    g = torch.Generator().manual_seed(15)
+    logits = torch.randn(8, 1, 256, 256, generator=g).cuda()
+    labels = (torch.rand(8, 1, 256, 256, generator=g) < 0.1).float().cuda()
+    crit = P.FocalLossV3()
+    first = crit(logits, labels).item()
+    for _ in range(5):
+        assert crit(logits, labels).item() == first
+    from pytorch_loss import _cabi
+    _cabi.read_status(logits.device)
