@@ -1,0 +1,391 @@
+#!/usr/bin/env python
+"""Benchmark of the fused V3 loss path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME|all] [--impl reference]
+
+A step is one forward + backward of a loss module over one synthetic batch
+(bench_workloads.py).  Rank 0 prints ONE JSON line.  Top-level fields describe the headline
+workload (focal, the baseline file's second configuration); `workloads` carries the same
+measurements for the other four configurations (1-GPU runs only, unless --workload says
+otherwise).
+
+  value      logit elements / s, forward+backward, inputs resident in HBM, timed with CUDA
+             events over K steps (max over ranks), step captured in a CUDA graph when possible
+  e2e        the same through the public module with pinned HOST inputs: H2D copy of logits
+             and labels, forward, backward, D2H read of the loss, every step
+  roofline   per C-ABI entry point: algorithmic bytes / CUDA-event duration of that call,
+             measured in a second (eager) pass over the same steps; peak from
+             MEASURED_PEAKS.json (hbm_gbs) or the 6650 GB/s fallback
+  cpu_baseline  the CPU port (oracle/) on the host cores, bounded sample, N=1 only
+
+`--impl reference` times the CPU port alone and prints the same line shape.
+L2 hygiene: every workload rotates 3 distinct input sets (each larger than L2 together
+with its gradient), so step k+1 never finds step k's lines in the 126 MB L2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "pytorch-loss_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+import bench_workloads as BW  # noqa: E402
+
+N_SETS = 3
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        return False
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_env():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return world, rank, local
+
+
+def time_cpu(fn, x, y, steps, warmup):
+    for _ in range(warmup):
+        fn(x, y)
+    best = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        fn(x, y)
+        best.append(time.perf_counter() - t0)
+    return best
+
+
+def cpu_baseline(wl, steps=3, warmup=1):
+    """The CPU port on a bounded sample of the workload, all host threads."""
+    from oracle import losses as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    items = min(wl.cpu_sample_items, wl.shape[0])
+    x, y = wl.make(items=items)
+    if wl.dtype == torch.float16:
+        x = x.float()                       # the reference's V1 upcasts half inputs on the CPU
+    times = time_cpu(wl.oracle(O), x, y, steps, warmup)
+    elems = x.numel()
+    return {"value": elems / min(times), "unit": "logit elements/s", "cores": cores, "kind": "port",
+            "sample": "%d of %d batch items of %s, forward+backward, best of %d" % (items, wl.shape[0], wl.name, steps),
+            "seconds_per_sample": min(times)}
+
+
+def run_reference_arm(args):
+    """`--impl reference`: the reference's CPU path (restated in oracle/) on the host cores."""
+    world, rank, _ = dist_env()
+    if rank != 0:
+        return
+    from oracle import losses as O
+    wl = BW.WORKLOADS[BW.HEADLINE if args.workload in ("all", None) else args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    items = min(wl.cpu_sample_items, wl.shape[0])
+    x, y = wl.make(items=items)
+    if wl.dtype == torch.float16:
+        x = x.float()
+    times = time_cpu(wl.oracle(O), x, y, args.steps, args.warmup)
+    ms = 1e3 * sum(times) / len(times)
+    value = x.numel() / (ms / 1e3)
+    sample = "%d of %d batch items per step" % (items, wl.shape[0])
+    line = {
+        "impl": "reference", "metric": "logit elements/s forward+backward", "value": value,
+        "unit": "logit elements/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl.desc, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "logit elements/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "logit elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def make_sets(wl, device, rank):
+    """N_SETS distinct (logits, labels) pairs on the device; set 0 is the CPU-seeded one."""
+    sets = []
+    x0, y0 = wl.make(seed_offset=1000 * rank)
+    sets.append((x0.to(device), y0.to(device)))
+    for r in range(1, N_SETS):
+        sets.append(wl.make(seed_offset=1000 * rank + 100 * r, device=device))
+    return sets, (x0, y0)
+
+
+def step_eager(crit, x, y):
+    x.grad = None
+    loss = crit(x, y)
+    loss.backward()
+    return loss
+
+
+def try_capture(crit, sets):
+    """One CUDA graph per input set holding forward+backward; None if capture fails."""
+    graphs = []
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for x, y in sets:
+                for _ in range(2):
+                    step_eager(crit, x, y)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        for x, y in sets:
+            x.grad = None
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                loss = crit(x, y)
+                loss.backward()
+            graphs.append((g, loss))
+        torch.cuda.synchronize()
+        return graphs
+    except Exception as exc:  # capture is an optimisation, eager is always available
+        sys.stderr.write("bench: CUDA graph capture unavailable (%s); timing eager steps\n" % (exc,))
+        torch.cuda.synchronize()
+        return None
+
+
+def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
+    import pytorch_loss as P
+    from pytorch_loss import _cabi
+    lib = _cabi.load_library()
+    peak, peak_kind = measured_peak()
+    group = True if world > 1 else None
+    crit = wl.criterion(P, process_group=group)
+    sets, host0 = make_sets(wl, device, rank)
+    for x, _ in sets:
+        x.requires_grad_(True)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput
+    graphs = None if args.no_graph else try_capture(crit, sets)
+    launches_before = lib.b200_kernel_launch_count()
+    step_eager(crit, *sets[0])
+    torch.cuda.synchronize()
+    launches_per_step = lib.b200_kernel_launch_count() - launches_before
+
+    def run_steps(n):
+        for k in range(n):
+            if graphs is not None:
+                graphs[k % N_SETS][0].replay()
+            else:
+                step_eager(crit, *sets[k % N_SETS])
+
+    run_steps(args.warmup)
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(device.index) as clocks:
+        start.record()
+        run_steps(args.steps)
+        end.record()
+        barrier()
+    ms_total = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms_total], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * wl.elems / (ms_step / 1e3)
+
+    # ---- per-entry-point durations (eager pass over the same steps)
+    for k in range(args.warmup):
+        step_eager(crit, *sets[k % N_SETS])
+    torch.cuda.synchronize()
+    with _cabi.CallTimer() as timer:
+        for k in range(args.steps):
+            step_eager(crit, *sets[k % N_SETS])
+    calls = timer.summary()
+    fwd_name, bwd_name = wl.entries()
+    kernels = {}
+    for name, nbytes in ((fwd_name, wl.bytes_forward()), (bwd_name, wl.bytes_backward())):
+        n, ms = calls.get(name, (0, 0.0))
+        if n:
+            gbs = nbytes / (ms / n / 1e3) / 1e9
+            kernels[name] = {"calls": n, "avg_ms": ms / n, "algorithmic_bytes": nbytes,
+                             "achieved_gbs": gbs, "frac": gbs / peak}
+    dominant = max(kernels, key=lambda k: kernels[k]["avg_ms"]) if kernels else None
+    roofline = None
+    if dominant:
+        d = kernels[dominant]
+        roofline = {"bound": "hbm", "kernel": dominant, "achieved": d["achieved_gbs"], "peak": peak,
+                    "unit": "GB/s", "frac": d["frac"], "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)"
+                    if peak_kind == "measured" else "fallback 6650 GB/s", "traffic": None,
+                    "step_frac": wl.bytes_step() / (ms_step / 1e3) / 1e9 / peak, "kernels": kernels}
+
+    # ---- end to end from pinned host memory (eager, public module API)
+    e2e = None
+    if with_e2e:
+        hx, hy = host0[0].pin_memory(), host0[1].pin_memory()
+        dx = torch.empty_like(sets[0][0]).detach().requires_grad_(True)
+        dy = torch.empty_like(sets[0][1])
+
+        def e2e_step():
+            with torch.no_grad():
+                dx.copy_(hx, non_blocking=True)
+                dy.copy_(hy, non_blocking=True)
+            return float(step_eager(crit, dx, dy).item())
+
+        for _ in range(max(1, args.warmup // 2)):
+            e2e_step()
+        n_e2e = max(3, min(args.steps, 10))
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            e2e_step()
+        barrier()
+        dt = (time.perf_counter() - t0) / n_e2e
+        if world > 1:
+            t = torch.tensor([dt], dtype=torch.float64, device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            dt = float(t.item())
+        e2e = {"value": world * wl.elems / dt, "unit": "logit elements/s",
+               "h2d_bytes_per_step": hx.numel() * hx.element_size() + hy.numel() * hy.element_size(),
+               "d2h_bytes_per_step": 4, "ms_per_step": dt * 1e3, "steps": n_e2e}
+
+    _cabi.read_status(device)       # raises if any kernel gave up a bounded wait
+    res = {
+        "workload": wl.desc, "value": value, "ms_per_step": ms_step, "graph": graphs is not None,
+        "launches_per_step": int(launches_per_step), "roofline": roofline, "e2e": e2e,
+        "clocks": clocks.summary(),
+    }
+    if with_cpu and rank == 0:
+        res["cpu_baseline"] = cpu_baseline(wl)
+    del sets, graphs
+    torch.cuda.empty_cache()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=None, help="one of %s, or all" % ", ".join(BW.WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="time eager steps instead of CUDA-graph replays")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    world, rank, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); "
+                         "use --impl reference for the CPU port")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=device)
+    which = args.workload or ("all" if world == 1 else BW.HEADLINE)
+    names = list(BW.WORKLOADS) if which == "all" else [which]
+    headline = BW.HEADLINE if BW.HEADLINE in names else names[0]
+
+    results = {}
+    for name in [headline] + [n for n in names if n != headline]:
+        wl = BW.WORKLOADS[name]
+        try:
+            results[name] = measure_workload(wl, args, device, world, rank, with_cpu=(world == 1),
+                                             with_e2e=True)
+        except Exception as exc:
+            if name == headline:
+                raise
+            results[name] = {"workload": wl.desc, "error": repr(exc)}
+            torch.cuda.synchronize()
+
+    if rank == 0:
+        h = results[headline]
+        wl = BW.WORKLOADS[headline]
+        line = {
+            "metric": "logit elements/s forward+backward", "value": h["value"], "unit": "logit elements/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": h["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16" if wl.dtype == torch.float16 else "f32", "data": "synthetic",
+            "config": {"workload": wl.desc, "per_gpu_shape": list(wl.shape),
+                       "l2": "3 rotating input sets, each larger than L2 with its gradient",
+                       "cuda_graph": h["graph"], "reduction_collective": "16-byte all-reduce" if world > 1 else "none"},
+            "roofline": h["roofline"], "cpu_baseline": h.get("cpu_baseline"), "e2e": h["e2e"],
+            "gpu_launches": h["launches_per_step"] * args.steps, "clocks": h["clocks"],
+            "workloads": {k: v for k, v in results.items() if k != headline},
+        }
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

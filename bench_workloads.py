@@ -1,0 +1,132 @@
+"""Synthetic workloads of the benchmark: the five configurations of the task's baseline
+file, with their seeded generators, algorithmic byte counts and CPU-sample sizes.
+No dataset is involved: shapes and value distributions only.
+
+Draw order per configuration (one `torch.Generator().manual_seed(1234 + cfg)` on the CPU):
+logits, then labels (or the label cell grid), then the ignore mask.  "N(0, v)" is read as
+mean 0, variance v.
+"""
+import math
+
+import torch
+
+
+class Workload:
+    def __init__(self, name, cfg, shape, dtype, desc, cpu_sample_items):
+        self.name, self.cfg, self.shape, self.dtype, self.desc = name, cfg, shape, dtype, desc
+        self.cpu_sample_items = cpu_sample_items     # batch items timed on the CPU baseline
+
+    @property
+    def elems(self):
+        return math.prod(self.shape)
+
+    @property
+    def pixels(self):
+        return self.elems // self.shape[1]
+
+    def esize(self):
+        return 2 if self.dtype == torch.float16 else 4
+
+    # algorithmic bytes per entry point (inputs once per pass, gradient once, no per-pixel
+    # loss tensor, softmax recomputed in backward)
+    def bytes_forward(self):
+        e, p, s = self.elems, self.pixels, self.esize()
+        if self.name == "focal":
+            return 8 * e
+        if self.name == "lovasz":
+            return 84 * e + 8 * p            # keys 8E + sort 3 passes of the 4-pass model 64E + jaccard 12E
+        return s * e + 8 * p
+
+    def bytes_backward(self):
+        e, p, s = self.elems, self.pixels, self.esize()
+        if self.name == "focal":
+            return 12 * e
+        if self.name == "lovasz":
+            return 12 * e + 8 * p
+        return 2 * s * e + 8 * p
+
+    def bytes_step(self):
+        return self.bytes_forward() + self.bytes_backward()
+
+    def entries(self):
+        stem = {"lsr": "lsr", "lsr_rows": "lsr", "focal": "focal", "lmargin": "lmargin", "lovasz": "lovasz"}[self.name]
+        return "b200_%s_forward" % stem, "b200_%s_backward" % stem
+
+    # ---- data
+    def make(self, seed_offset=0, device="cpu", items=None):
+        """(logits, labels) for `items` batch items (default: all).  device='cpu' gives the
+        canonical seeded tensors; a CUDA device draws the same distributions there."""
+        shape = list(self.shape)
+        if items is not None:
+            shape[0] = items
+        g = torch.Generator(device=device).manual_seed(1234 + self.cfg + seed_offset)
+        kw = dict(generator=g, device=device)
+        n = shape[0]
+        if self.name == "focal":
+            logits = torch.randn(shape, **kw) * math.sqrt(3.0)
+            labels = (torch.rand(shape, **kw) < 0.1).float()
+            return logits, labels
+        if self.name == "lsr":
+            logits = torch.randn(shape, **kw) * math.sqrt(2.0)
+            labels = torch.randint(0, shape[1], [n] + shape[2:], **kw)
+            labels[torch.rand([n] + shape[2:], **kw) < 0.05] = 255
+            return logits, labels
+        if self.name == "lmargin":
+            logits = torch.randn(shape, **kw)
+            labels = torch.randint(0, shape[1], [n] + shape[2:], **kw)
+            labels[torch.rand([n] + shape[2:], **kw) < 0.10] = 255
+            return logits, labels
+        if self.name == "lovasz":
+            logits = torch.randn(shape, **kw)
+            h, w = shape[2], shape[3]
+            cells = torch.randint(0, shape[1], (n, h // 32, w // 32), **kw)
+            for i in range(n):                     # every image must contain every class
+                cells[i].view(-1)[:shape[1]] = torch.arange(shape[1], device=device)
+            labels = cells.repeat_interleave(32, 1).repeat_interleave(32, 2).contiguous()
+            labels[torch.rand((n, h, w), **kw) < 0.03] = 255
+            return logits, labels
+        if self.name == "lsr_rows":
+            logits = torch.randn(shape, **kw).half()
+            labels = torch.randint(0, shape[1], [n] + shape[2:], **kw)
+            return logits, labels
+        raise KeyError(self.name)
+
+    def criterion(self, package, process_group=None):
+        """The module under test from `package` (the CUDA package)."""
+        if self.name == "focal":
+            return package.FocalLossV3(0.25, 2, 'mean', process_group=process_group)
+        if self.name == "lsr":
+            return package.LabelSmoothSoftmaxCEV3(0.1, 'mean', 255, process_group=process_group)
+        if self.name == "lmargin":
+            return package.LargeMarginSoftmaxV3(0.3, 'mean', 255, process_group=process_group)
+        if self.name == "lovasz":
+            return package.LovaszSoftmaxV3('mean', 255, per_image=True, process_group=process_group)
+        return package.LabelSmoothSoftmaxCEV3(0.1, 'mean', -100, process_group=process_group)
+
+    def oracle(self, oracle_module):
+        """The CPU port's function for this workload: f(logits, labels) -> (loss, grad)."""
+        O = oracle_module
+        if self.name == "focal":
+            return lambda x, y: O.focal_loss(x, y, 0.25, 2.0, 'mean')
+        if self.name == "lsr":
+            return lambda x, y: O.label_smooth_ce(x, y, 0.1, 255, 'mean')
+        if self.name == "lmargin":
+            return lambda x, y: O.large_margin_softmax(x, y, 0.3, 255, 'mean')
+        if self.name == "lovasz":
+            return lambda x, y: O.lovasz_softmax(x, y, 255, 'mean', per_image=True)
+        return lambda x, y: O.label_smooth_ce(x, y, 0.1, -100, 'mean')
+
+
+WORKLOADS = {
+    "lsr": Workload("lsr", 1, (16, 19, 512, 512), torch.float32,
+                    "LabelSmoothSoftmaxCEV3 fp32 [16,19,512,512], 5% ignored, mean", 16),
+    "focal": Workload("focal", 2, (16, 1, 1024, 1024), torch.float32,
+                      "FocalLossV3 fp32 [16,1,1024,1024], alpha 0.25 gamma 2, mean", 16),
+    "lmargin": Workload("lmargin", 3, (8, 150, 512, 512), torch.float32,
+                        "LargeMarginSoftmaxV3 fp32 [8,150,512,512], 10% ignored, mean", 1),
+    "lovasz": Workload("lovasz", 4, (8, 19, 1024, 1024), torch.float32,
+                       "LovaszSoftmaxV3 per image fp32 [8,19,1024,1024], 3% ignored, mean", 1),
+    "lsr_rows": Workload("lsr_rows", 5, (16384, 32768, 1, 1), torch.float16,
+                         "LabelSmoothSoftmaxCEV3 fp16 [16384,32768,1,1], mean", 1024),
+}
+HEADLINE = "focal"

@@ -57,6 +57,10 @@ int b200_abi_version(void);
 /* Message of the calling thread's last failed call ("" if none). */
 const char *b200_last_error(void);
 
+/* Number of kernels this library has launched in this process so far (all threads,
+ * all devices); a monotonically increasing diagnostic counter. */
+uint64_t b200_kernel_launch_count(void);
+
 /* Bytes of workspace the reducing forward kernels need (constant). */
 size_t b200_reduce_workspace_bytes(void);
 

@@ -4,10 +4,12 @@
 #include "common.cuh"
 
 #include <string.h>
+#include <atomic>
 
 namespace b200 {
 
 static thread_local char g_error[512] = "";
+static std::atomic<uint64_t> g_launches{0};
 
 void set_error(const char *fmt, ...) {
     va_list ap;
@@ -18,6 +20,7 @@ void set_error(const char *fmt, ...) {
 
 int launch_status(const char *what) {
     const cudaError_t e = cudaGetLastError();
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     if (e == cudaSuccess) return B200_OK;
     set_error("%s: %s", what, cudaGetErrorString(e));
     return B200_ERR_LAUNCH;
@@ -59,6 +62,13 @@ static EncodeTiledFn encode_fn() {
 
 bool encode_tensor_map(CUtensorMap *map, int dtype, const void *base, int rank,
                        const uint64_t *dims, const uint64_t *strides_bytes, const uint32_t *box) {
+    // The encoder is a driver call and needs a context bound to this thread; a thread that
+    // has made no runtime call yet (e.g. a fresh autograd worker) has none.
+    static thread_local bool context_bound = false;
+    if (!context_bound) {
+        cudaFree(nullptr);
+        context_bound = true;
+    }
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -96,6 +106,8 @@ bool encode_tensor_map(CUtensorMap *map, int dtype, const void *base, int rank,
 extern "C" {
 
 int b200_abi_version(void) { return 1; }
+
+uint64_t b200_kernel_launch_count(void) { return b200::g_launches.load(std::memory_order_relaxed); }
 
 const char *b200_last_error(void) { return b200::g_error; }
 

@@ -18,7 +18,7 @@ namespace b200 {
 // ----------------------------------------------------------------- host side
 
 void set_error(const char *fmt, ...);
-int launch_status(const char *what);   // cudaGetLastError -> B200_OK / B200_ERR_LAUNCH
+int launch_status(const char *what);   // cudaGetLastError -> B200_OK / B200_ERR_LAUNCH; counts the launch
 int sm_count();                         // SMs of the current device (cached per device)
 
 // Workspace layout shared by all reducing kernels.

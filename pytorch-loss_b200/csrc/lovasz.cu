@@ -1,14 +1,839 @@
-// placeholder until the Lovasz pipeline lands
+// Lovasz-softmax for sm_100a.
+//
+// What is computed (reference csrc/lovasz_softmax.cu:72-152,183-211,243-278,380-417):
+// for every segment = (group, class), over the group's L pixels,
+//   err_i  = |1[label_i == c] - softmax(x_i)_c|            (ignored pixels sort last, count 0)
+//   sort err descending; fg_i = 1[label == c] in sorted order; n_pos = sum fg
+//   J_i    = 1 - (n_pos - cumsum(fg)_i) / (n_pos - cumsum(fg)_i + i + 1);  dJ_i = J_i - J_{i-1}
+//   loss   = sum_i err_i * dJ_i;     d loss / d p_{i,c} = dJ(rank of i) * (label_i == c ? -1 : +1)
+// followed by the softmax Jacobian in backward.  A group is the whole batch (per_image = 0,
+// the reference's behaviour) or one image (per_image = 1).
+//
+// How (all integer work exact, nothing compares floats):
+//   keys     one tile kernel (TMA in, TMA out): softmax, then a 32-bit key per (pixel, class)
+//            key = ((0x3F800000 - bits(err)) << 1) | fg  -> ascending key order = descending err,
+//            ignored pixels get 0xFFFFFFFF.  err is in [0, 1] so 30 key bits carry it exactly.
+//   sort     segmented LSD radix sort of (key, pixel index) pairs on key bits 1..30, kBits per
+//            pass.  Each pass: per-tile digit histogram -> per-segment scan -> stable scatter.
+//            The scatter ranks with warp match-any + per-warp counters, reorders the tile in
+//            shared memory and writes each digit's run contiguously.  No kernel waits on another.
+//   jaccard  one pass over the sorted pairs: integer prefix count of fg (tile counts come from
+//            atomics in the last scatter), dJ from the integer counts
+//                fg step: dJ = 1/U,   bg step: dJ = I/(U*(U+1)),   U = 0 (no fg, first) -> 1
+//            with I = remaining fg, U = union before the step; accumulates err*dJ and scatters
+//            dJ to pixel order (the `jacc` output).
+//   backward one tile kernel: softmax recomputed, g = p*(gp - sum p*gp), zero at ignored pixels.
 #include "common.cuh"
-using namespace b200;
-extern "C" size_t b200_lovasz_workspace_bytes(int64_t, int64_t, int64_t, int) { return 0; }
-extern "C" int b200_lovasz_forward(const void *, const int64_t *, float *, float *, void *, size_t,
-                                   int64_t, int64_t, int64_t, int, int64_t, int, void *) {
-    set_error("lovasz: not built yet");
-    return B200_ERR_UNSUPPORTED;
+
+namespace b200 {
+namespace {
+
+constexpr int kBits = 10;
+constexpr int kBins = 1 << kBits;
+constexpr int kPasses = 3;                 // key bits 1..30
+constexpr int kSortThreads = 256;
+constexpr int kSortItems = 32;
+constexpr int kSortTile = kSortThreads * kSortItems;   // 8192 pairs per tile
+constexpr int kSortWarps = kSortThreads / 32;
+static_assert(kBins % kSortThreads == 0, "each thread scans kBins / kSortThreads bins");
+constexpr uint32_t kKeyIgnored = 0xFFFFFFFFu;
+constexpr uint32_t kOneBits = 0x3F800000u;
+
+constexpr int kTileThreads = 256;
+
+__device__ __forceinline__ uint32_t lanemask_lt() {
+    uint32_t m;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+    return m;
 }
-extern "C" int b200_lovasz_backward(const float *, const void *, const int64_t *, const float *,
-                                    void *, int64_t, int64_t, int64_t, int, int64_t, int, void *) {
-    set_error("lovasz: not built yet");
-    return B200_ERR_UNSUPPORTED;
+
+// ---------------------------------------------------------------- geometry
+
+struct LovaszGeom {
+    int64_t N, C, M;
+    int per_image;
+    int64_t G, L, S;          // groups, pixels per group, segments
+    int64_t T;                // sort tiles per segment
+    // tile kernels
+    int TP, KS, CB, nbox, rows;
+    int64_t tiles_per_image, total_tiles;
+};
+
+struct Workspace {
+    uint32_t *keysA, *keysB, *valsA, *valsB;
+    uint32_t *hist;       // [S][T][kBins]
+    uint32_t *fghist;     // [S][T][kBins]  (last pass)
+    uint32_t *n_pos;      // [S]
+    double *partial;      // [S][T]
+    unsigned *status;     // 1 word
+    size_t bytes;
+};
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+Workspace carve(void *base, const LovaszGeom &g) {
+    Workspace w{};
+    char *p = static_cast<char *>(base);
+    size_t off = 0;
+    const size_t e = size_t(g.S) * g.L;
+    auto take = [&](size_t bytes) {
+        char *r = p ? p + off : nullptr;
+        off += align256(bytes);
+        return r;
+    };
+    w.status = reinterpret_cast<unsigned *>(take(256));
+    w.keysA = reinterpret_cast<uint32_t *>(take(e * 4));
+    w.keysB = reinterpret_cast<uint32_t *>(take(e * 4));
+    w.valsA = reinterpret_cast<uint32_t *>(take(e * 4));
+    w.valsB = reinterpret_cast<uint32_t *>(take(e * 4));
+    w.hist = reinterpret_cast<uint32_t *>(take(size_t(g.S) * g.T * kBins * 4));
+    w.fghist = reinterpret_cast<uint32_t *>(take(size_t(g.S) * g.T * kBins * 4));
+    w.n_pos = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
+    w.partial = reinterpret_cast<double *>(take(size_t(g.S) * g.T * 8));
+    w.bytes = off;
+    return w;
+}
+
+bool make_geom(LovaszGeom &g, int64_t N, int64_t C, int64_t M, int per_image) {
+    g.N = N; g.C = C; g.M = M; g.per_image = per_image;
+    g.G = per_image ? N : 1;
+    g.L = per_image ? M : N * M;
+    g.S = g.G * C;
+    g.T = (g.L + kSortTile - 1) / kSortTile;
+    int TP = 256;
+    while (TP > 32 && size_t(C) * TP * 4 > 40 * 1024) TP >>= 1;
+    while (TP > 32 && TP / 2 >= M) TP >>= 1;
+    g.TP = TP;
+    g.KS = kTileThreads / TP;
+    g.nbox = int((C + 255) / 256);
+    g.CB = int((C + g.nbox - 1) / g.nbox);
+    g.rows = g.nbox * g.CB;
+    g.tiles_per_image = (M + TP - 1) / TP;
+    g.total_tiles = N * g.tiles_per_image;
+    return true;
+}
+
+// --------------------------------------------------- tile kernels (keys, backward)
+
+struct TileArgs {
+    const float *logits;
+    const int64_t *labels;
+    uint32_t *keys;          // keys kernel: segment-major output
+    const float *jacc;       // backward: segment-major input
+    const float *seg_grad;   // backward: [S]
+    float *grads;            // backward: [N, C, M]
+    unsigned *status;
+    int64_t ignore;
+    LovaszGeom g;
+};
+
+// Offset of (image n, class c, pixel m) in a segment-major array.
+__device__ __forceinline__ int64_t seg_offset(const LovaszGeom &g, int64_t n, int64_t c, int64_t m) {
+    return g.per_image ? (n * g.C + c) * g.M + m : c * (g.N * g.M) + n * g.M + m;
+}
+
+// BWD = false: logits tile -> key tile (in place, 4 bytes each) -> keys.
+// BWD = true : logits tile + jacc tile -> gradient tile (in place) -> grads.
+template <bool BWD, bool TMA>
+__global__ void __launch_bounds__(kTileThreads)
+lovasz_tile_kernel(const TileArgs a, const __grid_constant__ CUtensorMap map_logits,
+                   const __grid_constant__ CUtensorMap map_seg,
+                   const __grid_constant__ CUtensorMap map_grads) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar;
+    const LovaszGeom &g = a.g;
+    const int TP = g.TP, KS = g.KS, C = int(g.C);
+    unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    const size_t tile_bytes_al = (size_t(g.rows) * TP * 4 + 127) & ~size_t(127);
+    float *tile = reinterpret_cast<float *>(base);
+    float *jt = reinterpret_cast<float *>(base + tile_bytes_al);                 // BWD only
+    float *red = reinterpret_cast<float *>(base + (BWD ? 2 : 1) * tile_bytes_al);  // [2][256]
+
+    const int tid = threadIdx.x, p = tid % TP, ks = tid / TP, slab = KS * TP;
+    if (TMA && tid == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    uint32_t phase = 0;
+    const uint32_t tx_bytes = uint32_t(g.nbox) * g.CB * TP * 4 * (BWD ? 2 : 1);
+
+    for (int64_t t = blockIdx.x; t < g.total_tiles; t += gridDim.x) {
+        const int64_t n = t / g.tiles_per_image;
+        const int64_t p0 = (t % g.tiles_per_image) * TP;
+        const int64_t img_base = n * g.C * g.M;
+        if (TMA) {
+            if (tid == 0) {
+                mbar_expect_tx(&bar, tx_bytes);
+                for (int b = 0; b < g.nbox; ++b) {
+                    tma_load_3d(tile + size_t(b) * g.CB * TP, &map_logits, int(p0), b * g.CB, int(n), &bar);
+                    if (BWD) tma_load_3d(jt + size_t(b) * g.CB * TP, &map_seg, int(p0), b * g.CB, int(n), &bar);
+                }
+            }
+        } else {
+            for (int idx = tid; idx < C * TP; idx += kTileThreads) {
+                const int j = idx / TP, pp = idx % TP;
+                const int64_t px = p0 + pp;
+                tile[idx] = px < g.M ? a.logits[img_base + int64_t(j) * g.M + px] : 0.f;
+                if (BWD) jt[idx] = px < g.M ? a.jacc[seg_offset(g, n, j, px)] : 0.f;
+            }
+        }
+        const int64_t pix = p0 + p;
+        const bool inb = pix < g.M;
+        const int64_t lb = inb ? a.labels[n * g.M + pix] : a.ignore;
+        const bool valid = inb && lb != a.ignore;
+        if (TMA) {
+            const bool ok = mbar_wait_bounded(&bar, phase, a.status);
+            if (!__syncthreads_and(ok)) break;
+            phase ^= 1;
+        } else {
+            __syncthreads();
+        }
+        float *col = tile + p;
+        // softmax statistics
+        float m = -3.402823466e38f;
+        for (int j = ks; j < C; j += KS) m = fmaxf(m, col[j * TP]);
+        if (KS > 1) {
+            red[tid] = m;
+            __syncthreads();
+            for (int q = 0; q < KS; ++q) m = fmaxf(m, red[q * TP + p]);
+        }
+        float s = 0.f;
+        for (int j = ks; j < C; j += KS) s += exp_fast(col[j * TP] - m);
+        if (KS > 1) {
+            red[slab + tid] = s;
+            __syncthreads();
+            s = 0.f;
+            for (int q = 0; q < KS; ++q) s += red[slab + q * TP + p];
+        }
+        const float inv_s = 1.f / s;
+
+        if (!BWD) {
+            uint32_t *kcol = reinterpret_cast<uint32_t *>(col);
+            for (int j = ks; j < C; j += KS) {
+                uint32_t key = kKeyIgnored;
+                if (valid) {
+                    const float pr = exp_fast(col[j * TP] - m) * inv_s;
+                    const bool fg = (j == lb);
+                    const float err = fg ? 1.f - pr : pr;
+                    uint32_t eb = __float_as_uint(fmaxf(err, 0.f));
+                    eb = eb > kOneBits ? kOneBits : eb;
+                    key = ((kOneBits - eb) << 1) | (fg ? 1u : 0u);
+                }
+                kcol[j * TP] = key;
+            }
+        } else {
+            const float *jcol = jt + p;
+            const int64_t gseg = g.per_image ? n * g.C : 0;
+            float dot = 0.f;
+            for (int j = ks; j < C; j += KS) {
+                const float pr = exp_fast(col[j * TP] - m) * inv_s;
+                const float gp = (j == lb ? -jcol[j * TP] : jcol[j * TP]) * a.seg_grad[gseg + j];
+                dot += pr * gp;
+            }
+            if (KS > 1) {
+                __syncthreads();          // red[0..slab) is free again (everyone has read the maxima)
+                red[tid] = dot;
+                __syncthreads();
+                dot = 0.f;
+                for (int q = 0; q < KS; ++q) dot += red[q * TP + p];
+            }
+            for (int j = ks; j < C; j += KS) {
+                float gl = 0.f;
+                if (valid) {
+                    const float pr = exp_fast(col[j * TP] - m) * inv_s;
+                    const float gp = (j == lb ? -jcol[j * TP] : jcol[j * TP]) * a.seg_grad[gseg + j];
+                    gl = pr * (gp - dot);
+                }
+                col[j * TP] = gl;
+            }
+        }
+        // write the tile back
+        if (TMA) {
+            fence_proxy_async_smem();
+            __syncthreads();
+            if (tid == 0) {
+                for (int b = 0; b < g.nbox; ++b)
+                    tma_store_3d(BWD ? &map_grads : &map_seg, int(p0), b * g.CB, int(n),
+                                 tile + size_t(b) * g.CB * TP);
+                bulk_commit();
+                bulk_wait_read_all();
+            }
+        } else {
+            __syncthreads();
+            for (int idx = tid; idx < C * TP; idx += kTileThreads) {
+                const int j = idx / TP, pp = idx % TP;
+                const int64_t px = p0 + pp;
+                if (px < g.M) {
+                    if (BWD) a.grads[img_base + int64_t(j) * g.M + px] = tile[idx];
+                    else a.keys[seg_offset(g, n, j, px)] = reinterpret_cast<uint32_t *>(tile)[idx];
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (TMA && tid == 0) bulk_wait_all();
+}
+
+// ------------------------------------------------------------------ sort kernels
+//
+// Element order inside a tile is "warp-striped": warp w owns the contiguous chunk
+// [w*32*kSortItems, (w+1)*32*kSortItems) and in round r its lane l holds element
+// chunk + r*32 + l, so every global access of a round is one coalesced 128-byte line and
+// (warp, round, lane) order equals array order -- which is what makes the ranking stable.
+
+__device__ __forceinline__ uint32_t digit_of(uint32_t key, int shift) {
+    return (key >> shift) & (kBins - 1);
+}
+__device__ __forceinline__ bool key_is_fg(uint32_t key) { return (key & 1u) && key != kKeyIgnored; }
+
+// Per-tile digit histogram (plain shared-memory atomics: cost follows the multiplicity of a
+// digit inside a warp, which is low for the uniform low digits and bounded by 32 otherwise).
+// LAST: also a histogram of the foreground elements.   hist[seg][tile][bin]
+template <bool LAST>
+__global__ void __launch_bounds__(kSortThreads)
+sort_hist_kernel(const uint32_t *__restrict__ keys, uint32_t *__restrict__ hist,
+                 uint32_t *__restrict__ fghist, int64_t L, int64_t T, int shift) {
+    __shared__ uint32_t sh[kBins];
+    __shared__ uint32_t shfg[LAST ? kBins : 1];
+    const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
+    const int64_t t0 = tile * kSortTile;
+    const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
+    const uint32_t *src = keys + seg * L + t0;
+    for (int b = threadIdx.x; b < kBins; b += kSortThreads) {
+        sh[b] = 0;
+        if (LAST) shfg[b] = 0;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wbase = warp * (32 * kSortItems);
+    uint32_t key[kSortItems];
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = wbase + r * 32 + lane;
+        key[r] = idx < n ? __ldg(src + idx) : 0u;
+    }
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = wbase + r * 32 + lane;
+        if (idx < n) {
+            const uint32_t d = digit_of(key[r], shift);
+            atomicAdd(&sh[d], 1u);
+            if (LAST && key_is_fg(key[r])) atomicAdd(&shfg[d], 1u);
+        }
+    }
+    __syncthreads();
+    const int64_t o = (seg * T + tile) * kBins;
+    for (int b = threadIdx.x; b < kBins; b += kSortThreads) {
+        hist[o + b] = sh[b];
+        if (LAST) fghist[o + b] = shfg[b];
+    }
+}
+
+// Exclusive scan of kBins per-thread values across a block of kBins threads.
+__device__ __forceinline__ uint32_t block_excl_scan_1024(uint32_t v, uint32_t *warp_tot, uint32_t *total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+    }
+    __syncthreads();
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const uint32_t w = warp_tot[lane];
+        uint32_t wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t u = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += u;
+        }
+        warp_tot[lane] = wi - w;
+        if (lane == 31 && total) *total = wi;
+    }
+    __syncthreads();
+    return warp_tot[warp] + incl - v;
+}
+
+// Per-segment scan: counts hist[seg][tile][bin] -> exclusive offsets inside the segment in
+// (bin, tile) order.  One block of kBins threads per segment.  LAST: the foreground
+// histogram gets the same treatment and its grand total is the segment's n_pos.
+template <bool LAST>
+__global__ void __launch_bounds__(kBins)
+sort_scan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fghist,
+                 uint32_t *__restrict__ n_pos, int64_t T) {
+    __shared__ uint32_t warp_tot[32];
+    __shared__ uint32_t grand;
+    const int64_t seg = blockIdx.x;
+    const int b = threadIdx.x;
+#pragma unroll
+    for (int which = 0; which < (LAST ? 2 : 1); ++which) {
+        uint32_t *h = (which ? fghist : hist) + seg * T * kBins;
+        uint32_t total = 0;
+        for (int64_t t = 0; t < T; ++t) total += h[t * kBins + b];
+        uint32_t run = block_excl_scan_1024(total, warp_tot, &grand);
+        for (int64_t t = 0; t < T; ++t) {
+            const uint32_t c = h[t * kBins + b];
+            h[t * kBins + b] = run;
+            run += c;
+        }
+        if (which && b == 0) n_pos[seg] = grand;
+        __syncthreads();
+    }
+}
+
+// Shared-memory layout of the two ranking kernels.
+//   match  u32 [warps][kBins]   per-warp lane masks of the current round (zero between rounds)
+//   wcnt   u16 [warps][kBins]   per-warp digit counters -> exclusive prefix over warps
+//   (scatter) bufk u32 [tile], bufv u32 [tile] (aliases match), binstart/goff u32 [kBins]
+//   (jaccard) wfg u16 [warps][kBins], off/fgoff u32 [kBins]
+constexpr size_t kMatchBytes = size_t(kSortWarps) * kBins * 4;
+constexpr size_t kCntBytes = size_t(kSortWarps) * kBins * 2;
+constexpr size_t kTileWordsBytes = size_t(kSortTile) * 4;
+static_assert(kMatchBytes <= kTileWordsBytes, "the value buffer reuses the match masks");
+constexpr size_t kScatterSmem = kTileWordsBytes /*bufv|match*/ + kTileWordsBytes /*bufk*/ + kCntBytes + 2 * kBins * 4;
+constexpr size_t kJaccardSmem = kMatchBytes + 2 * kCntBytes + 2 * kBins * 4;
+
+// One ranking round of a warp: which lanes hold my digit (through an atomic OR into the
+// warp's mask word of that digit), my stable rank among them, and the warp counter update.
+// Returns the rank of this lane's element inside (warp, digit) counting all earlier rounds.
+__device__ __forceinline__ uint32_t rank_round(uint32_t d, uint32_t *wmatch, uint16_t *wcnt, int lane,
+                                               uint32_t lt, uint32_t &peers_out) {
+    atomicOr(&wmatch[d], 1u << lane);
+    __syncwarp();
+    const uint32_t peers = wmatch[d];
+    __syncwarp();
+    const int leader = __ffs(peers) - 1;
+    uint32_t old = 0;
+    if (lane == leader) {
+        old = wcnt[d];
+        wcnt[d] = uint16_t(old + __popc(peers));
+        wmatch[d] = 0;
+    }
+    __syncwarp();
+    old = __shfl_sync(0xffffffffu, old, leader);
+    peers_out = peers;
+    return old + __popc(peers & lt);
+}
+
+// Stable scatter of one tile (passes that are not the last).  vals_in == nullptr: values are
+// the positions inside the segment (first pass).
+__global__ void __launch_bounds__(kSortThreads, 2)
+sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__restrict__ vals_in,
+                    uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
+                    const uint32_t *__restrict__ offsets, int64_t L, int64_t T, int shift) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint32_t *match = reinterpret_cast<uint32_t *>(smem_raw);
+    uint32_t *bufv = match;                                                  // after ranking
+    uint32_t *bufk = reinterpret_cast<uint32_t *>(smem_raw + kTileWordsBytes);
+    uint16_t *wcnt_all = reinterpret_cast<uint16_t *>(smem_raw + 2 * kTileWordsBytes);
+    uint32_t *binstart = reinterpret_cast<uint32_t *>(smem_raw + 2 * kTileWordsBytes + kCntBytes);
+    uint32_t *goff = binstart + kBins;
+    __shared__ uint32_t warp_tot[32];
+
+    const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
+    const int64_t t0 = tile * kSortTile;
+    const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
+    const int64_t sbase = seg * L;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wbase = warp * (32 * kSortItems);
+
+    for (int i = tid; i < int(kMatchBytes / 4); i += kSortThreads) match[i] = 0;
+    for (int i = tid; i < int(kCntBytes / 4); i += kSortThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
+    uint32_t key[kSortItems];
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = wbase + r * 32 + lane;
+        key[r] = idx < n ? __ldg(keys_in + sbase + t0 + idx) : 0xFFFFFFFFu;
+    }
+    __syncthreads();
+    uint32_t rank2[kSortItems / 2];     // two 16-bit ranks per register
+    uint32_t *wmatch = match + warp * kBins;
+    uint16_t *wcnt = wcnt_all + warp * kBins;
+    const uint32_t lt = lanemask_lt();
+#pragma unroll
+    for (int r = 0; r < kSortItems; r += 2) {
+        uint32_t peers;
+        const uint32_t r0 = rank_round(digit_of(key[r], shift), wmatch, wcnt, lane, lt, peers);
+        const uint32_t r1 = rank_round(digit_of(key[r + 1], shift), wmatch, wcnt, lane, lt, peers);
+        rank2[r / 2] = r0 | (r1 << 16);
+    }
+    __syncthreads();
+    // per digit: exclusive prefix over warps (in place), then over digits
+    constexpr int BPT = kBins / kSortThreads;
+    uint32_t cnt[BPT];
+    uint32_t mine = 0;
+#pragma unroll
+    for (int q = 0; q < BPT; ++q) {
+        const int b = BPT * tid + q;
+        uint32_t run = 0;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; ++w) {
+            const uint32_t c = wcnt_all[w * kBins + b];
+            wcnt_all[w * kBins + b] = uint16_t(run);
+            run += c;
+        }
+        cnt[q] = run;
+        mine += run;
+    }
+    {
+        uint32_t incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            const uint32_t w = lane < kSortWarps ? warp_tot[lane] : 0;
+            uint32_t wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= o) wi += v;
+            }
+            warp_tot[lane] = wi - w;
+        }
+        __syncthreads();
+        uint32_t excl = warp_tot[warp] + incl - mine;
+        const uint32_t *off = offsets + (seg * T + tile) * kBins;
+#pragma unroll
+        for (int q = 0; q < BPT; ++q) {
+            const int b = BPT * tid + q;
+            binstart[b] = excl;
+            goff[b] = __ldg(off + b) - excl;
+            excl += cnt[q];
+        }
+    }
+    __syncthreads();
+    // local sorted position; keys and values into the reorder buffers
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = wbase + r * 32 + lane;
+        const uint32_t d = digit_of(key[r], shift);
+        const uint32_t rk = (r & 1) ? (rank2[r / 2] >> 16) : (rank2[r / 2] & 0xffffu);
+        const uint32_t lp = binstart[d] + wcnt[d] + rk;
+        bufk[lp] = key[r];
+        uint32_t v = uint32_t(t0 + idx);
+        if (vals_in && idx < n) v = __ldg(vals_in + sbase + t0 + idx);
+        bufv[lp] = v;
+    }
+    __syncthreads();
+    // each digit's run goes out contiguously
+#pragma unroll 4
+    for (int i = tid; i < n; i += kSortThreads) {
+        const uint32_t k = bufk[i];
+        const uint32_t gp = goff[digit_of(k, shift)] + uint32_t(i);
+        keys_out[sbase + gp] = k;
+        vals_out[sbase + gp] = bufv[i];
+    }
+}
+
+// Last pass, fused with the Jaccard step.  Nothing is moved: the final rank of an element is
+//   i  = offsets[digit][tile] + (rank among the tile's elements with this digit)
+//   cs = fgoffsets[digit][tile] + (rank among the tile's FOREGROUND elements with this digit)
+// (elements with a smaller top digit come first, equal digits keep the order of the previous
+// passes), which is all dJ needs.  Writes dJ to the pixel's slot and a loss partial per tile.
+__global__ void __launch_bounds__(kSortThreads, 2)
+rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals,
+                    const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ fgoffsets,
+                    const uint32_t *__restrict__ n_pos_seg, float *__restrict__ jacc,
+                    double *__restrict__ partial, int64_t L, int64_t T, int shift) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint32_t *match = reinterpret_cast<uint32_t *>(smem_raw);
+    uint16_t *wcnt_all = reinterpret_cast<uint16_t *>(smem_raw + kMatchBytes);
+    uint16_t *wfg_all = reinterpret_cast<uint16_t *>(smem_raw + kMatchBytes + kCntBytes);
+    uint32_t *off = reinterpret_cast<uint32_t *>(smem_raw + kMatchBytes + 2 * kCntBytes);
+    uint32_t *fgoff = off + kBins;
+    __shared__ double sh_d[32];
+
+    const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
+    const int64_t t0 = tile * kSortTile;
+    const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
+    const int64_t sbase = seg * L;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wbase = warp * (32 * kSortItems);
+
+    for (int i = tid; i < int(kMatchBytes / 4); i += kSortThreads) match[i] = 0;
+    for (int i = tid; i < int(2 * kCntBytes / 4); i += kSortThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
+    {
+        const int64_t o = (seg * T + tile) * kBins;
+        for (int b = tid; b < kBins; b += kSortThreads) {
+            off[b] = __ldg(offsets + o + b);
+            fgoff[b] = __ldg(fgoffsets + o + b);
+        }
+    }
+    uint32_t key[kSortItems];
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = wbase + r * 32 + lane;
+        key[r] = idx < n ? __ldg(keys + sbase + t0 + idx) : 0xFFFFFFFFu;
+    }
+    __syncthreads();
+    uint32_t rkfg[kSortItems];          // rank | fg rank << 16
+    uint32_t *wmatch = match + warp * kBins;
+    uint16_t *wcnt = wcnt_all + warp * kBins;
+    uint16_t *wfg = wfg_all + warp * kBins;
+    const uint32_t lt = lanemask_lt();
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const uint32_t d = digit_of(key[r], shift);
+        const bool fg = key_is_fg(key[r]);
+        const uint32_t fgball = __ballot_sync(0xffffffffu, fg);
+        uint32_t peers;
+        const uint32_t fgold_src = wfg[d];            // read before any leader updates it this round
+        const uint32_t rk = rank_round(d, wmatch, wcnt, lane, lt, peers);
+        const int leader = __ffs(peers) - 1;
+        const uint32_t fgold = fgold_src;            // every peer read the same word
+        if (lane == leader) wfg[d] = uint16_t(fgold + __popc(peers & fgball));
+        __syncwarp();
+        rkfg[r] = rk | ((fgold + __popc(peers & fgball & lt)) << 16);
+    }
+    __syncthreads();
+    constexpr int BPT = kBins / kSortThreads;
+#pragma unroll
+    for (int q = 0; q < BPT; ++q) {
+        const int b = BPT * tid + q;
+        uint32_t run = 0, runfg = 0;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; ++w) {
+            const uint32_t c = wcnt_all[w * kBins + b];
+            wcnt_all[w * kBins + b] = uint16_t(run);
+            run += c;
+            const uint32_t f = wfg_all[w * kBins + b];
+            wfg_all[w * kBins + b] = uint16_t(runfg);
+            runfg += f;
+        }
+    }
+    __syncthreads();
+    const uint32_t n_pos = __ldg(n_pos_seg + seg);
+    float acc = 0.f;
+    float *dst = jacc + sbase;
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = wbase + r * 32 + lane;
+        if (idx < n) {
+            const uint32_t k = key[r];
+            const uint32_t d = digit_of(k, shift);
+            const bool ign = k == kKeyIgnored;
+            const bool fg = key_is_fg(k);
+            const uint32_t i_glob = off[d] + wcnt[d] + (rkfg[r] & 0xffffu);
+            const uint32_t cs_before = fgoff[d] + wfg[d] + (rkfg[r] >> 16);
+            const uint32_t union_before = n_pos + (i_glob - cs_before);
+            const float I = float(n_pos - cs_before);
+            const float U = float(union_before);
+            float dj;
+            if (fg) dj = 1.f / U;
+            else dj = union_before == 0u ? 1.f : I / (U * (U + 1.f));
+            const float err = ign ? 0.f : __uint_as_float(kOneBits - (k >> 1));
+            acc += err * dj;
+            const uint32_t v = __ldg(vals + sbase + t0 + idx);
+            dst[v] = dj;
+        }
+    }
+    double a = double(acc);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+    if (lane == 0) sh_d[warp] = a;
+    __syncthreads();
+    if (tid == 0) {
+        double s = 0.0;
+        for (int w = 0; w < kSortWarps; ++w) s += sh_d[w];
+        partial[seg * T + tile] = s;
+    }
+}
+
+// loss[seg] = sum of the segment's tile partials, fixed order.
+__global__ void __launch_bounds__(32)
+loss_kernel(const double *__restrict__ partial, float *__restrict__ loss, int64_t T) {
+    const int64_t seg = blockIdx.x;
+    double s = 0.0;
+    for (int64_t t = threadIdx.x; t < T; t += 32) s += partial[seg * T + t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (threadIdx.x == 0) loss[seg] = float(s);
+}
+
+// ------------------------------------------------------------------- host side
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_args(const char *who, int64_t N, int64_t C, int64_t M, int dtype) {
+    if (N < 0 || C < 1 || M < 0) {
+        set_error("%s: bad shape N=%lld C=%lld M=%lld", who, (long long)N, (long long)C, (long long)M);
+        return B200_ERR_ARG;
+    }
+    if (dtype != B200_F32) {
+        set_error("%s: float32 logits only (cast half inputs first, as autocast does)", who);
+        return B200_ERR_UNSUPPORTED;
+    }
+    if (C > 1024) {
+        set_error("%s: C=%lld exceeds the supported 1024 classes", who, (long long)C);
+        return B200_ERR_UNSUPPORTED;
+    }
+    if (N * M >= (int64_t(1) << 31) || N * C * M >= (int64_t(1) << 40)) {
+        set_error("%s: tensor too large (N*M must stay below 2^31)", who);
+        return B200_ERR_UNSUPPORTED;
+    }
+    return B200_OK;
+}
+
+// Tensor maps of the two layouts a tile kernel touches.
+bool make_maps(const LovaszGeom &g, const void *logits_like, const void *seg_like, CUtensorMap *map_img,
+               CUtensorMap *map_seg, int seg_dtype) {
+    const uint64_t dims[3] = {uint64_t(g.M), uint64_t(g.C), uint64_t(g.N)};
+    const uint32_t box[3] = {uint32_t(g.TP), uint32_t(g.CB), 1u};
+    const uint64_t st_img[3] = {4, uint64_t(g.M) * 4, uint64_t(g.C) * g.M * 4};
+    const uint64_t st_glob[3] = {4, uint64_t(g.N) * g.M * 4, uint64_t(g.M) * 4};
+    if (logits_like && !encode_tensor_map(map_img, B200_F32, logits_like, 3, dims, st_img, box)) return false;
+    if (seg_like &&
+        !encode_tensor_map(map_seg, seg_dtype, seg_like, 3, dims, g.per_image ? st_img : st_glob, box))
+        return false;
+    return true;
+}
+
+template <bool BWD>
+int launch_tile(const TileArgs &a, cudaStream_t stream) {
+    const LovaszGeom &g = a.g;
+    const size_t tile_al = (size_t(g.rows) * g.TP * 4 + 127) & ~size_t(127);
+    const size_t smem = 128 + (BWD ? 2 : 1) * tile_al + 2 * kTileThreads * sizeof(float);
+    int per_sm = int((220 * 1024) / (smem + 1024));
+    if (per_sm > 8) per_sm = 8;
+    if (per_sm < 1) {
+        set_error("lovasz: C=%lld needs %zu bytes of shared memory per tile", (long long)g.C, smem);
+        return B200_ERR_UNSUPPORTED;
+    }
+    int64_t grid = int64_t(sm_count()) * per_sm;
+    if (grid > g.total_tiles) grid = g.total_tiles;
+    const void *seg_ptr = BWD ? static_cast<const void *>(a.jacc) : static_cast<const void *>(a.keys);
+    const bool tma_ok = (g.M * 4) % 16 == 0 && aligned16(a.logits) && aligned16(seg_ptr) &&
+                        (!BWD || aligned16(a.grads));
+    CUtensorMap m_logits{}, m_seg{}, m_grads{};
+    if (tma_ok) {
+        if (!make_maps(g, a.logits, seg_ptr, &m_logits, &m_seg, BWD ? B200_F32 : 99)) return B200_ERR_LAUNCH;
+        if (BWD && !make_maps(g, a.grads, nullptr, &m_grads, nullptr, 0)) return B200_ERR_LAUNCH;
+    }
+    auto launch = [&](auto kern) -> int {
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+            return launch_status("cudaFuncSetAttribute(lovasz tile)");
+        kern<<<dim3(unsigned(grid)), kTileThreads, smem, stream>>>(a, m_logits, m_seg, m_grads);
+        return launch_status(BWD ? "lovasz backward kernel launch" : "lovasz keys kernel launch");
+    };
+    return tma_ok ? launch(lovasz_tile_kernel<BWD, true>) : launch(lovasz_tile_kernel<BWD, false>);
+}
+
+
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_lovasz_workspace_bytes(int64_t N, int64_t C, int64_t M, int per_image) {
+    if (N <= 0 || C <= 0 || M <= 0) return 256;
+    LovaszGeom g{};
+    make_geom(g, N, C, M, per_image);
+    return carve(nullptr, g).bytes;
+}
+
+extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, float *loss,
+                                   float *jacc, void *workspace, size_t workspace_bytes, int64_t N,
+                                   int64_t C, int64_t M, int dtype, int64_t ignore_index,
+                                   int per_image, void *stream) {
+    int rc = check_args("b200_lovasz_forward", N, C, M, dtype);
+    if (rc != B200_OK) return rc;
+    if (N * M == 0) return B200_OK;
+    if (!logits || !labels || !loss || !jacc || !workspace) {
+        set_error("b200_lovasz_forward: null pointer");
+        return B200_ERR_ARG;
+    }
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) {
+        set_error("b200_lovasz_forward: workspace must be 256-byte aligned");
+        return B200_ERR_ARG;
+    }
+    LovaszGeom g{};
+    make_geom(g, N, C, M, per_image);
+    Workspace w = carve(workspace, g);
+    if (workspace_bytes < w.bytes) {
+        set_error("b200_lovasz_forward: workspace of %zu bytes required, got %zu", w.bytes, workspace_bytes);
+        return B200_ERR_WORKSPACE;
+    }
+    if (g.S * g.T >= (int64_t(1) << 31)) {
+        set_error("b200_lovasz_forward: too many sort tiles");
+        return B200_ERR_UNSUPPORTED;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(w.status, 0, 256, s) != cudaSuccess) return launch_status("lovasz status memset");
+
+    TileArgs ta{};
+    ta.logits = static_cast<const float *>(logits);
+    ta.labels = labels;
+    ta.keys = w.keysA;
+    ta.status = w.status;
+    ta.ignore = ignore_index;
+    ta.g = g;
+    if ((rc = launch_tile<false>(ta, s)) != B200_OK) return rc;
+
+    if (cudaFuncSetAttribute(sort_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(kScatterSmem)) != cudaSuccess ||
+        cudaFuncSetAttribute(rank_jaccard_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             int(kJaccardSmem)) != cudaSuccess)
+        return launch_status("cudaFuncSetAttribute(lovasz sort kernels)");
+    const unsigned nblk = unsigned(g.S * g.T);
+    const uint32_t *kin = w.keysA;
+    const uint32_t *vin = nullptr;
+    uint32_t *kout = w.keysB, *vout = w.valsB;
+    for (int pass = 0; pass < kPasses - 1; ++pass) {
+        const int shift = 1 + pass * kBits;
+        sort_hist_kernel<false><<<nblk, kSortThreads, 0, s>>>(kin, w.hist, nullptr, g.L, g.T, shift);
+        if ((rc = launch_status("lovasz sort histogram launch")) != B200_OK) return rc;
+        sort_scan_kernel<false><<<unsigned(g.S), kBins, 0, s>>>(w.hist, nullptr, nullptr, g.T);
+        if ((rc = launch_status("lovasz sort scan launch")) != B200_OK) return rc;
+        sort_scatter_kernel<<<nblk, kSortThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, g.L, g.T, shift);
+        if ((rc = launch_status("lovasz sort scatter launch")) != B200_OK) return rc;
+        kin = kout;
+        vin = vout;
+        if (kout == w.keysB) { kout = w.keysA; vout = w.valsA; } else { kout = w.keysB; vout = w.valsB; }
+    }
+    {
+        const int shift = 1 + (kPasses - 1) * kBits;
+        sort_hist_kernel<true><<<nblk, kSortThreads, 0, s>>>(kin, w.hist, w.fghist, g.L, g.T, shift);
+        if ((rc = launch_status("lovasz last histogram launch")) != B200_OK) return rc;
+        sort_scan_kernel<true><<<unsigned(g.S), kBins, 0, s>>>(w.hist, w.fghist, w.n_pos, g.T);
+        if ((rc = launch_status("lovasz last scan launch")) != B200_OK) return rc;
+        rank_jaccard_kernel<<<nblk, kSortThreads, kJaccardSmem, s>>>(kin, vin, w.hist, w.fghist, w.n_pos, jacc,
+                                                                      w.partial, g.L, g.T, shift);
+        if ((rc = launch_status("lovasz rank+jaccard launch")) != B200_OK) return rc;
+    }
+    loss_kernel<<<unsigned(g.S), 32, 0, s>>>(w.partial, loss, g.T);
+    return launch_status("lovasz loss launch");
+}
+
+extern "C" int b200_lovasz_backward(const float *grad, const void *logits, const int64_t *labels,
+                                    const float *jacc, void *grad_logits, int64_t N, int64_t C,
+                                    int64_t M, int dtype, int64_t ignore_index, int per_image,
+                                    void *stream) {
+    int rc = check_args("b200_lovasz_backward", N, C, M, dtype);
+    if (rc != B200_OK) return rc;
+    if (N * M == 0) return B200_OK;
+    if (!grad || !logits || !labels || !jacc || !grad_logits) {
+        set_error("b200_lovasz_backward: null pointer");
+        return B200_ERR_ARG;
+    }
+    LovaszGeom g{};
+    make_geom(g, N, C, M, per_image);
+    TileArgs ta{};
+    ta.logits = static_cast<const float *>(logits);
+    ta.labels = labels;
+    ta.jacc = jacc;
+    ta.seg_grad = grad;
+    ta.grads = static_cast<float *>(grad_logits);
+    ta.status = nullptr;
+    ta.ignore = ignore_index;
+    ta.g = g;
+    return launch_tile<true>(ta, static_cast<cudaStream_t>(stream));
 }

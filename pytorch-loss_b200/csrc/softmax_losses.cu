@@ -529,6 +529,8 @@ int forward(const char *who, const void *logits, const int64_t *labels, void *lo
             int64_t ignore_index, float hp, void *stream) {
     int rc = check_shape(who, N, C, M);
     if (rc != B200_OK) return rc;
+    const int64_t P = N * M;
+    if (P == 0 && !out) return B200_OK;   // empty input, nothing to write
     if (!losses && !out) {
         set_error("%s: at least one of losses / out must be given", who);
         return B200_ERR_ARG;
@@ -537,8 +539,6 @@ int forward(const char *who, const void *logits, const int64_t *labels, void *lo
         set_error("%s: workspace of %zu bytes required", who, kReduceWorkspaceBytes);
         return B200_ERR_WORKSPACE;
     }
-    const int64_t P = N * M;
-    if (P == 0 && !out) return B200_OK;
     if (P > 0 && (!logits || !labels)) {
         set_error("%s: null input pointer", who);
         return B200_ERR_ARG;

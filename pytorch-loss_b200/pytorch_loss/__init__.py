@@ -16,3 +16,6 @@ __all__ = [
     "LabelSmoothSoftmaxCEV3", "LSRCrossEntropyFunctionV3",
     "LargeMarginSoftmaxV3", "LargeMarginSoftmaxFuncV3", "LargeMarginSoftmaxFuncV3FB",
 ]
+from .lovasz_softmax import LovaszSoftmaxV3, LovaszSoftmaxFunctionV3
+
+__all__ += ["LovaszSoftmaxV3", "LovaszSoftmaxFunctionV3"]

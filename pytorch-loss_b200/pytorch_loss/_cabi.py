@@ -24,6 +24,7 @@ _vp, _i64, _int, _f32, _f64, _sz = _c.c_void_p, _c.c_int64, _c.c_int, _c.c_float
 SIGNATURES = {
     "b200_abi_version": (_int, []),
     "b200_last_error": (_c.c_char_p, []),
+    "b200_kernel_launch_count": (_c.c_uint64, []),
     "b200_reduce_workspace_bytes": (_sz, []),
     "b200_read_status": (_int, [_vp, _vp]),
     "b200_focal_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _int, _f32, _f32, _vp]),
@@ -173,3 +174,51 @@ def grad_mode_of(grad_output, pixel_shape):
     if tuple(grad_output.shape) != tuple(pixel_shape):
         grad_output = grad_output.expand(pixel_shape)
     return 2, grad_output.contiguous()
+
+
+# --- per-call device timing (used by the benchmark, off by default) ---------------------
+
+class CallTimer:
+    """Context manager: while active, every kernel-launching C-ABI call made through
+    `load_library()` is bracketed by CUDA events on the current stream.  `summary()`
+    returns {entry point: (calls, total milliseconds)} after a synchronise."""
+
+    def __init__(self):
+        self.records = []
+
+    def __enter__(self):
+        global _lib
+        self._real = load_library()
+        timer = self
+
+        class _Proxy:
+            def __getattr__(self, name):
+                fn = getattr(timer._real, name)
+                if not name.endswith(("_forward", "_backward", "_forward_backward")):
+                    return fn
+
+                def timed(*args):
+                    a = torch.cuda.Event(enable_timing=True)
+                    b = torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    rc = fn(*args)
+                    b.record()
+                    timer.records.append((name, a, b))
+                    return rc
+                return timed
+
+        _lib = _Proxy()
+        return self
+
+    def __exit__(self, *exc):
+        global _lib
+        _lib = self._real
+        return False
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b in self.records:
+            n, ms = out.get(name, (0, 0.0))
+            out[name] = (n + 1, ms + a.elapsed_time(b))
+        return out
