@@ -95,6 +95,28 @@ int b200_focal_forward_backward(const void *logits, const void *labels, void *lo
                                 void *grad_logits, int64_t E, int dtype, float gamma,
                                 float alpha, void *stream);
 
+/* Reducing focal forward that needs no workspace and allocates nothing.
+ * This entry point has no counterpart in the reference.  It is for callers that cannot
+ * provide device memory beyond inputs and outputs: a host that handed every byte of the GPU
+ * to its own pool at start-up, or a bare FFI caller with no allocator that must not cause a
+ * device-wide stall inside a hot loop.  The scratch of the reduction (64-byte header + one
+ * 16-byte partial per block, 16 448 bytes in total) is a fixed array inside the library's
+ * device image; every GPU that loads the library holds it until the process exits.
+ *   - `out` (the 32-byte reduction record) is required, `losses` (E elements) is optional;
+ *     both, like the inputs, are the caller's device memory.
+ *   - E may be at most 2^28 = 268 435 456 elements; larger inputs are refused with
+ *     B200_ERR_UNSUPPORTED (use b200_focal_forward with your own workspace instead).
+ *   - The first call on each device looks up the array's device address (the device that
+ *     is current at that moment must be the one the pointers live on).  Make that first
+ *     call before any stream capture begins.
+ *   - All calls on a device share the one array and each call re-arms its header on
+ *     `stream` first.  Two calls that overlap on the GPU (different streams or threads)
+ *     race on it: serialise them.
+ * Neither this function nor anything it calls uses cudaMalloc, cudaFree or an allocating
+ * library routine.  Results are identical to b200_focal_forward on the same input. */
+int b200_focal_forward_noalloc(const void *logits, const void *labels, void *losses, void *out,
+                               int64_t E, int dtype, float gamma, float alpha, void *stream);
+
 /* -------------------------------------------------- label-smooth softmax CE ---
  * Replaces lsr_cpp.lsr_forward / lsr_backward (reference csrc/lsr_kernel.cu:296-322;
  * math at :66-185) including the ATen log_softmax/softmax calls and the Python-side

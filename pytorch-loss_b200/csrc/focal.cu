@@ -14,6 +14,8 @@
 // per-element loss at all (8 B/element), the backward recomputes (12 B/element).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace b200 {
 namespace {
 
@@ -285,4 +287,114 @@ extern "C" int b200_focal_forward_backward(const void *logits, const void *label
     prm.gamma = gamma;
     prm.alpha = alpha;
     return dispatch_focal<kFwdBwd, false>(prm, dtype, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------- focal forward without any allocation
+//
+// Some users of this library cannot hand it a workspace: a host that gave all device
+// memory to its own pool at start-up (a later cudaMalloc would fail or stall the device), or
+// a plain-FFI caller that has no allocator of its own and must not trigger one inside a
+// latency-critical loop.  For them the reducing focal forward also exists with its scratch
+// (ticket, status word, one partial per block) in a fixed array that lives in the library's
+// device image: kFocalNoAllocScratchBytes bytes on every GPU that loads the library, for
+// the life of the process.
+//
+// The array's name is only a host-side handle; the device address is looked up once per
+// device with cudaGetSymbolAddress while that device is current, and that address is what
+// the kernel receives.  All calls on a device share the array: calls that overlap on the
+// GPU (two streams, two threads) race on it and must be serialised by the caller.
+static __device__ __align__(256) unsigned char b200_focal_noalloc_scratch[b200::kPartialsOffset + 1024 * 16];
+
+namespace b200 {
+namespace {
+
+constexpr int kFocalNoAllocMaxBlocks = 1024;
+constexpr size_t kFocalNoAllocScratchBytes = kPartialsOffset + size_t(kFocalNoAllocMaxBlocks) * 16;
+constexpr int64_t kFocalNoAllocMaxElems = int64_t(1) << 28;
+constexpr int kMaxDevices = 64;
+
+// Device address of the scratch array on the current device (set up on first use).
+int focal_noalloc_scratch(void **out) {
+    static void *ptrs[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_error("b200_focal_forward_noalloc: cannot identify the current device");
+        return B200_ERR_LAUNCH;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, b200_focal_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            set_error("b200_focal_forward_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return B200_ERR_LAUNCH;
+        }
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return B200_OK;
+}
+
+template <typename T>
+int launch_focal_noalloc(const FocalParams &prm, cudaStream_t stream) {
+    const int vn = Vec16<T>::N;
+    int64_t want = (prm.E / vn + kThreads - 1) / kThreads;
+    int64_t cap = int64_t(sm_count()) * kBlocksPerSM;
+    if (cap > kFocalNoAllocMaxBlocks) cap = kFocalNoAllocMaxBlocks;   // one partial slot per block
+    if (want > cap) want = cap;
+    if (want < 1) want = 1;
+    const dim3 grid(static_cast<unsigned>(want));
+    const bool al = aligned16(prm.logits) && aligned16(prm.labels) && (!prm.losses || aligned16(prm.losses));
+    if (!al) {
+        focal_kernel_unaligned<T, kFwd, true><<<grid, kThreads, 0, stream>>>(prm);
+    } else if (prm.gamma == 2.f) {
+        focal_kernel<T, kFwd, true, true><<<grid, kThreads, 0, stream>>>(prm);
+    } else {
+        focal_kernel<T, kFwd, false, true><<<grid, kThreads, 0, stream>>>(prm);
+    }
+    return launch_status("focal no-alloc kernel launch");
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_focal_forward_noalloc(const void *logits, const void *labels, void *losses,
+                                          void *out, int64_t E, int dtype, float gamma, float alpha,
+                                          void *stream) {
+    if (E < 0 || !out) {
+        set_error("b200_focal_forward_noalloc: need E >= 0 and an output record");
+        return B200_ERR_ARG;
+    }
+    if (E > kFocalNoAllocMaxElems) {
+        set_error("b200_focal_forward_noalloc: E=%lld exceeds the maximum of %lld elements of this entry point; "
+                  "use b200_focal_forward with a caller-provided workspace",
+                  (long long)E, (long long)kFocalNoAllocMaxElems);
+        return B200_ERR_UNSUPPORTED;
+    }
+    if (E > 0 && (!logits || !labels)) {
+        set_error("b200_focal_forward_noalloc: null input pointer");
+        return B200_ERR_ARG;
+    }
+    if (dtype != B200_F32 && dtype != B200_F16) {
+        set_error("b200_focal_forward_noalloc: unknown dtype code %d", dtype);
+        return B200_ERR_ARG;
+    }
+    void *scratch = nullptr;
+    const int rc = focal_noalloc_scratch(&scratch);
+    if (rc != B200_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the array keeps whatever the previous call left: re-arm ticket and status word
+    if (cudaMemsetAsync(scratch, 0, kPartialsOffset, s) != cudaSuccess)
+        return launch_status("b200_focal_forward_noalloc: clearing the scratch header");
+    FocalParams prm{};
+    prm.logits = logits;
+    prm.labels = labels;
+    prm.losses = losses;
+    prm.workspace = scratch;
+    prm.out = static_cast<ReduceRecord *>(out);
+    prm.E = E;
+    prm.gamma = gamma;
+    prm.alpha = alpha;
+    return dtype == B200_F32 ? launch_focal_noalloc<float>(prm, s) : launch_focal_noalloc<__half>(prm, s);
 }
