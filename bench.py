@@ -214,6 +214,48 @@ def try_capture(crit, sets):
         return None
 
 
+def direct_calls(wl, sets, device):
+    """(forward, backward) callables that launch the workload's two C-ABI entry points on
+    input set i with preallocated outputs: what `roofline` times."""
+    from pytorch_loss import _cabi
+    lib = _cabi.load_library()
+    P = _cabi.ptr
+    st = _cabi.stream_ptr(device)
+    ws = _cabi.reduce_workspace(device)
+    recs = [_cabi.new_record(device) for _ in sets]
+    grads = [torch.empty_like(x) for x, _ in sets]
+    one = torch.ones(1, dtype=torch.float32, device=device)
+    xs = [x.detach() for x, _ in sets]
+    ys = [y for _, y in sets]
+    n, c = wl.shape[0], wl.shape[1]
+    m = wl.elems // (n * c)
+    dt = _cabi.dtype_code(xs[0])
+    denoms = [_cabi._vp(r.data_ptr() + 8) for r in recs]
+    if wl.name == "focal":
+        e = wl.elems
+        fwd = lambda i: _cabi.check(lib.b200_focal_forward(P(xs[i]), P(ys[i]), None, P(recs[i]), P(ws), ws.numel(),
+                                                           e, dt, 2.0, 0.25, st))
+        bwd = lambda i: _cabi.check(lib.b200_focal_backward(P(xs[i]), P(ys[i]), P(one), 1, denoms[i], P(grads[i]),
+                                                            e, dt, 2.0, 0.25, st))
+        return fwd, bwd
+    if wl.name == "lovasz":
+        nbytes = int(lib.b200_lovasz_workspace_bytes(n, c, m, 1))
+        lws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        loss = torch.empty(n, c, dtype=torch.float32, device=device)
+        jacc = torch.empty(n, c, m, dtype=torch.float32, device=device)
+        up = torch.full((n, c), 1.0 / (n * c), dtype=torch.float32, device=device)
+        fwd = lambda i: _cabi.check(lib.b200_lovasz_forward(P(xs[i]), P(ys[i]), P(loss), P(jacc), P(lws), nbytes,
+                                                            n, c, m, dt, 255, 1, st))
+        bwd = lambda i: _cabi.check(lib.b200_lovasz_backward(P(up), P(xs[i]), P(ys[i]), P(jacc), P(grads[i]),
+                                                             n, c, m, dt, 255, 1, st))
+        return fwd, bwd
+    stem, hyper, ign = {"lsr": ("lsr", 0.1, 255), "lsr_rows": ("lsr", 0.1, -100), "lmargin": ("lmargin", 0.3, 255)}[wl.name]
+    f_fwd, f_bwd = getattr(lib, "b200_%s_forward" % stem), getattr(lib, "b200_%s_backward" % stem)
+    fwd = lambda i: _cabi.check(f_fwd(P(xs[i]), P(ys[i]), None, P(recs[i]), P(ws), ws.numel(), n, c, m, dt, ign, hyper, st))
+    bwd = lambda i: _cabi.check(f_bwd(P(xs[i]), P(ys[i]), P(one), 1, denoms[i], P(grads[i]), n, c, m, dt, ign, hyper, st))
+    return fwd, bwd
+
+
 def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
     import pytorch_loss as P
     from pytorch_loss import _cabi
@@ -260,22 +302,26 @@ def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
     ms_step = ms_total / args.steps
     value = world * wl.elems / (ms_step / 1e3)
 
-    # ---- per-entry-point durations (eager pass over the same steps)
-    for k in range(args.warmup):
-        step_eager(crit, *sets[k % N_SETS])
-    torch.cuda.synchronize()
-    with _cabi.CallTimer() as timer:
-        for k in range(args.steps):
-            step_eager(crit, *sets[k % N_SETS])
-    calls = timer.summary()
+    # ---- per-entry-point durations: K back-to-back launches of the entry point through the
+    # C ABI (rotating input sets, preallocated outputs) between one pair of CUDA events, so
+    # the queue stays full and the figure is the kernels' own time, not the host's.
     fwd_name, bwd_name = wl.entries()
+    fwd_call, bwd_call = direct_calls(wl, sets, device)
     kernels = {}
-    for name, nbytes in ((fwd_name, wl.bytes_forward()), (bwd_name, wl.bytes_backward())):
-        n, ms = calls.get(name, (0, 0.0))
-        if n:
-            gbs = nbytes / (ms / n / 1e3) / 1e9
-            kernels[name] = {"calls": n, "avg_ms": ms / n, "algorithmic_bytes": nbytes,
-                             "achieved_gbs": gbs, "frac": gbs / peak}
+    for name, call, nbytes in ((fwd_name, fwd_call, wl.bytes_forward()), (bwd_name, bwd_call, wl.bytes_backward())):
+        for k in range(args.warmup):
+            call(k % N_SETS)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for k in range(args.steps):
+            call(k % N_SETS)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        gbs = nbytes / (ms / 1e3) / 1e9
+        kernels[name] = {"calls": args.steps, "avg_ms": ms, "algorithmic_bytes": nbytes,
+                         "achieved_gbs": gbs, "frac": gbs / peak}
     dominant = max(kernels, key=lambda k: kernels[k]["avg_ms"]) if kernels else None
     roofline = None
     if dominant:

@@ -23,7 +23,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo",
+    "-O3", "-std=c++17", "-lineinfo", "-ftz=true",
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr", "--extended-lambda",
 ]

@@ -39,12 +39,12 @@ struct ReduceRecord {       // the 32-byte "out" record of the C ABI
 
 // --------------------------------------------------------------- dtype access
 
-template <typename T> struct Vec16;   // 16-byte vector of T
-template <> struct Vec16<float> {
+template <typename T> struct Vec16;   // 16-byte vector of T; alignas makes a copy ONE 128-bit access
+template <> struct alignas(16) Vec16<float> {
     static constexpr int N = 4;
     float v[4];
 };
-template <> struct Vec16<__half> {
+template <> struct alignas(16) Vec16<__half> {
     static constexpr int N = 8;
     __half v[8];
 };
@@ -199,6 +199,29 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
         if (mbar_try_wait(bar, parity)) break;
     }
     return false;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Named barrier 1 over the first `n` threads of a block (the compute warps of a
+// warp-specialised kernel; the copy warps never join it).  n must be a multiple of 32.
+__device__ __forceinline__ void compute_sync(int n) {
+    asm volatile("bar.sync 1, %0;" ::"r"(n) : "memory");
+}
+// Same barrier with an AND reduction of a per-thread predicate (uniform result).
+__device__ __forceinline__ bool compute_all(bool ok, int n) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(uint32_t(ok)), "r"(n)
+        : "memory");
+    return r != 0;
 }
 
 // 2-D / 3-D tiled loads global -> shared, completion on an mbarrier (no multicast).

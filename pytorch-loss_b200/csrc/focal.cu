@@ -15,6 +15,7 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 
 namespace b200 {
 namespace {
@@ -62,7 +63,7 @@ __device__ __forceinline__ void focal_core(float x, float y, float gamma, float 
     }
 }
 
-template <typename T, int MODE, bool GAMMA2, bool REDUCE>
+template <typename T, int MODE, bool GAMMA2, bool REDUCE, int UNROLL = 2>
 __global__ void __launch_bounds__(kThreads) focal_kernel(const FocalParams prm) {
     using V = Vec16<T>;
     constexpr int VN = V::N;
@@ -107,16 +108,18 @@ __global__ void __launch_bounds__(kThreads) focal_kernel(const FocalParams prm) 
         if (REDUCE) acc += double(part);
     };
 
-    // two vectors per array in flight per thread
-    for (; i + stride < nvec; i += 2 * stride) {
-        const V x0 = ld_stream16<V>(logits + i * VN);
-        const V y0 = ld_stream16<V>(labels + i * VN);
-        const V x1 = ld_stream16<V>(logits + (i + stride) * VN);
-        const V y1 = ld_stream16<V>(labels + (i + stride) * VN);
-        do_vec(i, x0, y0);
-        do_vec(i + stride, x1, y1);
+    // UNROLL vectors per array in flight per thread
+    for (; i + (UNROLL - 1) * stride < nvec; i += UNROLL * stride) {
+        V xs[UNROLL], ys[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            xs[u] = ld_stream16<V>(logits + (i + u * stride) * VN);
+            ys[u] = ld_stream16<V>(labels + (i + u * stride) * VN);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) do_vec(i + u * stride, xs[u], ys[u]);
     }
-    if (i < nvec) {
+    for (; i < nvec; i += stride) {
         const V x0 = ld_stream16<V>(logits + i * VN);
         const V y0 = ld_stream16<V>(labels + i * VN);
         do_vec(i, x0, y0);
@@ -137,6 +140,132 @@ __global__ void __launch_bounds__(kThreads) focal_kernel(const FocalParams prm) 
     if (REDUCE) {
         __shared__ double sh[64];
         const double cnt = (blockIdx.x == 0 && threadIdx.x == 0) ? double(prm.E) : 0.0;
+        grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh);
+    }
+}
+
+// Bulk-copy ring variant.  Plain 128-bit loads top out near 4 TB/s of reads on B200 (the SM's
+// outstanding-load capacity divided by the loaded latency), whatever the unrolling or the
+// number of blocks; bulk-async copies do not go through that path.  One thread of an extra
+// warp streams chunks of logits and labels into a ring of shared-memory stages, the compute
+// warps read them back with 16-byte shared loads, gradients/losses leave with plain 128-bit
+// stores (stores are not the limiter).  Hand-offs: full[s] (copy bytes landed), empty[s]
+// (one arrival per compute warp).  Every wait is bounded.
+constexpr int kRingStages = 4;
+constexpr int kRingChunkBytes = 8192;             // per array and stage
+constexpr int kRingBlock = kThreads + 32;
+
+template <typename T, int MODE, bool GAMMA2, bool REDUCE>
+__global__ void __launch_bounds__(kRingBlock) focal_ring_kernel(const FocalParams prm) {
+    using V = Vec16<T>;
+    constexpr int VN = V::N;
+    constexpr int kChunkElems = kRingChunkBytes / int(sizeof(T));
+    constexpr int kVecPerThread = kChunkElems / VN / kThreads;
+    static_assert(kVecPerThread >= 1, "chunk too small for the block");
+    extern __shared__ unsigned char ring_raw[];
+    unsigned char(*stage_mem)[2][kRingChunkBytes] = reinterpret_cast<unsigned char(*)[2][kRingChunkBytes]>(
+        ring_raw + ((128u - (smem_u32(ring_raw) & 127u)) & 127u));
+    __shared__ __align__(8) uint64_t full[kRingStages], empty[kRingStages];
+    __shared__ double sh[64];
+
+    const T *__restrict__ logits = static_cast<const T *>(prm.logits);
+    const T *__restrict__ labels = static_cast<const T *>(prm.labels);
+    T *__restrict__ losses = static_cast<T *>(prm.losses);
+    T *__restrict__ grads = static_cast<T *>(prm.grads);
+    const T *__restrict__ gout = static_cast<const T *>(prm.grad_out);
+    const float gamma = prm.gamma, alpha = prm.alpha;
+    constexpr bool kGrad = MODE != kFwd;
+    constexpr bool kLoss = MODE != kBwd;
+    const int tid = threadIdx.x;
+    unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
+
+    if (tid == 0) {
+        for (int s = 0; s < kRingStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kThreads / 32);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    const int64_t nvec = prm.E / VN;                        // whole vectors
+    const int64_t nchunks = (nvec * VN + kChunkElems - 1) / kChunkElems;
+    double acc = 0.0;
+
+    if (tid == kThreads) {
+        int k = 0;
+        for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x, ++k) {
+            const int s = k % kRingStages;
+            if (k >= kRingStages && !mbar_wait_bounded(&empty[s], ((k / kRingStages) - 1) & 1, status)) break;
+            const int64_t e0 = c * kChunkElems;
+            int64_t ne = nvec * VN - e0;
+            if (ne > kChunkElems) ne = kChunkElems;
+            const uint32_t bytes = uint32_t(ne) * sizeof(T);   // multiple of 16
+            mbar_expect_tx(&full[s], 2 * bytes);
+            bulk_load_1d(stage_mem[s][0], logits + e0, bytes, &full[s]);
+            bulk_load_1d(stage_mem[s][1], labels + e0, bytes, &full[s]);
+        }
+    } else if (tid < kThreads) {
+        float gscale = 1.f;
+        if (MODE == kBwd && prm.grad_mode == 1) gscale = *static_cast<const float *>(prm.grad_out);
+        if (MODE == kBwd && prm.denom) gscale = static_cast<float>(double(gscale) / *prm.denom);
+        const bool per_elem = (MODE == kBwd) && prm.grad_mode == 2;
+        const int lane = tid & 31;
+        int k = 0;
+        for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x, ++k) {
+            const int s = k % kRingStages;
+            const int64_t v0 = c * (kChunkElems / VN);          // first vector of the chunk
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(&full[s], (k / kRingStages) & 1, status);
+            if (!compute_all(ok, kThreads)) break;
+            const V *sx = reinterpret_cast<const V *>(stage_mem[s][0]);
+            const V *sy = reinterpret_cast<const V *>(stage_mem[s][1]);
+            float part = 0.f;
+#pragma unroll
+            for (int u = 0; u < kVecPerThread; ++u) {
+                const int lv = u * kThreads + tid;
+                const int64_t vi = v0 + lv;
+                if (vi < nvec) {
+                    const V xv = sx[lv], yv = sy[lv];
+                    V lvv, gv, sv;
+                    if (per_elem) sv = ld_stream16<V>(gout + vi * VN);
+#pragma unroll
+                    for (int q = 0; q < VN; ++q) {
+                        float loss, grad = 0.f;
+                        focal_core<GAMMA2>(to_f32(xv.v[q]), to_f32(yv.v[q]), gamma, alpha, loss, grad, kGrad);
+                        if (kLoss) {
+                            part += loss;
+                            lvv.v[q] = from_f32<T>(loss);
+                        }
+                        if (kGrad) {
+                            const float sc = per_elem ? gscale * to_f32(sv.v[q]) : gscale;
+                            gv.v[q] = from_f32<T>(MODE == kBwd ? grad * sc : grad);
+                        }
+                    }
+                    if (kLoss && losses) st_stream16(losses + vi * VN, lvv);
+                    if (kGrad) st_stream16(grads + vi * VN, gv);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (REDUCE) acc += double(part);
+        }
+        // scalar tail (E not a multiple of the vector width)
+        if (blockIdx.x == 0) {
+            for (int64_t j = nvec * VN + tid; j < prm.E; j += kThreads) {
+                float loss, grad = 0.f;
+                focal_core<GAMMA2>(to_f32(logits[j]), to_f32(labels[j]), gamma, alpha, loss, grad, kGrad);
+                if (kLoss && losses) losses[j] = from_f32<T>(loss);
+                if (kGrad) {
+                    const float sc = per_elem ? gscale * to_f32(gout[j]) : gscale;
+                    grads[j] = from_f32<T>(MODE == kBwd ? grad * sc : grad);
+                }
+                if (REDUCE) acc += double(loss);
+            }
+        }
+    }
+    if (REDUCE) {
+        const double cnt = (blockIdx.x == 0 && tid == 0) ? double(prm.E) : 0.0;
         grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh);
     }
 }
@@ -180,15 +309,38 @@ template <typename T, int MODE, bool REDUCE>
 int launch_focal(const FocalParams &prm, cudaStream_t stream) {
     const int vn = Vec16<T>::N;
     int64_t want = (prm.E / vn + kThreads - 1) / kThreads;
-    const int64_t cap = int64_t(sm_count()) * kBlocksPerSM;
+    const char *eb = getenv("B200_FOCAL_BLOCKS"), *eu = getenv("B200_FOCAL_UNROLL");
+    const int bps = eb && atoi(eb) > 0 ? atoi(eb) : kBlocksPerSM;
+    const int64_t cap = int64_t(sm_count()) * bps;
     if (want > cap) want = cap;
     if (want < 1) want = 1;
     const dim3 grid(static_cast<unsigned>(want));
     const bool al = aligned16(prm.logits) && aligned16(prm.labels) &&
                     (!prm.losses || aligned16(prm.losses)) && (!prm.grads || aligned16(prm.grads)) &&
                     (prm.grad_mode != 2 || aligned16(prm.grad_out));
+    // the ring wins for the read-only forward (8% at the 16.7 M-element size); with a gradient
+    // stream to write, plain loads + stores are as fast and simpler
+    if (al && MODE == kFwd && !getenv("B200_FOCAL_NO_RING")) {
+        constexpr size_t smem = 128 + size_t(kRingStages) * 2 * kRingChunkBytes;
+        const int per_sm = eb && atoi(eb) > 0 ? atoi(eb) : int((220 * 1024) / (smem + 1024));
+        const int64_t chunk_elems = kRingChunkBytes / sizeof(T);
+        int64_t g = (prm.E + chunk_elems - 1) / chunk_elems;
+        if (g > int64_t(sm_count()) * per_sm) g = int64_t(sm_count()) * per_sm;
+        if (g < 1) g = 1;
+        auto go = [&](auto kern) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+            kern<<<dim3(unsigned(g)), kRingBlock, smem, stream>>>(prm);
+        };
+        if (prm.gamma == 2.f) go(focal_ring_kernel<T, MODE, true, REDUCE>);
+        else go(focal_ring_kernel<T, MODE, false, REDUCE>);
+        return launch_status("focal ring kernel launch");
+    }
     if (!al) {
         focal_kernel_unaligned<T, MODE, REDUCE><<<grid, kThreads, 0, stream>>>(prm);
+    } else if (prm.gamma == 2.f && eu && atoi(eu) == 4) {
+        focal_kernel<T, MODE, true, REDUCE, 4><<<grid, kThreads, 0, stream>>>(prm);
+    } else if (prm.gamma == 2.f && eu && atoi(eu) == 1) {
+        focal_kernel<T, MODE, true, REDUCE, 1><<<grid, kThreads, 0, stream>>>(prm);
     } else if (prm.gamma == 2.f) {
         focal_kernel<T, MODE, true, REDUCE><<<grid, kThreads, 0, stream>>>(prm);
     } else {

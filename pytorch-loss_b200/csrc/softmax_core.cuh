@@ -117,7 +117,9 @@ template <> struct Stat2<kLMargin> {
     }
 };
 
-// Finalised per-pixel quantities: loss value and what phase 3 needs.
+// Finalised per-pixel quantities: loss value and what phase 3 needs.  Sums lie in [1, C], where
+// lg2.approx / rcp.approx are accurate to ~1e-7 relative; the per-pixel epilogue then costs a
+// dozen instructions instead of the ~60 of the IEEE-rounded logf / division sequences.
 template <int KIND> struct PixelFinal;
 
 template <> struct PixelFinal<kLSR> {
@@ -125,11 +127,15 @@ template <> struct PixelFinal<kLSR> {
     __device__ __forceinline__ void finish(const Stat1<kLSR> &a, const Stat2<kLSR> &b,
                                            const LossConsts &k) {
         m = a.m;
-        inv_s = 1.f / b.s;
-        loss = k.sumy * (a.m + logf(b.s)) - k.lb_neg * b.sx - (k.lb_pos - k.lb_neg) * b.xl;
+        inv_s = __fdividef(1.f, b.s);
+        loss = k.sumy * (a.m + __logf(b.s)) - k.lb_neg * b.sx - (k.lb_pos - k.lb_neg) * b.xl;
     }
     __device__ __forceinline__ float grad(float x, bool is_lb, const LossConsts &k) const {
         return k.sumy * exp_fast(x - m) * inv_s - (is_lb ? k.lb_pos : k.lb_neg);
+    }
+    // Gradient from e = e^{x-m} kept from phase 2 (saves the second exponential).
+    __device__ __forceinline__ float grad_from_exp(float e, bool is_lb, const LossConsts &k) const {
+        return k.sumy * e * inv_s - (is_lb ? k.lb_pos : k.lb_neg);
     }
 };
 
@@ -138,16 +144,16 @@ template <> struct PixelFinal<kLMargin> {
     __device__ __forceinline__ void finish(const Stat1<kLMargin> &a, const Stat2<kLMargin> &b,
                                            const LossConsts &k) {
         m_no = a.m_no;
-        inv_s_no = 1.f / b.s_no;
+        inv_s_no = __fdividef(1.f, b.s_no);
         sqx = b.sde * inv_s_no;
         // softmax over all channels from the off-target sum and the target logit
         const float m = fmaxf(a.m_no, a.xl);
-        const float e_no = b.s_no * expf(a.m_no - m);
-        const float e_lb = expf(a.xl - m);
+        const float e_no = b.s_no * __expf(a.m_no - m);
+        const float e_lb = __expf(a.xl - m);
         const float s_all = e_no + e_lb;
-        r = e_no / s_all;
+        r = __fdividef(e_no, s_all);
         g_lb = -r;                                 // p_lb - 1 = -(1 - p_lb)
-        loss = (m + logf(s_all)) - a.xl + k.half_lam * (sqx - k.a * b.sd);
+        loss = (m + __logf(s_all)) - a.xl + k.half_lam * (sqx - k.a * b.sd);
     }
     __device__ __forceinline__ float grad(float x, bool is_lb, const LossConsts &k) const {
         if (is_lb) return g_lb;
@@ -156,6 +162,22 @@ template <> struct PixelFinal<kLMargin> {
         return r * q + k.half_lam * (q * (d + 1.f - sqx) - k.a);
     }
 };
+
+// Helpers of the kernels that keep e^{x-m} in shared memory between phases 2 and 3 (LSR only;
+// the large-margin gradient needs x itself again).
+__device__ __forceinline__ float s1_max(const Stat1<kLSR> &a) { return a.m; }
+__device__ __forceinline__ void s2_add_with_exp(Stat2<kLSR> &b, float x, float e, bool is_lb) {
+    b.s += e;
+    b.sx += x;
+    if (is_lb) b.xl = x;
+}
+// Phase-3 gradient from what the tile holds: e^{x-m} for LSR, x for large margin.
+template <int KIND>
+__device__ __forceinline__ float grad_phase3(const PixelFinal<KIND> &fin, float v, bool is_lb,
+                                             const LossConsts &k) {
+    if constexpr (KIND == kLSR) return fin.grad_from_exp(v, is_lb, k);
+    else return fin.grad(v, is_lb, k);
+}
 
 // Upstream-gradient scale shared by all backward kernels: grad_mode 1 reads one device
 // float, denom (optional) is a device double; mode 2 multiplies per pixel later.
