@@ -44,6 +44,7 @@ struct SoftmaxParams {
     LossConsts k;
     // tile geometry
     int TP, KS, CB, nbox, rows;
+    int nbx;                 // boxes of TP pixels per tile (pair kernel)
     int stages;              // ring depth of the pipelined kernels
     int64_t tiles_per_image, total_tiles;
 };
@@ -407,108 +408,6 @@ __global__ void __launch_bounds__(kThreads) sweep_kernel(const SoftmaxParams prm
     if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
 }
 
-// ------------------------------------------------------------ registers regime
-// M > 1 and few channels (C <= 32): a thread owns V adjacent pixels (one 16-byte word per
-// channel) and holds all C words in registers.  Every global access is a coalesced 128-bit
-// load or store, the logits are read exactly once, there is no shared memory and no barrier;
-// memory-level parallelism comes from the C independent loads each thread has in flight.
-
-template <typename T, int KIND, int CMAX, bool BWD, bool REDUCE>
-__global__ void __launch_bounds__(kThreads)
-regs_kernel(const SoftmaxParams prm) {
-    constexpr int V = 16 / int(sizeof(T));
-    using VT = Vec16<T>;
-    __shared__ double sh_red[64];
-    const int C = static_cast<int>(prm.C);
-    const int64_t gpi = prm.M / V;                       // pixel groups per image
-    const int64_t groups = prm.N * gpi;
-    const T *logits = static_cast<const T *>(prm.logits);
-    T *grads = static_cast<T *>(prm.grads);
-    T *losses = static_cast<T *>(prm.losses);
-    const T *gout = static_cast<const T *>(prm.grad_out);
-    float gscale = 1.f;
-    if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
-    double acc_loss = 0.0, acc_cnt = 0.0;
-
-    for (int64_t g = int64_t(blockIdx.x) * kThreads + threadIdx.x; g < groups;
-         g += int64_t(gridDim.x) * kThreads) {
-        const int64_t n = g / gpi, m0 = (g % gpi) * V;
-        const T *src = logits + n * prm.C * prm.M + m0;
-        VT x[CMAX];
-#pragma unroll
-        for (int j = 0; j < CMAX; ++j)
-            if (j < C) x[j] = ld_stream16<VT>(src + int64_t(j) * prm.M);
-        int lbi[V];
-        float psc[V];
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const int64_t lb = __ldg(prm.labels + n * prm.M + m0 + i);
-            const bool valid = lb != prm.ignore;
-            lbi[i] = valid ? ((lb >= 0 && lb < (int64_t(1) << 31)) ? int(lb) : -2) : -1;
-            psc[i] = gscale;
-            if (BWD && prm.grad_mode == 2) psc[i] *= to_f32(gout[n * prm.M + m0 + i]);
-        }
-        Stat1<KIND> s1[V];
-        Stat2<KIND> s2[V];
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-            s1[i].init();
-            s2[i].init();
-        }
-#pragma unroll
-        for (int j = 0; j < CMAX; ++j)
-            if (j < C) {
-#pragma unroll
-                for (int i = 0; i < V; ++i) s1[i].add(to_f32(x[j].v[i]), j == lbi[i]);
-            }
-#pragma unroll
-        for (int j = 0; j < CMAX; ++j)
-            if (j < C) {
-#pragma unroll
-                for (int i = 0; i < V; ++i) {
-                    if constexpr (BWD && KIND == kLSR) {
-                        const float xv = to_f32(x[j].v[i]);
-                        const float e = exp_fast(xv - s1_max(s1[i]));
-                        s2_add_with_exp(s2[i], xv, e, j == lbi[i]);
-                        x[j].v[i] = from_f32<T>(e);
-                    } else {
-                        s2[i].add(to_f32(x[j].v[i]), j == lbi[i], s1[i]);
-                    }
-                }
-            }
-        PixelFinal<KIND> fin[V];
-#pragma unroll
-        for (int i = 0; i < V; ++i) fin[i].finish(s1[i], s2[i], prm.k);
-        if (!BWD) {
-#pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const float l = lbi[i] != -1 ? fin[i].loss : 0.f;
-                if (losses) losses[n * prm.M + m0 + i] = from_f32<T>(l);
-                if (REDUCE && lbi[i] != -1) {
-                    acc_loss += double(l);
-                    acc_cnt += 1.0;
-                }
-            }
-        } else {
-            T *dst = grads + n * prm.C * prm.M + m0;
-#pragma unroll
-            for (int j = 0; j < CMAX; ++j)
-                if (j < C) {
-                    VT gv;
-#pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        float gr = 0.f;
-                        if (lbi[i] != -1)
-                            gr = grad_phase3<KIND>(fin[i], to_f32(x[j].v[i]), j == lbi[i], prm.k) * psc[i];
-                        gv.v[i] = from_f32<T>(gr);
-                    }
-                    st_stream16(dst + int64_t(j) * prm.M, gv);
-                }
-        }
-    }
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
-}
-
 // ------------------------------------------------- warp-specialised copy pipelines
 //
 // The aligned (TMA) forms of the tile and rows regimes.  A block is kCompute compute threads
@@ -544,335 +443,8 @@ __device__ __forceinline__ void pipe_init(PipeBarriers &bars, int stages) {
     __syncthreads();
 }
 
-// Exchange of per-pixel statistics between the channel slices of a tile through shared
-// memory: every thread writes its V pixels' words (16-byte stores), the compute warps meet at
-// the named barrier, then every thread merges all slices of its pixels.
-//   red layout: [word][slice][TP] floats, `plane` = slices * TP floats per word.
-template <typename S, int V>
-__device__ __forceinline__ void stat_exchange(S (&st)[V], float *red, int plane, int my_off, int TP,
-                                              int pix_off, int slices) {
-    static_assert(V % 4 == 0, "pixels per thread come in groups of four");
-#pragma unroll
-    for (int w = 0; w < S::kWords; ++w) {
-#pragma unroll
-        for (int c = 0; c < V / 4; ++c) {
-            float4 f;
-            f.x = reinterpret_cast<const float *>(&st[4 * c + 0])[w];
-            f.y = reinterpret_cast<const float *>(&st[4 * c + 1])[w];
-            f.z = reinterpret_cast<const float *>(&st[4 * c + 2])[w];
-            f.w = reinterpret_cast<const float *>(&st[4 * c + 3])[w];
-            *reinterpret_cast<float4 *>(red + w * plane + my_off + 4 * c) = f;
-        }
-    }
-    compute_sync(256);
-#pragma unroll
-    for (int i = 0; i < V; ++i) st[i].init();
-    for (int q = 0; q < slices; ++q) {
-        S other[V];
-#pragma unroll
-        for (int w = 0; w < S::kWords; ++w) {
-#pragma unroll
-            for (int c = 0; c < V / 4; ++c) {
-                const float4 f = *reinterpret_cast<const float4 *>(red + w * plane + q * TP + pix_off + 4 * c);
-                reinterpret_cast<float *>(&other[4 * c + 0])[w] = f.x;
-                reinterpret_cast<float *>(&other[4 * c + 1])[w] = f.y;
-                reinterpret_cast<float *>(&other[4 * c + 2])[w] = f.z;
-                reinterpret_cast<float *>(&other[4 * c + 3])[w] = f.w;
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < V; ++i) st[i].merge(other[i]);
-    }
-}
-
 constexpr int kTileCompute = 256;
 constexpr int kTileBlock = kTileCompute + 64;
-
-template <typename T, int KIND, bool BWD, bool REDUCE, int VPT>
-__global__ void __launch_bounds__(kTileBlock)
-tile_pipe_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap map_in,
-                 const __grid_constant__ CUtensorMap map_out) {
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ PipeBarriers bars;
-    __shared__ double sh_red[64];
-
-    const int TP = prm.TP, KS = prm.KS, C = static_cast<int>(prm.C), NS = prm.stages;
-    unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
-    const size_t stage_bytes = (size_t(prm.rows) * TP * sizeof(T) + 127) & ~size_t(127);
-    float *red = reinterpret_cast<float *>(base + NS * stage_bytes);   // [5 words][slices][TP]
-    const int tid = threadIdx.x;
-    unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
-    const uint32_t tile_bytes = uint32_t(prm.nbox) * prm.CB * TP * sizeof(T);
-
-    pipe_init<kTileCompute, BWD>(bars, NS);
-
-    const int64_t first = blockIdx.x, stride = gridDim.x;
-    double acc_loss = 0.0, acc_cnt = 0.0;
-    float acc_loss32 = 0.f;
-    int acc_cnt32 = 0;
-
-    if (tid == kTileCompute) {
-        // ---- loader
-        int k = 0;
-        for (int64_t t = first; t < prm.total_tiles; t += stride, ++k) {
-            const int s = k % NS;
-            if (k >= NS && !mbar_wait_bounded(&bars.empty[s], ((k / NS) - 1) & 1, status)) break;
-            const int64_t n = t / prm.tiles_per_image;
-            const int64_t p0 = (t % prm.tiles_per_image) * TP;
-            T *stage = reinterpret_cast<T *>(base + s * stage_bytes);
-            mbar_expect_tx(&bars.full[s], tile_bytes);
-            for (int b = 0; b < prm.nbox; ++b)
-                tma_load_3d(stage + size_t(b) * prm.CB * TP, &map_in, int(p0), b * prm.CB, int(n), &bars.full[s]);
-        }
-    } else if (BWD && tid == kTileCompute + 32) {
-        // ---- storer
-        int k = 0;
-        for (int64_t t = first; t < prm.total_tiles; t += stride, ++k) {
-            const int s = k % NS;
-            if (!mbar_wait_bounded(&bars.ready[s], (k / NS) & 1, status)) break;
-            const int64_t n = t / prm.tiles_per_image;
-            const int64_t p0 = (t % prm.tiles_per_image) * TP;
-            const T *stage = reinterpret_cast<const T *>(base + s * stage_bytes);
-            for (int b = 0; b < prm.nbox; ++b)
-                tma_store_3d(&map_out, int(p0), b * prm.CB, int(n), stage + size_t(b) * prm.CB * TP);
-            bulk_commit();
-            bulk_wait_read_all();
-            mbar_arrive(&bars.empty[s]);
-        }
-        bulk_wait_all();
-    } else if (tid < kTileCompute) {
-        if constexpr (VPT == 1) {
-        // ---- compute, one pixel per thread: lanes run along pixels (conflict-free 4-byte
-        // shared-memory accesses), KS = kTileCompute / TP threads share a pixel's channels.
-        const int p = tid % TP, ks = tid / TP, lane = tid & 31;
-        const int KS = kTileCompute / TP;
-        constexpr int slab = kTileCompute;
-        const T *gout = static_cast<const T *>(prm.grad_out);
-        T *losses = static_cast<T *>(prm.losses);
-        float gscale = 1.f;
-        if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
-        int k = 0;
-        for (int64_t t = first; t < prm.total_tiles; t += stride, ++k) {
-            const int s = k % NS;
-            const int64_t n = t / prm.tiles_per_image;
-            const int64_t pix = (t % prm.tiles_per_image) * TP + p;
-            const bool inb = pix < prm.M;
-            const int64_t lb = inb ? __ldg(prm.labels + n * prm.M + pix) : prm.ignore;
-            const bool valid = inb && lb != prm.ignore;
-            const int lbi = valid ? ((lb >= 0 && lb < (int64_t(1) << 31)) ? int(lb) : -2) : -1;
-            float pscale = gscale;
-            if (BWD && prm.grad_mode == 2 && inb) pscale *= to_f32(gout[n * prm.M + pix]);
-
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
-            if (!compute_all(ok, kTileCompute)) break;
-
-            T *col = reinterpret_cast<T *>(base + s * stage_bytes) + p;
-            const int step = KS * TP;
-            Stat1<KIND> s1;
-            s1.init();
-            {
-                const T *q = col + ks * TP;
-#pragma unroll 4
-                for (int j = ks; j < C; j += KS, q += step) s1.add(to_f32(*q), j == lbi);
-            }
-            if (KS > 1) {
-                s1.store(red + tid, slab);
-                compute_sync(kTileCompute);
-                s1.init();
-                for (int q = 0; q < KS; ++q) {
-                    Stat1<KIND> o;
-                    o.load(red + q * TP + p, slab);
-                    s1.merge(o);
-                }
-            }
-            Stat2<KIND> s2;
-            s2.init();
-            {
-                T *q = col + ks * TP;
-                if constexpr (BWD && KIND == kLSR) {
-#pragma unroll 4
-                    for (int j = ks; j < C; j += KS, q += step) {
-                        const float x = to_f32(*q);
-                        const float e = exp_fast(x - s1_max(s1));
-                        s2_add_with_exp(s2, x, e, j == lbi);
-                        *q = from_f32<T>(e);
-                    }
-                } else {
-#pragma unroll 4
-                    for (int j = ks; j < C; j += KS, q += step) s2.add(to_f32(*q), j == lbi, s1);
-                }
-            }
-            if (KS > 1) {
-                float *r2 = red + 2 * slab;
-                s2.store(r2 + tid, slab);
-                compute_sync(kTileCompute);
-                s2.init();
-                for (int q = 0; q < KS; ++q) {
-                    Stat2<KIND> o;
-                    o.load(r2 + q * TP + p, slab);
-                    s2.merge(o);
-                }
-            }
-            PixelFinal<KIND> fin;
-            fin.finish(s1, s2, prm.k);
-
-            if (!BWD) {
-                if (ks == 0 && inb) {
-                    const float l = valid ? fin.loss : 0.f;
-                    if (losses) losses[n * prm.M + pix] = from_f32<T>(l);
-                    if (REDUCE && valid) {
-                        acc_loss32 += l;
-                        acc_cnt32 += 1;
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.empty[s]);
-            } else {
-                T *q = col + ks * TP;
-                if (valid) {
-#pragma unroll 4
-                    for (int j = ks; j < C; j += KS, q += step)
-                        *q = from_f32<T>(grad_phase3<KIND>(fin, to_f32(*q), j == lbi, prm.k) * pscale);
-                } else {
-                    for (int j = ks; j < C; j += KS, q += step) *q = from_f32<T>(0.f);
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.ready[s]);
-            }
-            // fold the fp32 running sums into the fp64 accumulators now and then
-            if (REDUCE && (k & 63) == 63) {
-                acc_loss += double(acc_loss32);
-                acc_cnt += double(acc_cnt32);
-                acc_loss32 = 0.f;
-                acc_cnt32 = 0;
-            }
-        }
-        acc_loss += double(acc_loss32);
-        acc_cnt += double(acc_cnt32);
-        } else {
-        // ---- compute: each thread owns V adjacent pixels (one 16-byte shared-memory word per
-        // channel) of channel slice ks; KS = kTileCompute / (TP / V) slices share a pixel.
-        constexpr int V = 16 / int(sizeof(T));
-        using VT = Vec16<T>;
-        const int TPV = TP / V;
-        const int pg = tid % TPV, ks = tid / TPV, lane = tid & 31;
-        const int KSV = kTileCompute / TPV;            // channel slices
-        const int plane = KSV * TP;                    // floats per statistic word in `red`
-        float *red1 = red;                             // [2][KSV][TP]
-        float *red2 = red + 2 * plane;                 // [3][KSV][TP]
-        const T *gout = static_cast<const T *>(prm.grad_out);
-        T *losses = static_cast<T *>(prm.losses);
-        float gscale = 1.f;
-        if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
-        int k = 0;
-        for (int64_t t = first; t < prm.total_tiles; t += stride, ++k) {
-            const int s = k % NS;
-            const int64_t n = t / prm.tiles_per_image;
-            const int64_t px0 = (t % prm.tiles_per_image) * TP + pg * V;
-            int lbi[V];                 // label as int, -1 where the pixel is ignored / out of range
-            unsigned inb_mask = 0;
-            float psc[V];
-#pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const int64_t pix = px0 + i;
-                const bool inb = pix < prm.M;
-                const int64_t lb = inb ? __ldg(prm.labels + n * prm.M + pix) : prm.ignore;
-                const bool valid = inb && lb != prm.ignore;
-                lbi[i] = valid ? ((lb >= 0 && lb < (int64_t(1) << 31)) ? int(lb) : -2) : -1;
-                inb_mask |= inb ? (1u << i) : 0u;
-                psc[i] = gscale;
-                if (BWD && prm.grad_mode == 2 && inb) psc[i] *= to_f32(gout[n * prm.M + pix]);
-            }
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
-            if (!compute_all(ok, kTileCompute)) break;
-
-            T *col = reinterpret_cast<T *>(base + s * stage_bytes) + pg * V;
-            // phase 1
-            Stat1<KIND> s1[V];
-#pragma unroll
-            for (int i = 0; i < V; ++i) s1[i].init();
-#pragma unroll 2
-            for (int j = ks; j < C; j += KSV) {
-                const VT xv = *reinterpret_cast<const VT *>(col + j * TP);
-#pragma unroll
-                for (int i = 0; i < V; ++i) s1[i].add(to_f32(xv.v[i]), j == lbi[i]);
-            }
-            if (KSV > 1) {
-                stat_exchange<Stat1<KIND>, V>(s1, red1, plane, ks * TP + pg * V, TP, pg * V, KSV);
-            }
-            // phase 2
-            Stat2<KIND> s2[V];
-#pragma unroll
-            for (int i = 0; i < V; ++i) s2[i].init();
-            if constexpr (BWD && KIND == kLSR) {
-                // keep e^{x-m} in the tile: phase 3 then needs no second exponential
-#pragma unroll 2
-                for (int j = ks; j < C; j += KSV) {
-                    VT xv = *reinterpret_cast<const VT *>(col + j * TP);
-#pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        const float x = to_f32(xv.v[i]);
-                        const float e = exp_fast(x - s1_max(s1[i]));
-                        s2_add_with_exp(s2[i], x, e, j == lbi[i]);
-                        xv.v[i] = from_f32<T>(e);
-                    }
-                    *reinterpret_cast<VT *>(col + j * TP) = xv;
-                }
-            } else {
-#pragma unroll 2
-                for (int j = ks; j < C; j += KSV) {
-                    const VT xv = *reinterpret_cast<const VT *>(col + j * TP);
-#pragma unroll
-                    for (int i = 0; i < V; ++i) s2[i].add(to_f32(xv.v[i]), j == lbi[i], s1[i]);
-                }
-            }
-            if (KSV > 1) {
-                stat_exchange<Stat2<KIND>, V>(s2, red2, plane, ks * TP + pg * V, TP, pg * V, KSV);
-            }
-            PixelFinal<KIND> fin[V];
-#pragma unroll
-            for (int i = 0; i < V; ++i) fin[i].finish(s1[i], s2[i], prm.k);
-
-            if (!BWD) {
-                if (ks == 0) {
-#pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        if (inb_mask & (1u << i)) {
-                            const float l = lbi[i] != -1 ? fin[i].loss : 0.f;
-                            if (losses) losses[n * prm.M + px0 + i] = from_f32<T>(l);
-                            if (REDUCE && lbi[i] != -1) {
-                                acc_loss += double(l);
-                                acc_cnt += 1.0;
-                            }
-                        }
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.empty[s]);
-            } else {
-#pragma unroll 2
-                for (int j = ks; j < C; j += KSV) {
-                    VT xv = *reinterpret_cast<const VT *>(col + j * TP);
-#pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        float g = 0.f;
-                        if (lbi[i] != -1) g = grad_phase3<KIND>(fin[i], to_f32(xv.v[i]), j == lbi[i], prm.k) * psc[i];
-                        xv.v[i] = from_f32<T>(g);
-                    }
-                    *reinterpret_cast<VT *>(col + j * TP) = xv;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.ready[s]);
-            }
-        }
-        }
-    }
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
-}
 
 // ---------------------------------------------------------- pair-per-thread tile kernel
 //
@@ -888,7 +460,7 @@ tile_pipe_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
 //     logit at -FLT_MAX for the max sweep and at min(x_lb, m') for the sum sweep, then takes its
 //     terms back out of the sums -- s' >= 1 >= e^{min(x_lb - m', 0)}, so nothing cancels);
 //   * exponentials are ex2.approx on a fused x*log2(e) - m*log2(e).
-// Copy pipeline and hand-offs are those of tile_pipe_kernel.
+// Copy pipeline and hand-offs as described above (loader, storer, full/ready/empty).
 
 __device__ __forceinline__ unsigned long long pk2(float2 v) {
     unsigned long long r;
@@ -959,14 +531,16 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
     __shared__ double sh_red[64];
 
     const int TP = prm.TP, C = static_cast<int>(prm.C), NS = prm.stages;
+    const int NBX = prm.nbx, TPT = TP * NBX;        // a tile is NBX boxes of TP pixels side by side
+    const int box_elems = prm.rows * TP;            // elements of one box in shared memory
     unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     // a stage = the logits tile followed by the tile's TP labels (both arrive by bulk copy)
-    const size_t label_off = (size_t(prm.rows) * TP * sizeof(T) + 127) & ~size_t(127);
-    const size_t stage_bytes = label_off + size_t(TP) * sizeof(int64_t);
+    const size_t label_off = (size_t(prm.rows) * TPT * sizeof(T) + 127) & ~size_t(127);
+    const size_t stage_bytes = label_off + size_t(TPT) * sizeof(int64_t);
     float *red = reinterpret_cast<float *>(base + NS * stage_bytes);   // [5 words][slices][TP]
     const int tid = threadIdx.x;
     unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
-    const uint32_t tile_bytes = uint32_t(prm.nbox) * prm.CB * TP * sizeof(T);
+    const uint32_t box_bytes = uint32_t(prm.nbox) * prm.CB * TP * sizeof(T);   // one column of boxes
 
     pipe_init<kTileCompute, BWD>(bars, NS);
     const int64_t first = blockIdx.x, stride = gridDim.x;
@@ -978,14 +552,17 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
             const int s = k % NS;
             if (k >= NS && !mbar_wait_bounded(&bars.empty[s], ((k / NS) - 1) & 1, status)) break;
             const int64_t n = t / prm.tiles_per_image;
-            const int64_t p0 = (t % prm.tiles_per_image) * TP;
+            const int64_t p0 = (t % prm.tiles_per_image) * TPT;
             T *stage = reinterpret_cast<T *>(base + s * stage_bytes);
             int64_t npix = prm.M - p0;
-            if (npix > TP) npix = TP;
+            if (npix > TPT) npix = TPT;
+            const int nbx = int((npix + TP - 1) / TP);                       // boxes that hold pixels
             const uint32_t label_bytes = uint32_t(npix) * sizeof(int64_t);   // M % 4 == 0: multiple of 16
-            mbar_expect_tx(&bars.full[s], tile_bytes + label_bytes);
-            for (int b = 0; b < prm.nbox; ++b)
-                tma_load_3d(stage + size_t(b) * prm.CB * TP, &map_in, int(p0), b * prm.CB, int(n), &bars.full[s]);
+            mbar_expect_tx(&bars.full[s], nbx * box_bytes + label_bytes);
+            for (int bx = 0; bx < nbx; ++bx)
+                for (int b = 0; b < prm.nbox; ++b)
+                    tma_load_3d(stage + size_t(bx) * box_elems + size_t(b) * prm.CB * TP, &map_in,
+                                int(p0) + bx * TP, b * prm.CB, int(n), &bars.full[s]);
             bulk_load_1d(base + s * stage_bytes + label_off, prm.labels + n * prm.M + p0, label_bytes, &bars.full[s]);
         }
     } else if (BWD && tid == kTileCompute + 32) {
@@ -994,21 +571,27 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
             const int s = k % NS;
             if (!mbar_wait_bounded(&bars.ready[s], (k / NS) & 1, status)) break;
             const int64_t n = t / prm.tiles_per_image;
-            const int64_t p0 = (t % prm.tiles_per_image) * TP;
+            const int64_t p0 = (t % prm.tiles_per_image) * TPT;
             const T *stage = reinterpret_cast<const T *>(base + s * stage_bytes);
-            for (int b = 0; b < prm.nbox; ++b)
-                tma_store_3d(&map_out, int(p0), b * prm.CB, int(n), stage + size_t(b) * prm.CB * TP);
+            int64_t npix = prm.M - p0;
+            if (npix > TPT) npix = TPT;
+            const int nbx = int((npix + TP - 1) / TP);
+            for (int bx = 0; bx < nbx; ++bx)
+                for (int b = 0; b < prm.nbox; ++b)
+                    tma_store_3d(&map_out, int(p0) + bx * TP, b * prm.CB, int(n),
+                                 stage + size_t(bx) * box_elems + size_t(b) * prm.CB * TP);
             bulk_commit();
             bulk_wait_read_all();
             mbar_arrive(&bars.empty[s]);
         }
         bulk_wait_all();
     } else if (tid < kTileCompute) {
-        const int TPV = TP >> 1;                      // pixel pairs per tile row
+        const int TPV = TPT >> 1;                     // pixel pairs per tile
         const int pg = tid % TPV, ks = tid / TPV, lane = tid & 31;
         const int KS = kTileCompute / TPV;
         const int pix = pg * 2;                       // first pixel of my pair inside the tile
-        const int plane = KS * TP;                    // floats per statistic word
+        const int plane = KS * TPT;                   // floats per statistic word
+        const int bxo = (pix / TP) * box_elems + (pix % TP);   // my pair's offset inside channel 0
         const int step = KS * TP;                     // tile elements between my channels
         const T *gout = static_cast<const T *>(prm.grad_out);
         T *losses = static_cast<T *>(prm.losses);
@@ -1021,7 +604,7 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
         for (int64_t t = first; t < prm.total_tiles; t += stride, ++k) {
             const int s = k % NS;
             const int64_t n = t / prm.tiles_per_image;
-            const int64_t px0 = (t % prm.tiles_per_image) * TP + pix;
+            const int64_t px0 = (t % prm.tiles_per_image) * TPT + pix;
             bool ok = true;
             if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
             if (!compute_all(ok, kTileCompute)) break;
@@ -1045,7 +628,7 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
             const bool own1 = lbi[1] >= 0 && lbi[1] % KS == ks;
 
             T *tile = reinterpret_cast<T *>(base + s * stage_bytes);
-            T *mine = tile + ks * TP + pix;           // my first channel, my pixel pair
+            T *mine = tile + bxo + ks * TP;           // my first channel, my pixel pair
 
             if constexpr (KIND == kLSR) {
                 // ---- phase 1: max
@@ -1055,12 +638,12 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
 #pragma unroll 4
                     for (int j = ks; j < C; j += KS, q += step) m = max2(m, ld_pair(q));
                 }
-                if (KS > 1) m = slice_combine<true>(m, red, ks, KS, TP, pix);
+                if (KS > 1) m = slice_combine<true>(m, red, ks, KS, TPT, pix);
                 // target logits (forward only; backward overwrites the tile with e^{x-m})
                 float2 xl = splat2(0.f);
                 if (!BWD && ks == 0) {
-                    if (lbi[0] >= 0) xl.x = to_f32(tile[lbi[0] * TP + pix]);
-                    if (lbi[1] >= 0) xl.y = to_f32(tile[lbi[1] * TP + pix + 1]);
+                    if (lbi[0] >= 0) xl.x = to_f32(tile[bxo + lbi[0] * TP]);
+                    if (lbi[1] >= 0) xl.y = to_f32(tile[bxo + lbi[1] * TP + 1]);
                 }
                 // ---- phase 2: sum of exponentials, sum of logits
                 const float2 nml = mul2(m, splat2(-kLog2e));
@@ -1077,8 +660,8 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     }
                 }
                 if (KS > 1) {
-                    sum = slice_combine<false>(sum, red + plane, ks, KS, TP, pix);
-                    if (!BWD) sx = slice_combine<false>(sx, red + 2 * plane, ks, KS, TP, pix);
+                    sum = slice_combine<false>(sum, red + plane, ks, KS, TPT, pix);
+                    if (!BWD) sx = slice_combine<false>(sx, red + 2 * plane, ks, KS, TPT, pix);
                 }
                 if (!BWD) {
                     if (ks == 0) {
@@ -1114,11 +697,11 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     }
                     const float dt = -(kc.lb_pos - kc.lb_neg);
                     if (own0) {
-                        T *e = tile + lbi[0] * TP + pix;
+                        T *e = tile + bxo + lbi[0] * TP;
                         *e = from_f32<T>(to_f32(*e) + dt * psc.x);
                     }
                     if (own1) {
-                        T *e = tile + lbi[1] * TP + pix + 1;
+                        T *e = tile + bxo + lbi[1] * TP + 1;
                         *e = from_f32<T>(to_f32(*e) + dt * psc.y);
                     }
                     fence_proxy_async_smem();
@@ -1130,12 +713,12 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                 // park the target logit out of the way of the max sweep
                 float2 xl = splat2(0.f);
                 if (own0) {
-                    T *e = tile + lbi[0] * TP + pix;
+                    T *e = tile + bxo + lbi[0] * TP;
                     xl.x = to_f32(*e);
                     *e = from_f32<T>(sizeof(T) == 2 ? -65504.f : kNegInf);
                 }
                 if (own1) {
-                    T *e = tile + lbi[1] * TP + pix + 1;
+                    T *e = tile + bxo + lbi[1] * TP + 1;
                     xl.y = to_f32(*e);
                     *e = from_f32<T>(sizeof(T) == 2 ? -65504.f : kNegInf);
                 }
@@ -1146,13 +729,13 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     for (int j = ks; j < C; j += KS, q += step) m = max2(m, ld_pair(q));
                 }
                 if (KS > 1) {
-                    m = slice_combine<true>(m, red, ks, KS, TP, pix);
-                    xl = slice_combine<false>(xl, red + plane, ks, KS, TP, pix);   // owner's value, others 0
+                    m = slice_combine<true>(m, red, ks, KS, TPT, pix);
+                    xl = slice_combine<false>(xl, red + plane, ks, KS, TPT, pix);   // owner's value, others 0
                 }
                 // the target re-enters the sum sweep clamped to the off-target maximum
                 const float2 cl = make_float2(fminf(xl.x, m.x), fminf(xl.y, m.y));
-                if (own0) tile[lbi[0] * TP + pix] = from_f32<T>(cl.x);
-                if (own1) tile[lbi[1] * TP + pix + 1] = from_f32<T>(cl.y);
+                if (own0) tile[bxo + lbi[0] * TP] = from_f32<T>(cl.x);
+                if (own1) tile[bxo + lbi[1] * TP + 1] = from_f32<T>(cl.y);
                 const float2 negm = make_float2(-m.x, -m.y);
                 float2 sum = splat2(0.f), sde = splat2(0.f), sx = splat2(0.f);
                 {
@@ -1168,9 +751,9 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     }
                 }
                 if (KS > 1) {
-                    sum = slice_combine<false>(sum, red + 2 * plane, ks, KS, TP, pix);
-                    sde = slice_combine<false>(sde, red + 3 * plane, ks, KS, TP, pix);
-                    sx = slice_combine<false>(sx, red + 4 * plane, ks, KS, TP, pix);
+                    sum = slice_combine<false>(sum, red + 2 * plane, ks, KS, TPT, pix);
+                    sde = slice_combine<false>(sde, red + 3 * plane, ks, KS, TPT, pix);
+                    sx = slice_combine<false>(sx, red + 4 * plane, ks, KS, TPT, pix);
                 }
                 // per pixel: take the clamped target back out, then the closed forms
                 float inv_s[2], rr[2], sqx[2], loss[2];
@@ -1232,8 +815,8 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                             st_pair(q, fma2(qq, fma2(qb, d, qa), cc));
                         }
                     }
-                    if (own0) tile[lbi[0] * TP + pix] = from_f32<T>(-rr[0] * psc.x);
-                    if (own1) tile[lbi[1] * TP + pix + 1] = from_f32<T>(-rr[1] * psc.y);
+                    if (own0) tile[bxo + lbi[0] * TP] = from_f32<T>(-rr[0] * psc.x);
+                    if (own1) tile[bxo + lbi[1] * TP + 1] = from_f32<T>(-rr[1] * psc.y);
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.ready[s]);
@@ -1252,29 +835,44 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
     if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
 }
 
-// Block-wide combine of per-thread statistics over the first n threads (named barrier).
-template <typename S>
-__device__ __forceinline__ void combine_over_compute(S &s, float *sh /* [32 * S::kWords] */, int n) {
+// Pair q of a 16-byte register vector as two floats, and back.
+__device__ __forceinline__ float2 pair_of(const Vec16<float> &v, int q) { return make_float2(v.v[2 * q], v.v[2 * q + 1]); }
+__device__ __forceinline__ float2 pair_of(const Vec16<__half> &v, int q) {
+    return __half22float2(__halves2half2(v.v[2 * q], v.v[2 * q + 1]));
+}
+__device__ __forceinline__ void set_pair(Vec16<float> &v, int q, float2 f) {
+    v.v[2 * q] = f.x;
+    v.v[2 * q + 1] = f.y;
+}
+__device__ __forceinline__ void set_pair(Vec16<__half> &v, int q, float2 f) {
+    const __half2 h = __float22half2_rn(f);
+    v.v[2 * q] = __low2half(h);
+    v.v[2 * q + 1] = __high2half(h);
+}
+
+// Reduce two values over the first n threads of the block (sum or max); every thread gets
+// the result.  sh holds 2 floats per warp.  Two named-barrier syncs.
+template <bool IS_MAX>
+__device__ __forceinline__ void block_reduce2(float &a, float &b, float *sh, int n) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        S other = s;
-        float *w = reinterpret_cast<float *>(&other);
-#pragma unroll
-        for (int i = 0; i < S::kWords; ++i) w[i] = __shfl_xor_sync(0xffffffffu, w[i], o);
-        s.merge(other);
+        const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
+        a = IS_MAX ? fmaxf(a, oa) : a + oa;
+        b = IS_MAX ? fmaxf(b, ob) : b + ob;
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = n >> 5;
-    compute_sync(n);
-    if (lane == 0) s.store(sh + warp, 32);
-    compute_sync(n);
-    S tot;
-    tot.load(sh, 32);
-    for (int w = 1; w < nwarp; ++w) {
-        S o;
-        o.load(sh + w, 32);
-        tot.merge(o);
+    compute_sync(n);                     // previous readers of sh are done
+    if (lane == 0) {
+        sh[2 * warp] = a;
+        sh[2 * warp + 1] = b;
     }
-    s = tot;
+    compute_sync(n);
+    a = sh[0];
+    b = sh[1];
+    for (int w = 1; w < nwarp; ++w) {
+        a = IS_MAX ? fmaxf(a, sh[2 * w]) : a + sh[2 * w];
+        b = IS_MAX ? fmaxf(b, sh[2 * w + 1]) : b + sh[2 * w + 1];
+    }
 }
 
 constexpr int kRowsCompute = 512;
@@ -1332,80 +930,171 @@ rows_pipe_kernel(const SoftmaxParams prm) {
         }
         bulk_wait_all();
     } else if (tid < kRowsCompute) {
+        // ---- compute: 16-byte shared loads, pairs of elements through packed fp32x2 math, no
+        // per-element label compare (the thread that owns the label's vector edits that element).
+        constexpr int NP = VN / 2;                    // pairs per 16-byte vector
         const int lane = tid & 31;
         const T *gout = static_cast<const T *>(prm.grad_out);
         T *losses = static_cast<T *>(prm.losses);
+        const LossConsts kc = prm.k;
         float gscale = 1.f;
         if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
         int k = 0;
         for (int64_t r = first; r < prm.N; r += stride, ++k) {
             const int s = k % NS;
-            const int64_t lb = prm.labels[r];
+            const int64_t lb = __ldg(prm.labels + r);
             const bool valid = lb != prm.ignore;
-            float pscale = gscale;
-            if (BWD && prm.grad_mode == 2) pscale *= to_f32(gout[r]);
-            const bool ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
+            const int lbi = valid ? ((lb >= 0 && lb < C) ? int(lb) : -2) : -1;
+            float psc = gscale;
+            if (BWD && prm.grad_mode == 2) psc *= to_f32(gout[r]);
+            const bool own = lbi >= 0 && (lbi / VN) % kRowsCompute == tid;   // my loop visits element lbi
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
             if (!compute_all(ok, kRowsCompute)) break;
             T *row = reinterpret_cast<T *>(base + s * stage_bytes);
 
-            Stat1<KIND> s1;
-            s1.init();
+            float xl = KIND == kLMargin ? kNegInf : 0.f;
+            if (KIND == kLMargin) {
+                // park the target logit out of the way of the max sweep
+                if (own) {
+                    xl = to_f32(row[lbi]);
+                    row[lbi] = from_f32<T>(sizeof(T) == 2 ? -65504.f : kNegInf);
+                }
+            } else if (!BWD && tid == 0 && lbi >= 0) {
+                xl = to_f32(row[lbi]);
+            }
+            // ---- phase 1: maximum
+            float2 m2 = splat2(kNegInf);
             for (int v = tid; v < nvec; v += kRowsCompute) {
                 const V xv = *reinterpret_cast<const V *>(row + v * VN);
 #pragma unroll
-                for (int i = 0; i < VN; ++i) s1.add(to_f32(xv.v[i]), v * VN + i == lb);
+                for (int q = 0; q < NP; ++q) m2 = max2(m2, pair_of(xv, q));
             }
-            combine_over_compute(s1, sh_stat, kRowsCompute);
-
-            Stat2<KIND> s2;
-            s2.init();
-            for (int v = tid; v < nvec; v += kRowsCompute) {
-                V xv = *reinterpret_cast<const V *>(row + v * VN);
-                if constexpr (BWD && KIND == kLSR) {
-#pragma unroll
-                    for (int i = 0; i < VN; ++i) {
-                        const float x = to_f32(xv.v[i]);
-                        const float e = exp_fast(x - s1_max(s1));
-                        s2_add_with_exp(s2, x, e, v * VN + i == lb);
-                        xv.v[i] = from_f32<T>(e);
-                    }
-                    *reinterpret_cast<V *>(row + v * VN) = xv;
-                } else {
-#pragma unroll
-                    for (int i = 0; i < VN; ++i) s2.add(to_f32(xv.v[i]), v * VN + i == lb, s1);
-                }
-            }
-            combine_over_compute(s2, sh_stat, kRowsCompute);
-            PixelFinal<KIND> fin;
-            fin.finish(s1, s2, prm.k);
-
-            if (!BWD) {
-                if (tid == 0) {
-                    const float l = valid ? fin.loss : 0.f;
-                    if (losses) losses[r] = from_f32<T>(l);
-                    if (REDUCE && valid) {
-                        acc_loss += double(l);
-                        acc_cnt += 1.0;
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.empty[s]);
+            float red1[2] = {fmaxf(m2.x, m2.y), xl};
+            if (KIND == kLMargin) {
+                // max and the owner's x_lb (others hold 0) in one exchange
+                block_reduce2<true>(red1[0], red1[1], sh_stat, kRowsCompute);
+                xl = lbi >= 0 ? red1[1] : 0.f;
             } else {
+                float dummy = 0.f;
+                block_reduce2<true>(red1[0], dummy, sh_stat, kRowsCompute);
+            }
+            const float m = red1[0];
+
+            if constexpr (KIND == kLSR) {
+                // ---- phase 2: sum of exponentials (kept in the row for backward), sum of logits
+                const float2 nml = splat2(-m * kLog2e);
+                float2 sum2 = splat2(0.f), sx2 = splat2(0.f);
                 for (int v = tid; v < nvec; v += kRowsCompute) {
                     V xv = *reinterpret_cast<const V *>(row + v * VN);
 #pragma unroll
-                    for (int i = 0; i < VN; ++i) {
-                        const float x = to_f32(xv.v[i]);
-                        float g = 0.f;
-                        if (valid)
-                            g = grad_phase3<KIND>(fin, x, v * VN + i == lb, prm.k) * pscale;
-                        xv.v[i] = from_f32<T>(g);
+                    for (int q = 0; q < NP; ++q) {
+                        const float2 x = pair_of(xv, q);
+                        const float2 e = ex2_2(fma2(x, splat2(kLog2e), nml));
+                        sum2 = add2(sum2, e);
+                        if (!BWD) sx2 = add2(sx2, x);
+                        if (BWD) set_pair(xv, q, e);
                     }
-                    *reinterpret_cast<V *>(row + v * VN) = xv;
+                    if (BWD) *reinterpret_cast<V *>(row + v * VN) = xv;
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.ready[s]);
+                float ssum = sum2.x + sum2.y, ssx = sx2.x + sx2.y;
+                block_reduce2<false>(ssum, ssx, sh_stat, kRowsCompute);
+                if (!BWD) {
+                    if (tid == 0) {
+                        float l = 0.f;
+                        if (lbi != -1)
+                            l = kc.sumy * (m + __logf(ssum)) - kc.lb_neg * ssx - (kc.lb_pos - kc.lb_neg) * xl;
+                        if (losses) losses[r] = from_f32<T>(l);
+                        if (REDUCE && lbi != -1) {
+                            acc_loss += double(l);
+                            acc_cnt += 1.0;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.empty[s]);
+                } else {
+                    const float2 a = splat2(lbi != -1 ? kc.sumy * __fdividef(psc, ssum) : 0.f);
+                    const float2 b = splat2(lbi != -1 ? -kc.lb_neg * psc : 0.f);
+                    for (int v = tid; v < nvec; v += kRowsCompute) {
+                        V xv = *reinterpret_cast<const V *>(row + v * VN);
+#pragma unroll
+                        for (int q = 0; q < NP; ++q) set_pair(xv, q, fma2(pair_of(xv, q), a, b));
+                        *reinterpret_cast<V *>(row + v * VN) = xv;
+                    }
+                    if (own) row[lbi] = from_f32<T>(to_f32(row[lbi]) - (kc.lb_pos - kc.lb_neg) * psc);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.ready[s]);
+                }
+            } else {
+                // =============================== large margin ===============================
+                // the target re-enters the sum sweep clamped to the off-target maximum
+                const float cl = fminf(xl, m);
+                if (own) row[lbi] = from_f32<T>(cl);
+                const float2 negm = splat2(-m);
+                float2 sum2 = splat2(0.f), sde2 = splat2(0.f), sx2 = splat2(0.f);
+                for (int v = tid; v < nvec; v += kRowsCompute) {
+                    const V xv = *reinterpret_cast<const V *>(row + v * VN);
+#pragma unroll
+                    for (int q = 0; q < NP; ++q) {
+                        const float2 x = pair_of(xv, q);
+                        const float2 d = add2(x, negm);
+                        const float2 e = ex2_2(mul2(d, splat2(kLog2e)));
+                        sum2 = add2(sum2, e);
+                        sde2 = fma2(d, e, sde2);
+                        sx2 = add2(sx2, x);
+                    }
+                }
+                float ssum = sum2.x + sum2.y, ssde = sde2.x + sde2.y, ssx = sx2.x + sx2.y;
+                block_reduce2<false>(ssum, ssde, sh_stat, kRowsCompute);
+                float dummy = 0.f;
+                block_reduce2<false>(ssx, dummy, sh_stat, kRowsCompute);
+                // take the clamped target back out, then the closed forms
+                const float dc = cl - m;
+                const float ec = ex2f(dc * kLog2e);
+                const float s_no = ssum - ec;
+                const float sde_no = ssde - dc * ec;
+                const float sd = (ssx - cl) - float(C - 1) * m;
+                const float inv_s = __fdividef(1.f, s_no);
+                const float sqx = sde_no * inv_s;
+                const float mm = fmaxf(m, xl);
+                const float e_no = s_no * ex2f((m - mm) * kLog2e);
+                const float e_lb = ex2f((xl - mm) * kLog2e);
+                const float s_all = e_no + e_lb;
+                const float rr = __fdividef(e_no, s_all);
+                if (!BWD) {
+                    if (tid == 0) {
+                        float l = 0.f;
+                        if (lbi != -1) l = (mm + __logf(s_all)) - xl + kc.half_lam * (sqx - kc.a * sd);
+                        if (losses) losses[r] = from_f32<T>(l);
+                        if (REDUCE && lbi != -1) {
+                            acc_loss += double(l);
+                            acc_cnt += 1.0;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.empty[s]);
+                } else {
+                    const float sc = lbi != -1 ? psc : 0.f;
+                    const float2 qa = splat2((rr + kc.half_lam * (1.f - sqx)) * sc);
+                    const float2 qb = splat2(kc.half_lam * sc);
+                    const float2 cc = splat2(-kc.half_lam * kc.a * sc);
+                    const float2 qs = splat2(lbi != -1 ? inv_s : 0.f);
+                    for (int v = tid; v < nvec; v += kRowsCompute) {
+                        V xv = *reinterpret_cast<const V *>(row + v * VN);
+#pragma unroll
+                        for (int q = 0; q < NP; ++q) {
+                            const float2 d = add2(pair_of(xv, q), negm);
+                            const float2 qq = mul2(ex2_2(mul2(d, splat2(kLog2e))), qs);
+                            set_pair(xv, q, fma2(qq, fma2(qb, d, qa), cc));
+                        }
+                        *reinterpret_cast<V *>(row + v * VN) = xv;
+                    }
+                    if (own) row[lbi] = from_f32<T>(-rr * psc);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars.ready[s]);
+                }
             }
         }
     }
@@ -1440,28 +1129,6 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
     const void *io = BWD ? prm.grads : prm.logits;
 
     const bool aligned_io = aligned16(prm.logits) && aligned16(io);
-    // (half holds 8 pixels per thread: beyond 16 channels the register file does not take it)
-    if (prm.M > 1 && prm.C <= (es == 4 ? 32 : 16) && prm.M % (16 / es) == 0 && aligned_io && !getenv("B200_NO_REGS")) {
-        // ---- registers regime
-        const int64_t groups = prm.N * (prm.M / int64_t(16 / es));
-        auto launch = [&](auto kern) -> int {
-            int per_sm = 0;
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, 0) != cudaSuccess || per_sm < 1)
-                per_sm = 1;
-            int64_t grid = int64_t(sms) * per_sm;
-            const int64_t want = (groups + kThreads - 1) / kThreads;
-            if (grid > want) grid = want;
-            if (grid > kMaxPartials) grid = kMaxPartials;
-            kern<<<dim3(unsigned(grid)), kThreads, 0, stream>>>(prm);
-            return launch_status("softmax registers kernel launch");
-        };
-        if (prm.C <= 8) return launch(regs_kernel<T, KIND, 8, BWD, REDUCE>);
-        if (prm.C <= 16) return launch(regs_kernel<T, KIND, 16, BWD, REDUCE>);
-        if constexpr (sizeof(T) == 4) {
-            if (prm.C <= 24) return launch(regs_kernel<T, KIND, 24, BWD, REDUCE>);
-            return launch(regs_kernel<T, KIND, 32, BWD, REDUCE>);
-        }
-    }
     if (prm.M > 1 && size_t(prm.C) * 32 * es + 8192 <= kSmemLimit) {
         // ---- tile regime
         const bool tma_ok = (prm.M * es) % 16 == 0 && aligned_io && prm.M < (int64_t(1) << 31) &&
@@ -1475,19 +1142,19 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
         prm.nbox = int((prm.C + 255) / 256);
         prm.CB = int((prm.C + prm.nbox - 1) / prm.nbox);
         prm.rows = prm.nbox * prm.CB;
-        prm.tiles_per_image = (prm.M + TP - 1) / TP;
+        // few channels: two boxes side by side, so that one thread pair-column spans all channels
+        prm.nbx = (tma_ok && TP == 256 && 2 * size_t(prm.rows) * TP * es <= target && prm.M > TP) ? 2 : 1;
+        const int TPT = TP * prm.nbx;
+        prm.tiles_per_image = (prm.M + TPT - 1) / TPT;
         prm.total_tiles = prm.N * prm.tiles_per_image;
-        const size_t tile_bytes = (size_t(prm.rows) * TP * es + 127) & ~size_t(127);
+        const size_t tile_bytes = (size_t(prm.rows) * TPT * es + 127) & ~size_t(127);
         const size_t red_bytes = size_t(6) * kThreads * sizeof(float);
         int rc;
         if (tma_ok) {
-            // ring depth and blocks per SM from the shared-memory budget
-            // one pixel per thread, or (B200_TILE_VEC=1) 16 bytes of pixels per thread
-            const bool vec = tune_int("B200_TILE_VEC", 0) == 1;
-            // statistics exchange area: 5 words x (slices * TP = 256 * pixels-per-thread) floats
-            const bool pair = tune_int("B200_TILE_PAIR", 1) == 1;
-            const size_t xchg_bytes = size_t(5) * kTileCompute * (vec ? 16 / es : (pair ? 2 : 1)) * sizeof(float);
-            const size_t stage_bytes = pair ? tile_bytes + size_t(TP) * sizeof(int64_t) : tile_bytes;
+            // statistics exchange area: 5 words x (slices * TP = 2 * 256) floats
+            const size_t xchg_bytes = size_t(5) * kTileCompute * 2 * sizeof(float);
+            // a stage holds the logits tile and the tile's labels
+            const size_t stage_bytes = tile_bytes + size_t(TPT) * sizeof(int64_t);
             int stages = tune_int("B200_STAGES", 2);
             while (stages > 1 && 128 + stages * stage_bytes + xchg_bytes > kSmemLimit) --stages;
             if (stages > kMaxStages) stages = kMaxStages;
@@ -1506,19 +1173,9 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             const uint32_t box[3] = {uint32_t(TP), uint32_t(prm.CB), 1u};
             if (!encode_tensor_map(&map_in, dtype, prm.logits, 3, dims, strides, box)) return B200_ERR_LAUNCH;
             if (BWD && !encode_tensor_map(&map_out, dtype, prm.grads, 3, dims, strides, box)) return B200_ERR_LAUNCH;
-            if (pair) {
-                auto kern = tile_pair_kernel<T, KIND, BWD, REDUCE>;
-                if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
-                kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in, map_out);
-            } else if (vec) {
-                auto kern = tile_pipe_kernel<T, KIND, BWD, REDUCE, 16 / int(sizeof(T))>;
-                if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
-                kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in, map_out);
-            } else {
-                auto kern = tile_pipe_kernel<T, KIND, BWD, REDUCE, 1>;
-                if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
-                kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in, map_out);
-            }
+            auto kern = tile_pair_kernel<T, KIND, BWD, REDUCE>;
+            if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
+            kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in, map_out);
         } else {
             const size_t smem = 128 + tile_bytes + red_bytes;
             int per_sm = int((220 * 1024) / (smem + 1024));
