@@ -393,24 +393,35 @@ constexpr size_t kMatchBytes = size_t(kSortWarps) * kBins * 4;
 constexpr size_t kCntBytes = size_t(kSortWarps) * kBins * 2;
 constexpr size_t kTileWordsBytes = size_t(kSortTile) * 4;
 static_assert(kMatchBytes <= kTileWordsBytes, "the value buffer reuses the match masks");
-constexpr size_t kScatterSmem = kTileWordsBytes /*bufv|match*/ + kTileWordsBytes /*bufk*/ + kCntBytes + 2 * kBins * 4;
-constexpr size_t kJaccardSmem = kMatchBytes + 2 * kCntBytes + 2 * kBins * 4;
+// The scatter kernel runs 512 threads x 16 elements on the same 8192-element tile: half the
+// registers per thread, twice the warps per SM to hide the ranking's shared-memory latency.
+constexpr int kScatThreads = 512;
+constexpr int kScatItems = kSortTile / kScatThreads;
+constexpr int kScatWarps = kScatThreads / 32;
+constexpr size_t kScatCntBytes = size_t(kScatWarps) * kBins * 2;
+constexpr size_t kScatterSmem = kTileWordsBytes /*bufv*/ + kTileWordsBytes /*bufk*/ + kScatCntBytes + 2 * kBins * 4;
+constexpr size_t kJaccardSmem = kMatchBytes + 2 * kCntBytes + 2 * kBins * 4 + kTileWordsBytes;
 
-// One ranking round of a warp: which lanes hold my digit (through an atomic OR into the
-// warp's mask word of that digit), my stable rank among them, and the warp counter update.
+// One ranking round of a warp: which lanes hold my digit, my stable rank among them, and the
+// warp counter update.  The lane mask comes from kBits ballots (one per digit bit, all
+// independent of each other), so a round is a fixed ~50 issue slots with a single
+// shared-memory round trip (the leader's counter update) -- atomics or match.any on the digit
+// cost as much per round as there are equal / distinct digits and left the kernel waiting.
 // Returns the rank of this lane's element inside (warp, digit) counting all earlier rounds.
-__device__ __forceinline__ uint32_t rank_round(uint32_t d, uint32_t *wmatch, uint16_t *wcnt, int lane,
+__device__ __forceinline__ uint32_t rank_round(uint32_t d, uint32_t * /*unused*/, uint16_t *wcnt, int lane,
                                                uint32_t lt, uint32_t &peers_out) {
-    atomicOr(&wmatch[d], 1u << lane);
-    __syncwarp();
-    const uint32_t peers = wmatch[d];
-    __syncwarp();
+    uint32_t peers = 0xffffffffu;
+#pragma unroll
+    for (int b = 0; b < kBits; ++b) {
+        const bool bit = (d >> b) & 1u;
+        const uint32_t bal = __ballot_sync(0xffffffffu, bit);
+        peers &= bit ? bal : ~bal;
+    }
     const int leader = __ffs(peers) - 1;
     uint32_t old = 0;
     if (lane == leader) {
         old = wcnt[d];
         wcnt[d] = uint16_t(old + __popc(peers));
-        wmatch[d] = 0;
     }
     __syncwarp();
     old = __shfl_sync(0xffffffffu, old, leader);
@@ -420,7 +431,7 @@ __device__ __forceinline__ uint32_t rank_round(uint32_t d, uint32_t *wmatch, uin
 
 // Stable scatter of one tile (passes that are not the last).  vals_in == nullptr: values are
 // the positions inside the segment (first pass).
-__global__ void __launch_bounds__(kSortThreads, 2)
+__global__ void __launch_bounds__(kScatThreads, 2)
 sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__restrict__ vals_in,
                     uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
                     const uint32_t *__restrict__ offsets, int64_t L, int64_t T, int shift) {
@@ -429,7 +440,7 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
     uint32_t *bufv = match;                                                  // after ranking
     uint32_t *bufk = reinterpret_cast<uint32_t *>(smem_raw + kTileWordsBytes);
     uint16_t *wcnt_all = reinterpret_cast<uint16_t *>(smem_raw + 2 * kTileWordsBytes);
-    uint32_t *binstart = reinterpret_cast<uint32_t *>(smem_raw + 2 * kTileWordsBytes + kCntBytes);
+    uint32_t *binstart = reinterpret_cast<uint32_t *>(smem_raw + 2 * kTileWordsBytes + kScatCntBytes);
     uint32_t *goff = binstart + kBins;
     __shared__ uint32_t warp_tot[32];
 
@@ -438,23 +449,22 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
     const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
     const int64_t sbase = seg * L;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wbase = warp * (32 * kSortItems);
+    const int wbase = warp * (32 * kScatItems);
 
-    for (int i = tid; i < int(kMatchBytes / 4); i += kSortThreads) match[i] = 0;
-    for (int i = tid; i < int(kCntBytes / 4); i += kSortThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
-    uint32_t key[kSortItems];
+    for (int i = tid; i < int(kScatCntBytes / 4); i += kScatThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
+    uint32_t key[kScatItems];
 #pragma unroll
-    for (int r = 0; r < kSortItems; ++r) {
+    for (int r = 0; r < kScatItems; ++r) {
         const int idx = wbase + r * 32 + lane;
         key[r] = idx < n ? __ldg(keys_in + sbase + t0 + idx) : 0xFFFFFFFFu;
     }
     __syncthreads();
-    uint32_t rank2[kSortItems / 2];     // two 16-bit ranks per register
+    uint32_t rank2[kScatItems / 2];     // two 16-bit ranks per register
     uint32_t *wmatch = match + warp * kBins;
     uint16_t *wcnt = wcnt_all + warp * kBins;
     const uint32_t lt = lanemask_lt();
 #pragma unroll
-    for (int r = 0; r < kSortItems; r += 2) {
+    for (int r = 0; r < kScatItems; r += 2) {
         uint32_t peers;
         const uint32_t r0 = rank_round(digit_of(key[r], shift), wmatch, wcnt, lane, lt, peers);
         const uint32_t r1 = rank_round(digit_of(key[r + 1], shift), wmatch, wcnt, lane, lt, peers);
@@ -462,7 +472,7 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
     }
     __syncthreads();
     // per digit: exclusive prefix over warps (in place), then over digits
-    constexpr int BPT = kBins / kSortThreads;
+    constexpr int BPT = kBins / kScatThreads;
     uint32_t cnt[BPT];
     uint32_t mine = 0;
 #pragma unroll
@@ -470,7 +480,7 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
         const int b = BPT * tid + q;
         uint32_t run = 0;
 #pragma unroll
-        for (int w = 0; w < kSortWarps; ++w) {
+        for (int w = 0; w < kScatWarps; ++w) {
             const uint32_t c = wcnt_all[w * kBins + b];
             wcnt_all[w * kBins + b] = uint16_t(run);
             run += c;
@@ -488,7 +498,7 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
         if (lane == 31) warp_tot[warp] = incl;
         __syncthreads();
         if (warp == 0) {
-            const uint32_t w = lane < kSortWarps ? warp_tot[lane] : 0;
+            const uint32_t w = lane < kScatWarps ? warp_tot[lane] : 0;
             uint32_t wi = w;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -509,22 +519,37 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
         }
     }
     __syncthreads();
-    // local sorted position; keys and values into the reorder buffers
+    // local sorted position (kept in place of the rank); keys into the reorder buffer
 #pragma unroll
-    for (int r = 0; r < kSortItems; ++r) {
-        const int idx = wbase + r * 32 + lane;
+    for (int r = 0; r < kScatItems; ++r) {
         const uint32_t d = digit_of(key[r], shift);
         const uint32_t rk = (r & 1) ? (rank2[r / 2] >> 16) : (rank2[r / 2] & 0xffffu);
         const uint32_t lp = binstart[d] + wcnt[d] + rk;
         bufk[lp] = key[r];
-        uint32_t v = uint32_t(t0 + idx);
-        if (vals_in && idx < n) v = __ldg(vals_in + sbase + t0 + idx);
-        bufv[lp] = v;
+        rank2[r / 2] = (r & 1) ? ((rank2[r / 2] & 0xffffu) | (lp << 16)) : ((rank2[r / 2] & 0xffff0000u) | lp);
+    }
+    // values: all loads of a batch are issued before the first is used
+    constexpr int kBatch = 16;
+#pragma unroll
+    for (int r0 = 0; r0 < kScatItems; r0 += kBatch) {
+        uint32_t v[kBatch];
+#pragma unroll
+        for (int r = 0; r < kBatch; ++r) {
+            const int idx = wbase + (r0 + r) * 32 + lane;
+            v[r] = uint32_t(t0 + idx);
+            if (vals_in && idx < n) v[r] = __ldg(vals_in + sbase + t0 + idx);
+        }
+#pragma unroll
+        for (int r = 0; r < kBatch; ++r) {
+            const int rr = r0 + r;
+            const uint32_t lp = (rr & 1) ? (rank2[rr / 2] >> 16) : (rank2[rr / 2] & 0xffffu);
+            bufv[lp] = v[r];
+        }
     }
     __syncthreads();
     // each digit's run goes out contiguously
 #pragma unroll 4
-    for (int i = tid; i < n; i += kSortThreads) {
+    for (int i = tid; i < n; i += kScatThreads) {
         const uint32_t k = bufk[i];
         const uint32_t gp = goff[digit_of(k, shift)] + uint32_t(i);
         keys_out[sbase + gp] = k;
@@ -548,6 +573,7 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
     uint16_t *wfg_all = reinterpret_cast<uint16_t *>(smem_raw + kMatchBytes + kCntBytes);
     uint32_t *off = reinterpret_cast<uint32_t *>(smem_raw + kMatchBytes + 2 * kCntBytes);
     uint32_t *fgoff = off + kBins;
+    uint32_t *keybuf = fgoff + kBins;                  // [kSortTile] keys of the tile
     __shared__ double sh_d[32];
 
     const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
@@ -557,7 +583,6 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wbase = warp * (32 * kSortItems);
 
-    for (int i = tid; i < int(kMatchBytes / 4); i += kSortThreads) match[i] = 0;
     for (int i = tid; i < int(2 * kCntBytes / 4); i += kSortThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
     {
         const int64_t o = (seg * T + tile) * kBins;
@@ -566,11 +591,23 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
             fgoff[b] = __ldg(fgoffsets + o + b);
         }
     }
-    uint32_t key[kSortItems];
+    // keys and pixel indices wait in shared memory (same slot, same thread: no barrier needed
+    // for them): all their global loads are in flight together and the registers stay free for
+    // the ranks
 #pragma unroll
-    for (int r = 0; r < kSortItems; ++r) {
-        const int idx = wbase + r * 32 + lane;
-        key[r] = idx < n ? __ldg(keys + sbase + t0 + idx) : 0xFFFFFFFFu;
+    for (int r0 = 0; r0 < kSortItems; r0 += 16) {
+        uint32_t kk[16], v[16];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int idx = wbase + (r0 + r) * 32 + lane;
+            kk[r] = idx < n ? __ldg(keys + sbase + t0 + idx) : 0xFFFFFFFFu;
+            v[r] = idx < n ? __ldg(vals + sbase + t0 + idx) : 0u;
+        }
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            keybuf[wbase + (r0 + r) * 32 + lane] = kk[r];
+            match[wbase + (r0 + r) * 32 + lane] = v[r];
+        }
     }
     __syncthreads();
     uint32_t rkfg[kSortItems];          // rank | fg rank << 16
@@ -580,8 +617,9 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
     const uint32_t lt = lanemask_lt();
 #pragma unroll
     for (int r = 0; r < kSortItems; ++r) {
-        const uint32_t d = digit_of(key[r], shift);
-        const bool fg = key_is_fg(key[r]);
+        const uint32_t kr = keybuf[wbase + r * 32 + lane];
+        const uint32_t d = digit_of(kr, shift);
+        const bool fg = key_is_fg(kr);
         const uint32_t fgball = __ballot_sync(0xffffffffu, fg);
         uint32_t peers;
         const uint32_t fgold_src = wfg[d];            // read before any leader updates it this round
@@ -616,7 +654,7 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
     for (int r = 0; r < kSortItems; ++r) {
         const int idx = wbase + r * 32 + lane;
         if (idx < n) {
-            const uint32_t k = key[r];
+            const uint32_t k = keybuf[idx];
             const uint32_t d = digit_of(k, shift);
             const bool ign = k == kKeyIgnored;
             const bool fg = key_is_fg(k);
@@ -626,12 +664,11 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
             const float I = float(n_pos - cs_before);
             const float U = float(union_before);
             float dj;
-            if (fg) dj = 1.f / U;
-            else dj = union_before == 0u ? 1.f : I / (U * (U + 1.f));
+            if (fg) dj = __fdividef(1.f, U);
+            else dj = union_before == 0u ? 1.f : __fdividef(I, U * (U + 1.f));
             const float err = ign ? 0.f : __uint_as_float(kOneBits - (k >> 1));
             acc += err * dj;
-            const uint32_t v = __ldg(vals + sbase + t0 + idx);
-            dst[v] = dj;
+            dst[match[idx]] = dj;
         }
     }
     double a = double(acc);
@@ -793,7 +830,7 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
         if ((rc = launch_status("lovasz sort histogram launch")) != B200_OK) return rc;
         sort_scan_kernel<false><<<unsigned(g.S), kBins, 0, s>>>(w.hist, nullptr, nullptr, g.T);
         if ((rc = launch_status("lovasz sort scan launch")) != B200_OK) return rc;
-        sort_scatter_kernel<<<nblk, kSortThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, g.L, g.T, shift);
+        sort_scatter_kernel<<<nblk, kScatThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, g.L, g.T, shift);
         if ((rc = launch_status("lovasz sort scatter launch")) != B200_OK) return rc;
         kin = kout;
         vin = vout;

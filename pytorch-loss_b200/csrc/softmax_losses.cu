@@ -522,6 +522,35 @@ __device__ __forceinline__ float2 slice_combine(float2 v, float *area, int ks, i
     return r;
 }
 
+// Sums of two / three statistics across the slices with ONE barrier.
+__device__ __forceinline__ void slice_sum2(float2 &a, float2 &b, float *area, int plane, int ks, int KS,
+                                           int TP, int pix) {
+    st_pair(area + ks * TP + pix, a);
+    st_pair(area + plane + ks * TP + pix, b);
+    compute_sync(kTileCompute);
+    a = ld_pair(area + pix);
+    b = ld_pair(area + plane + pix);
+    for (int q = 1; q < KS; ++q) {
+        a = add2(a, ld_pair(area + q * TP + pix));
+        b = add2(b, ld_pair(area + plane + q * TP + pix));
+    }
+}
+__device__ __forceinline__ void slice_sum3(float2 &a, float2 &b, float2 &c, float *area, int plane, int ks,
+                                           int KS, int TP, int pix) {
+    st_pair(area + ks * TP + pix, a);
+    st_pair(area + plane + ks * TP + pix, b);
+    st_pair(area + 2 * plane + ks * TP + pix, c);
+    compute_sync(kTileCompute);
+    a = ld_pair(area + pix);
+    b = ld_pair(area + plane + pix);
+    c = ld_pair(area + 2 * plane + pix);
+    for (int q = 1; q < KS; ++q) {
+        a = add2(a, ld_pair(area + q * TP + pix));
+        b = add2(b, ld_pair(area + plane + q * TP + pix));
+        c = add2(c, ld_pair(area + 2 * plane + q * TP + pix));
+    }
+}
+
 template <typename T, int KIND, bool BWD, bool REDUCE>
 __global__ void __launch_bounds__(kTileBlock)
 tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap map_in,
@@ -660,8 +689,8 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     }
                 }
                 if (KS > 1) {
-                    sum = slice_combine<false>(sum, red + plane, ks, KS, TPT, pix);
-                    if (!BWD) sx = slice_combine<false>(sx, red + 2 * plane, ks, KS, TPT, pix);
+                    if (BWD) sum = slice_combine<false>(sum, red + plane, ks, KS, TPT, pix);
+                    else slice_sum2(sum, sx, red + plane, plane, ks, KS, TPT, pix);
                 }
                 if (!BWD) {
                     if (ks == 0) {
@@ -729,8 +758,12 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     for (int j = ks; j < C; j += KS, q += step) m = max2(m, ld_pair(q));
                 }
                 if (KS > 1) {
+                    // the owner publishes x_lb ahead of the max exchange's barrier; all read it after
+                    if (own0) red[plane + pix] = xl.x;
+                    if (own1) red[plane + pix + 1] = xl.y;
                     m = slice_combine<true>(m, red, ks, KS, TPT, pix);
-                    xl = slice_combine<false>(xl, red + plane, ks, KS, TPT, pix);   // owner's value, others 0
+                    xl.x = lbi[0] >= 0 ? red[plane + pix] : 0.f;
+                    xl.y = lbi[1] >= 0 ? red[plane + pix + 1] : 0.f;
                 }
                 // the target re-enters the sum sweep clamped to the off-target maximum
                 const float2 cl = make_float2(fminf(xl.x, m.x), fminf(xl.y, m.y));
@@ -751,9 +784,7 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     }
                 }
                 if (KS > 1) {
-                    sum = slice_combine<false>(sum, red + 2 * plane, ks, KS, TPT, pix);
-                    sde = slice_combine<false>(sde, red + 3 * plane, ks, KS, TPT, pix);
-                    sx = slice_combine<false>(sx, red + 4 * plane, ks, KS, TPT, pix);
+                    slice_sum3(sum, sde, sx, red + 2 * plane, plane, ks, KS, TPT, pix);
                 }
                 // per pixel: take the clamped target back out, then the closed forms
                 float inv_s[2], rr[2], sqx[2], loss[2];
