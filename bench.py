@@ -13,9 +13,10 @@ otherwise).
              events over K steps (max over ranks), step captured in a CUDA graph when possible
   e2e        the same through the public module with pinned HOST inputs: H2D copy of logits
              and labels, forward, backward, D2H read of the loss, every step
-  roofline   per C-ABI entry point: algorithmic bytes / CUDA-event duration of that call,
-             measured in a second (eager) pass over the same steps; peak from
-             MEASURED_PEAKS.json (hbm_gbs) or the 6650 GB/s fallback
+  roofline   per C-ABI entry point (forward, backward): algorithmic bytes / average duration of
+             K back-to-back launches of that entry point between one pair of CUDA events
+             (rotating input sets, preallocated outputs); peak from MEASURED_PEAKS.json
+             (hbm_gbs) or the 6650 GB/s fallback
   cpu_baseline  the CPU port (oracle/) on the host cores, bounded sample, N=1 only
 
 `--impl reference` times the CPU port alone and prints the same line shape.
@@ -256,6 +257,30 @@ def direct_calls(wl, sets, device):
     return fwd, bwd
 
 
+def time_entries(wl, sets, device, args, peak):
+    """Per-entry-point durations: K back-to-back launches of the entry point through the C ABI
+    (rotating input sets, preallocated outputs) between one pair of CUDA events, so the queue
+    stays full and the figure is the kernels' own time, not the host's."""
+    fwd_name, bwd_name = wl.entries()
+    fwd_call, bwd_call = direct_calls(wl, sets, device)
+    kernels = {}
+    for name, call, nbytes in ((fwd_name, fwd_call, wl.bytes_forward()), (bwd_name, bwd_call, wl.bytes_backward())):
+        for k in range(args.warmup):
+            call(k % N_SETS)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for k in range(args.steps):
+            call(k % N_SETS)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        gbs = nbytes / (ms / 1e3) / 1e9
+        kernels[name] = {"calls": args.steps, "avg_ms": ms, "algorithmic_bytes": nbytes,
+                         "achieved_gbs": gbs, "frac": gbs / peak}
+    return kernels
+
+
 def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
     import pytorch_loss as P
     from pytorch_loss import _cabi
@@ -266,6 +291,11 @@ def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
     sets, host0 = make_sets(wl, device, rank)
     for x, _ in sets:
         x.requires_grad_(True)
+    if args.kernels_only:
+        # short path for profiler captures: only the two entry points, launched back to back
+        kernels = time_entries(wl, sets, device, args, peak)
+        _cabi.read_status(device)
+        return {"workload": wl.desc, "shape": list(wl.shape), "kernels_only": True, "kernels": kernels}
 
     def barrier():
         if world > 1:
@@ -302,33 +332,16 @@ def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
     ms_step = ms_total / args.steps
     value = world * wl.elems / (ms_step / 1e3)
 
-    # ---- per-entry-point durations: K back-to-back launches of the entry point through the
-    # C ABI (rotating input sets, preallocated outputs) between one pair of CUDA events, so
-    # the queue stays full and the figure is the kernels' own time, not the host's.
+    kernels = time_entries(wl, sets, device, args, peak)
     fwd_name, bwd_name = wl.entries()
-    fwd_call, bwd_call = direct_calls(wl, sets, device)
-    kernels = {}
-    for name, call, nbytes in ((fwd_name, fwd_call, wl.bytes_forward()), (bwd_name, bwd_call, wl.bytes_backward())):
-        for k in range(args.warmup):
-            call(k % N_SETS)
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for k in range(args.steps):
-            call(k % N_SETS)
-        b.record()
-        torch.cuda.synchronize()
-        ms = a.elapsed_time(b) / args.steps
-        gbs = nbytes / (ms / 1e3) / 1e9
-        kernels[name] = {"calls": args.steps, "avg_ms": ms, "algorithmic_bytes": nbytes,
-                         "achieved_gbs": gbs, "frac": gbs / peak}
     dominant = max(kernels, key=lambda k: kernels[k]["avg_ms"]) if kernels else None
     roofline = None
     if dominant:
         d = kernels[dominant]
         roofline = {"bound": "hbm", "kernel": dominant, "achieved": d["achieved_gbs"], "peak": peak,
                     "unit": "GB/s", "frac": d["frac"], "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)"
-                    if peak_kind == "measured" else "fallback 6650 GB/s", "traffic": None,
+                    if peak_kind == "measured" else "fallback 6650 GB/s",
+                    "traffic": wl.traffic_forward() if dominant == fwd_name else wl.traffic_backward(),
                     "step_frac": wl.bytes_step() / (ms_step / 1e3) / 1e9 / peak, "kernels": kernels}
 
     # ---- end to end from pinned host memory (eager, public module API)
@@ -382,6 +395,10 @@ def main():
     ap.add_argument("--workload", default=None, help="one of %s, or all" % ", ".join(BW.WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="time eager steps instead of CUDA-graph replays")
+    ap.add_argument("--items", type=int, default=None,
+                    help="batch items per GPU instead of the configuration's (reduced cases for profiler captures)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="only launch the forward and backward entry points back to back (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -403,6 +420,8 @@ def main():
     results = {}
     for name in [headline] + [n for n in names if n != headline]:
         wl = BW.WORKLOADS[name]
+        if args.items:
+            wl = wl.with_items(args.items)
         try:
             results[name] = measure_workload(wl, args, device, world, rank, with_cpu=(world == 1),
                                              with_e2e=True)
@@ -412,9 +431,13 @@ def main():
             results[name] = {"workload": wl.desc, "error": repr(exc)}
             torch.cuda.synchronize()
 
-    if rank == 0:
+    if rank == 0 and args.kernels_only:
+        print(json.dumps({"kernels_only": True, "steps": args.steps, "warmup": args.warmup, "workloads": results}))
+    elif rank == 0:
         h = results[headline]
         wl = BW.WORKLOADS[headline]
+        if args.items:
+            wl = wl.with_items(args.items)
         line = {
             "metric": "logit elements/s forward+backward", "value": h["value"], "unit": "logit elements/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": h["ms_per_step"],

@@ -16,6 +16,11 @@ class Workload:
         self.name, self.cfg, self.shape, self.dtype, self.desc = name, cfg, shape, dtype, desc
         self.cpu_sample_items = cpu_sample_items     # batch items timed on the CPU baseline
 
+    def with_items(self, items):
+        """The same workload with another batch size (reduced cases for profiler captures)."""
+        return Workload(self.name, self.cfg, (items,) + tuple(self.shape[1:]), self.dtype,
+                        self.desc + " [batch %d]" % items, min(self.cpu_sample_items, items))
+
     @property
     def elems(self):
         return math.prod(self.shape)
@@ -47,6 +52,21 @@ class Workload:
 
     def bytes_step(self):
         return self.bytes_forward() + self.bytes_backward()
+
+    # DRAM traffic per logit element (dram__bytes_read.sum + dram__bytes_write.sum of every kernel
+    # behind the entry point) from the ncu captures summarised under profiles/, taken on reduced
+    # batches and scaled by the element count (traffic grows in proportion).  Written gradients
+    # that are still in the 126 MB L2 when the kernel ends are not counted by those counters.
+    MEASURED_TRAFFIC = {
+        "focal": (8.13, 9.92), "lsr": (4.51, 5.73), "lmargin": (4.10, 7.38),
+        "lovasz": (61.0, 11.57), "lsr_rows": (2.03, 3.14),
+    }
+
+    def traffic_forward(self):
+        return self.MEASURED_TRAFFIC[self.name][0] * self.elems
+
+    def traffic_backward(self):
+        return self.MEASURED_TRAFFIC[self.name][1] * self.elems
 
     def entries(self):
         stem = {"lsr": "lsr", "lsr_rows": "lsr", "focal": "focal", "lmargin": "lmargin", "lovasz": "lovasz"}[self.name]

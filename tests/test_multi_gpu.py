@@ -1,0 +1,75 @@
+"""Batch sharded over 2 GPUs (one process each, NCCL): the modules built with
+`process_group=True` return the loss of the concatenated batch and its gradient on the local
+shard.  Skipped on boxes with fewer than two GPUs."""
+import datetime
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import PKG_PARENT, ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out):
+    for p in (ROOT, PKG_PARENT):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=120))
+    import pytorch_loss as P
+    from pytorch_loss import _sharding
+    from oracle import losses as O
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(4, 19, 32, 32, generator=g)
+    labels = torch.randint(0, 19, (4, 32, 32), generator=g)
+    labels[0, :20] = 255                                    # uneven ignore counts across ranks
+    flabels = (torch.rand(4, 19, 32, 32, generator=g) < 0.2).float()
+    lo, hi = _sharding.shard_bounds(4, world, rank)
+    cases = [
+        (P.LabelSmoothSoftmaxCEV3(0.1, 'mean', 255, process_group=True), labels,
+         O.label_smooth_ce(logits, labels, 0.1, 255, 'mean')),
+        (P.LargeMarginSoftmaxV3(0.3, 'mean', 255, process_group=True), labels,
+         O.large_margin_softmax(logits, labels, 0.3, 255, 'mean')),
+        (P.FocalLossV3(0.25, 2, 'mean', process_group=True), flabels,
+         O.focal_loss(logits, flabels, 0.25, 2.0, 'mean')),
+        (P.LovaszSoftmaxV3('mean', 255, per_image=True, process_group=True), labels,
+         O.lovasz_softmax(logits, labels, 255, 'mean', per_image=True)),
+    ]
+    errs = []
+    for crit, lab, (want_loss, want_grad) in cases:
+        x = logits[lo:hi].to(dev).requires_grad_(True)
+        loss = crit(x, lab[lo:hi].to(dev))
+        loss.backward()
+        errs.append((abs(float(loss) - float(want_loss)) / abs(float(want_loss)),
+                     float((x.grad.cpu() - want_grad[lo:hi]).abs().max())))
+    torch.save(errs, "%s.%d" % (out, rank))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_losses_match_concatenated_batch(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = str(tmp_path / "errs")
+    mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    for rank in range(2):
+        for loss_err, grad_err in torch.load("%s.%d" % (out, rank)):
+            assert loss_err <= 1e-5, loss_err
+            assert grad_err <= 1e-5, grad_err
