@@ -506,6 +506,41 @@ __device__ __forceinline__ void st_pair(__half *p, float2 v) {
     *reinterpret_cast<__half2 *>(p) = __float22half2_rn(v);
 }
 
+// The same operations on values that STAY packed in one 64-bit register pair across a loop
+// (loads and stores move the pair as one 8-byte word; only the two ex2 need the halves).
+typedef unsigned long long pk_t;
+__device__ __forceinline__ pk_t padd(pk_t a, pk_t b) {
+    pk_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ pk_t pmul(pk_t a, pk_t b) {
+    pk_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ pk_t pfma(pk_t a, pk_t b, pk_t c) {
+    pk_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ pk_t pex2(pk_t t) {
+    pk_t r;
+    asm("{\n\t.reg .f32 a, b;\n\t"
+        "mov.b64 {a, b}, %1;\n\t"
+        "ex2.approx.ftz.f32 a, a;\n\t"
+        "ex2.approx.ftz.f32 b, b;\n\t"
+        "mov.b64 %0, {a, b};\n\t}"
+        : "=l"(r)
+        : "l"(t));
+    return r;
+}
+__device__ __forceinline__ pk_t psplat(float v) { return pk2(make_float2(v, v)); }
+__device__ __forceinline__ pk_t ld_pk(const float *p) { return *reinterpret_cast<const pk_t *>(p); }
+__device__ __forceinline__ pk_t ld_pk(const __half *p) { return pk2(ld_pair(p)); }
+__device__ __forceinline__ void st_pk(float *p, pk_t v) { *reinterpret_cast<pk_t *>(p) = v; }
+__device__ __forceinline__ void st_pk(__half *p, pk_t v) { st_pair(p, upk2(v)); }
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -653,8 +688,9 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     if (i == 0) psc.x *= g; else psc.y *= g;
                 }
             }
-            const bool own0 = lbi[0] >= 0 && lbi[0] % KS == ks;   // I visit the label channel of pixel i
-            const bool own1 = lbi[1] >= 0 && lbi[1] % KS == ks;
+            // KS is a power of two: I visit the label channel of pixel i iff its low bits are ks
+            const bool own0 = lbi[0] >= 0 && (lbi[0] & (KS - 1)) == ks;
+            const bool own1 = lbi[1] >= 0 && (lbi[1] & (KS - 1)) == ks;
 
             T *tile = reinterpret_cast<T *>(base + s * stage_bytes);
             T *mine = tile + bxo + ks * TP;           // my first channel, my pixel pair
@@ -675,18 +711,21 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     if (lbi[1] >= 0) xl.y = to_f32(tile[bxo + lbi[1] * TP + 1]);
                 }
                 // ---- phase 2: sum of exponentials, sum of logits
-                const float2 nml = mul2(m, splat2(-kLog2e));
-                float2 sum = splat2(0.f), sx = splat2(0.f);
+                float2 sum, sx;
                 {
+                    const pk_t nml = pk2(mul2(m, splat2(-kLog2e))), l2e = psplat(kLog2e);
+                    pk_t psum = psplat(0.f), psx = psplat(0.f);
                     T *q = mine;
 #pragma unroll 4
                     for (int j = ks; j < C; j += KS, q += step) {
-                        const float2 x = ld_pair(q);
-                        const float2 e = ex2_2(fma2(x, splat2(kLog2e), nml));
-                        sum = add2(sum, e);
-                        if (!BWD) sx = add2(sx, x);
-                        if (BWD) st_pair(q, e);
+                        const pk_t x = ld_pk(q);
+                        const pk_t e = pex2(pfma(x, l2e, nml));
+                        psum = padd(psum, e);
+                        if (!BWD) psx = padd(psx, x);
+                        if (BWD) st_pk(q, e);
                     }
+                    sum = upk2(psum);
+                    sx = upk2(psx);
                 }
                 if (KS > 1) {
                     if (BWD) sum = slice_combine<false>(sum, red + plane, ks, KS, TPT, pix);
@@ -720,9 +759,10 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     b.x = lbi[0] != -1 ? -kc.lb_neg * psc.x : 0.f;
                     b.y = lbi[1] != -1 ? -kc.lb_neg * psc.y : 0.f;
                     {
+                        const pk_t pa = pk2(a), pb = pk2(b);
                         T *q = mine;
 #pragma unroll 4
-                        for (int j = ks; j < C; j += KS, q += step) st_pair(q, fma2(ld_pair(q), a, b));
+                        for (int j = ks; j < C; j += KS, q += step) st_pk(q, pfma(ld_pk(q), pa, pb));
                     }
                     const float dt = -(kc.lb_pos - kc.lb_neg);
                     if (own0) {
@@ -770,18 +810,23 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                 if (own0) tile[bxo + lbi[0] * TP] = from_f32<T>(cl.x);
                 if (own1) tile[bxo + lbi[1] * TP + 1] = from_f32<T>(cl.y);
                 const float2 negm = make_float2(-m.x, -m.y);
-                float2 sum = splat2(0.f), sde = splat2(0.f), sx = splat2(0.f);
+                float2 sum, sde, sx;
                 {
+                    const pk_t pnegm = pk2(negm), l2e = psplat(kLog2e);
+                    pk_t psum = psplat(0.f), psde = psplat(0.f), psx = psplat(0.f);
                     const T *q = mine;
 #pragma unroll 4
                     for (int j = ks; j < C; j += KS, q += step) {
-                        const float2 x = ld_pair(q);
-                        const float2 d = add2(x, negm);
-                        const float2 e = ex2_2(mul2(d, splat2(kLog2e)));
-                        sum = add2(sum, e);
-                        sde = fma2(d, e, sde);
-                        sx = add2(sx, x);
+                        const pk_t x = ld_pk(q);
+                        const pk_t d = padd(x, pnegm);
+                        const pk_t e = pex2(pmul(d, l2e));
+                        psum = padd(psum, e);
+                        psde = pfma(d, e, psde);
+                        psx = padd(psx, x);
                     }
+                    sum = upk2(psum);
+                    sde = upk2(psde);
+                    sx = upk2(psx);
                 }
                 if (KS > 1) {
                     slice_sum3(sum, sde, sx, red + 2 * plane, plane, ks, KS, TPT, pix);
@@ -837,13 +882,14 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                         else { qa.y = A; qb.y = B; cc.y = Cc; qs.y = Q; }
                     }
                     {
+                        const pk_t pnegm = pk2(negm), l2e = psplat(kLog2e);
+                        const pk_t pqa = pk2(qa), pqb = pk2(qb), pcc = pk2(cc), pqs = pk2(qs);
                         T *q = mine;
 #pragma unroll 4
                         for (int j = ks; j < C; j += KS, q += step) {
-                            const float2 x = ld_pair(q);
-                            const float2 d = add2(x, negm);
-                            const float2 qq = mul2(ex2_2(mul2(d, splat2(kLog2e))), qs);
-                            st_pair(q, fma2(qq, fma2(qb, d, qa), cc));
+                            const pk_t d = padd(ld_pk(q), pnegm);
+                            const pk_t qq = pmul(pex2(pmul(d, l2e)), pqs);
+                            st_pk(q, pfma(qq, pfma(pqb, d, pqa), pcc));
                         }
                     }
                     if (own0) tile[bxo + lbi[0] * TP] = from_f32<T>(-rr[0] * psc.x);
