@@ -58,8 +58,8 @@ class Workload:
     # batches and scaled by the element count (traffic grows in proportion).  Written gradients
     # that are still in the 126 MB L2 when the kernel ends are not counted by those counters.
     MEASURED_TRAFFIC = {
-        "focal": (8.13, 9.92), "lsr": (4.51, 5.73), "lmargin": (4.10, 7.38),
-        "lovasz": (61.0, 11.57), "lsr_rows": (2.03, 3.14),
+        "focal": (8.05, 9.95), "lsr": (4.45, 5.72), "lmargin": (4.10, 7.37),
+        "lovasz": (61.2, 11.55), "lsr_rows": (2.01, 3.15),
     }
 
     def traffic_forward(self):
