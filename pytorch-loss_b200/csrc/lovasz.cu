@@ -24,6 +24,9 @@
 //            dJ to pixel order (the `jacc` output).
 //   backward one tile kernel: softmax recomputed, g = p*(gp - sum p*gp), zero at ignored pixels.
 #include "common.cuh"
+#include "pipeline.cuh"
+
+#include <cstdlib>
 
 namespace b200 {
 namespace {
@@ -273,6 +276,217 @@ lovasz_tile_kernel(const TileArgs a, const __grid_constant__ CUtensorMap map_log
         }
     }
     if (TMA && tid == 0) bulk_wait_all();
+}
+
+// -------------------------------------------- pipelined pair-per-thread tile kernels
+//
+// The production form of the keys and backward kernels for few classes (a tile of all C
+// channels x 512 pixels fits one shared-memory stage).  Block = 256 compute threads + a loader
+// warp + a storer warp on the mbarrier ring of pipeline.cuh; a stage holds the logits tile
+// (two TMA boxes of 256 pixels side by side), in backward the dJ tile behind it, and the 512
+// labels of the tile.  A compute thread owns two adjacent pixels over ALL channels, so the
+// per-pixel statistics never leave its registers, and every sweep moves 8-byte pairs through
+// packed fp32x2 arithmetic.  The label channel is not compared per element: the thread edits
+// that one element of its column instead (keys: rewrites the key after the sweep; backward:
+// flips the sign of dJ before it).
+
+constexpr int kPairTP = 256;               // pixels per TMA box
+constexpr int kPairTile = 2 * kPairTP;     // pixels per tile
+
+struct PairLayout {
+    int box_elems;          // floats of one box (C * 256)
+    uint32_t tile_bytes;    // one C x 512 fp32 tile
+    uint32_t label_off;     // byte offset of the labels inside a stage
+    uint32_t stage_bytes;
+};
+
+__host__ __device__ inline PairLayout pair_layout(int C, bool bwd) {
+    PairLayout l;
+    l.box_elems = C * kPairTP;
+    l.tile_bytes = uint32_t(C) * kPairTile * 4u;
+    l.label_off = (bwd ? 2u : 1u) * l.tile_bytes;          // multiples of 2 KB: 128-byte aligned
+    l.stage_bytes = l.label_off + kPairTile * 8u;
+    return l;
+}
+
+template <bool BWD>
+__global__ void __launch_bounds__(kTileBlock)
+lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUtensorMap map_logits,
+                   const __grid_constant__ CUtensorMap map_seg,
+                   const __grid_constant__ CUtensorMap map_grads) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ PipeBarriers bars;
+    const LovaszGeom &g = a.g;
+    const int C = int(g.C);
+    const PairLayout lay = pair_layout(C, BWD);
+    unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    const int tid = threadIdx.x;
+    const int64_t tiles_per_image = (g.M + kPairTile - 1) / kPairTile;
+    const int64_t total_tiles = g.N * tiles_per_image;
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+
+    // keys: the storer frees the stage, as in backward
+    pipe_init<kTileCompute, true>(bars, NS);
+
+    if (tid == kTileCompute) {
+        int k = 0;
+        for (int64_t t = first; t < total_tiles; t += stride, ++k) {
+            const int s = k % NS;
+            if (k >= NS && !mbar_wait_bounded(&bars.empty[s], ((k / NS) - 1) & 1, a.status)) break;
+            const int64_t n = t / tiles_per_image;
+            const int64_t p0 = (t % tiles_per_image) * kPairTile;
+            unsigned char *stage = base + size_t(s) * lay.stage_bytes;
+            float *lt = reinterpret_cast<float *>(stage);
+            float *jt = reinterpret_cast<float *>(stage + lay.tile_bytes);
+            int64_t npix = g.M - p0;
+            if (npix > kPairTile) npix = kPairTile;
+            const int nbx = int((npix + kPairTP - 1) / kPairTP);
+            const uint32_t label_bytes = uint32_t(npix) * 8u;        // M % 4 == 0: a multiple of 16
+            mbar_expect_tx(&bars.full[s], uint32_t(nbx) * (BWD ? 2u : 1u) * (lay.tile_bytes / 2) + label_bytes);
+            for (int bx = 0; bx < nbx; ++bx) {
+                tma_load_3d(lt + size_t(bx) * lay.box_elems, &map_logits, int(p0) + bx * kPairTP, 0, int(n),
+                            &bars.full[s]);
+                if (BWD)
+                    tma_load_3d(jt + size_t(bx) * lay.box_elems, &map_seg, int(p0) + bx * kPairTP, 0, int(n),
+                                &bars.full[s]);
+            }
+            bulk_load_1d(stage + lay.label_off, a.labels + n * g.M + p0, label_bytes, &bars.full[s]);
+        }
+    } else if (tid == kTileCompute + 32) {
+        int k = 0;
+        for (int64_t t = first; t < total_tiles; t += stride, ++k) {
+            const int s = k % NS;
+            if (!mbar_wait_bounded(&bars.ready[s], (k / NS) & 1, a.status)) break;
+            const int64_t n = t / tiles_per_image;
+            const int64_t p0 = (t % tiles_per_image) * kPairTile;
+            const float *lt = reinterpret_cast<const float *>(base + size_t(s) * lay.stage_bytes);
+            int64_t npix = g.M - p0;
+            if (npix > kPairTile) npix = kPairTile;
+            const int nbx = int((npix + kPairTP - 1) / kPairTP);
+            for (int bx = 0; bx < nbx; ++bx)
+                tma_store_3d(BWD ? &map_grads : &map_seg, int(p0) + bx * kPairTP, 0, int(n),
+                             lt + size_t(bx) * lay.box_elems);
+            bulk_commit();
+            bulk_wait_read_all();
+            mbar_arrive(&bars.empty[s]);
+        }
+        bulk_wait_all();
+    } else if (tid < kTileCompute) {
+        const int lane = tid & 31;
+        const int pix = tid * 2;                                          // my pair inside the tile
+        const int bxo = (pix / kPairTP) * lay.box_elems + (pix % kPairTP);   // its offset in channel 0
+        int k = 0;
+        for (int64_t t = first; t < total_tiles; t += stride, ++k) {
+            const int s = k % NS;
+            const int64_t n = t / tiles_per_image;
+            const int64_t px0 = (t % tiles_per_image) * kPairTile + pix;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, a.status);
+            if (!compute_all(ok, kTileCompute)) break;
+
+            unsigned char *stage = base + size_t(s) * lay.stage_bytes;
+            const int64_t *tile_labels = reinterpret_cast<const int64_t *>(stage + lay.label_off);
+            bool valid[2];
+            int lbi[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const bool inb = px0 + i < g.M;
+                const int64_t lb = inb ? tile_labels[pix + i] : a.ignore;
+                valid[i] = inb && lb != a.ignore;
+                lbi[i] = (valid[i] && lb >= 0 && lb < C) ? int(lb) : -1;   // -1: no foreground channel
+            }
+            float *mine = reinterpret_cast<float *>(stage) + bxo;
+
+            // ---- sweep 1: maximum
+            float2 m = splat2(-3.402823466e38f);
+            {
+                const float *q = mine;
+#pragma unroll 4
+                for (int j = 0; j < C; ++j, q += kPairTP) m = max2(m, ld_pair(q));
+            }
+            // ---- sweep 2: e = 2^((x - m) log2 e) left in the tile, and its sum
+            float2 sum;
+            {
+                const pk_t nml = pk2(mul2(m, splat2(-kLog2e))), l2e = psplat(kLog2e);
+                pk_t psum = psplat(0.f);
+                float *q = mine;
+#pragma unroll 4
+                for (int j = 0; j < C; ++j, q += kPairTP) {
+                    const pk_t e = pex2(pfma(ld_pk(q), l2e, nml));
+                    psum = padd(psum, e);
+                    st_pk(q, e);
+                }
+                sum = upk2(psum);
+            }
+            const float2 inv = make_float2(__fdividef(1.f, sum.x), __fdividef(1.f, sum.y));
+
+            if constexpr (!BWD) {
+                // ---- sweep 3: key = ((bits(1.0) - bits(err)) << 1) | fg with err = p off the label
+                // channel; an ignored pixel gets multiplier 0 and addend 0xFFFFFFFF instead.
+                float e_lb[2] = {0.f, 0.f};
+                if (lbi[0] >= 0) e_lb[0] = mine[lbi[0] * kPairTP];
+                if (lbi[1] >= 0) e_lb[1] = mine[lbi[1] * kPairTP + 1];
+                const uint32_t mul0 = valid[0] ? 0xFFFFFFFEu : 0u, add0 = valid[0] ? 2u * kOneBits : kKeyIgnored;
+                const uint32_t mul1 = valid[1] ? 0xFFFFFFFEu : 0u, add1 = valid[1] ? 2u * kOneBits : kKeyIgnored;
+                const pk_t pinv = pk2(inv);
+                {
+                    float *q = mine;
+#pragma unroll 4
+                    for (int j = 0; j < C; ++j, q += kPairTP) {
+                        const float2 p = upk2(pmul(ld_pk(q), pinv));
+                        const uint32_t b0 = min(__float_as_uint(p.x), kOneBits);
+                        const uint32_t b1 = min(__float_as_uint(p.y), kOneBits);
+                        uint2 key;
+                        key.x = b0 * mul0 + add0;
+                        key.y = b1 * mul1 + add1;
+                        *reinterpret_cast<uint2 *>(q) = key;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    if (lbi[i] >= 0) {
+                        const float err = fmaxf(1.f - e_lb[i] * (i ? inv.y : inv.x), 0.f);
+                        const uint32_t eb = min(__float_as_uint(err), kOneBits);
+                        reinterpret_cast<uint32_t *>(mine)[lbi[i] * kPairTP + i] = ((kOneBits - eb) << 1) | 1u;
+                    }
+                }
+            } else {
+                float *jmine = reinterpret_cast<float *>(stage + lay.tile_bytes) + bxo;
+                const float *go = a.seg_grad + (g.per_image ? n * g.C : 0);
+                // the label channel's dJ enters with the opposite sign
+                if (lbi[0] >= 0) jmine[lbi[0] * kPairTP] = -jmine[lbi[0] * kPairTP];
+                if (lbi[1] >= 0) jmine[lbi[1] * kPairTP + 1] = -jmine[lbi[1] * kPairTP + 1];
+                // ---- sweep 3: gp = dJ * dL/dloss_c (left in the dJ tile), dot = sum e * gp
+                float2 dot;
+                {
+                    pk_t pdot = psplat(0.f);
+                    const float *q = mine;
+                    float *jq = jmine;
+#pragma unroll 4
+                    for (int j = 0; j < C; ++j, q += kPairTP, jq += kPairTP) {
+                        const pk_t gp = pmul(ld_pk(jq), psplat(__ldg(go + j)));
+                        pdot = pfma(ld_pk(q), gp, pdot);
+                        st_pk(jq, gp);
+                    }
+                    dot = upk2(pdot);
+                }
+                // ---- sweep 4: g = p * (gp - sum p gp) = e * (gp * inv - dot * inv^2); 0 if ignored
+                const float2 iv = make_float2(valid[0] ? inv.x : 0.f, valid[1] ? inv.y : 0.f);
+                const pk_t piv = pk2(iv);
+                const pk_t pc = pk2(make_float2(-dot.x * iv.x * iv.x, -dot.y * iv.y * iv.y));
+                {
+                    float *q = mine;
+                    const float *jq = jmine;
+#pragma unroll 4
+                    for (int j = 0; j < C; ++j, q += kPairTP, jq += kPairTP)
+                        st_pk(q, pmul(ld_pk(q), pfma(ld_pk(jq), piv, pc)));
+                }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.ready[s]);
+        }
+    }
 }
 
 // ------------------------------------------------------------------ sort kernels
@@ -732,6 +946,11 @@ bool make_maps(const LovaszGeom &g, const void *logits_like, const void *seg_lik
     return true;
 }
 
+inline int env_int(const char *name, int dflt) {
+    const char *v = std::getenv(name);
+    return (v && *v) ? std::atoi(v) : dflt;
+}
+
 template <bool BWD>
 int launch_tile(const TileArgs &a, cudaStream_t stream) {
     const LovaszGeom &g = a.g;
@@ -752,6 +971,29 @@ int launch_tile(const TileArgs &a, cudaStream_t stream) {
     if (tma_ok) {
         if (!make_maps(g, a.logits, seg_ptr, &m_logits, &m_seg, BWD ? B200_F32 : 99)) return B200_ERR_LAUNCH;
         if (BWD && !make_maps(g, a.grads, nullptr, &m_grads, nullptr, 0)) return B200_ERR_LAUNCH;
+    }
+    // few classes, aligned: the pipelined pair-per-thread kernel
+    const PairLayout lay = pair_layout(int(g.C), BWD);
+    if (tma_ok && g.TP == kPairTP && g.nbox == 1 && g.M >= kPairTile && g.M % 4 == 0 && aligned16(a.labels) &&
+        lay.stage_bytes <= 110u * 1024 && !env_int("B200_LOVASZ_NO_PAIR", 0)) {
+        int stages = env_int("B200_LOVASZ_STAGES", 1);
+        if (stages < 1) stages = 1;
+        if (stages > kMaxStages) stages = kMaxStages;
+        while (stages > 1 && size_t(stages) * lay.stage_bytes > 200u * 1024) --stages;
+        const size_t psmem = 128 + size_t(stages) * lay.stage_bytes;
+        int ctas = int((224u * 1024) / (psmem + 1280));
+        const int cap = env_int("B200_LOVASZ_CTAS", BWD ? 3 : 4);
+        if (ctas > cap) ctas = cap;
+        if (ctas < 1) ctas = 1;
+        const int64_t ptiles = g.N * ((g.M + kPairTile - 1) / kPairTile);
+        int64_t pgrid = int64_t(sm_count()) * ctas;
+        if (pgrid > ptiles) pgrid = ptiles;
+        auto kern = lovasz_pair_kernel<BWD>;
+        if (psmem > 40 * 1024 &&
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(psmem)) != cudaSuccess)
+            return launch_status("cudaFuncSetAttribute(lovasz pair)");
+        kern<<<dim3(unsigned(pgrid)), kTileBlock, psmem, stream>>>(a, stages, m_logits, m_seg, m_grads);
+        return launch_status(BWD ? "lovasz backward kernel launch" : "lovasz keys kernel launch");
     }
     auto launch = [&](auto kern) -> int {
         if (smem > 48 * 1024 &&

@@ -20,7 +20,9 @@ def _blocky_labels(gen, n, c, h, w, cell, ignore, frac):
 
 
 SHAPES = [(2, 5, 12, 11), (1, 19, 16, 16), (3, 4, 9, 7), (2, 7, 40, 52), (1, 3, 130, 127),
-          (2, 19, 96, 96), (1, 2, 8, 8), (2, 40, 33, 20), (1, 300, 12, 12)]
+          (2, 19, 96, 96), (1, 2, 8, 8), (2, 40, 33, 20), (1, 300, 12, 12),
+          # 512-pixel pipelined tiles: ragged second box, widest backward / forward class counts
+          (2, 19, 26, 30), (1, 26, 24, 37), (1, 40, 30, 28)]
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
