@@ -27,6 +27,7 @@
 #include "pipeline.cuh"
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace b200 {
 namespace {
@@ -69,6 +70,10 @@ struct Workspace {
     uint32_t *n_pos;      // [S]
     double *partial;      // [S][T]
     unsigned *status;     // 1 word
+    uint32_t *maxfg;      // [S]  largest foreground key seen (0: none)
+    uint32_t *minkey;     // [S]  smallest key among the sampled tiles (0xFFFFFFFF: none)
+    uint32_t *kept;       // [S][T] kept elements per tile -> exclusive offsets
+    uint32_t *Lp;         // [S]  kept elements of the segment
     size_t bytes;
 };
 
@@ -85,6 +90,10 @@ Workspace carve(void *base, const LovaszGeom &g) {
         return r;
     };
     w.status = reinterpret_cast<unsigned *>(take(256));
+    w.maxfg = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
+    w.minkey = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
+    w.kept = reinterpret_cast<uint32_t *>(take(size_t(g.S) * g.T * 4));
+    w.Lp = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
     w.keysA = reinterpret_cast<uint32_t *>(take(e * 4));
     w.keysB = reinterpret_cast<uint32_t *>(take(e * 4));
     w.valsA = reinterpret_cast<uint32_t *>(take(e * 4));
@@ -125,6 +134,8 @@ struct TileArgs {
     const float *jacc;       // backward: segment-major input
     const float *seg_grad;   // backward: [S]
     float *grads;            // backward: [N, C, M]
+    uint32_t *maxfg;         // keys kernel: per-segment trackers of the pruning bound
+    uint32_t *minkey;
     unsigned *status;
     int64_t ignore;
     LovaszGeom g;
@@ -134,6 +145,28 @@ struct TileArgs {
 __device__ __forceinline__ int64_t seg_offset(const LovaszGeom &g, int64_t n, int64_t c, int64_t m) {
     return g.per_image ? (n * g.C + c) * g.M + m : c * (g.N * g.M) + n * g.M + m;
 }
+
+// Pruning bound of a segment.  Once the last foreground element of a class has gone by in the
+// sorted order, the intersection count is zero and every later element has dJ = 0 exactly: it
+// adds nothing to the loss and its gradient weight is zero.  So only elements whose error is
+// at least the SMALLEST foreground error (the largest foreground key) need sorting; a class
+// without foreground pixels needs only its largest error, for which any lower bound of it (the
+// smallest key among a sample of the tiles) serves.  The keys kernels track both per segment.
+//
+// One pixel's foreground key: when the whole warp holds the same class (the usual case inside
+// an object) one redux + one atomic, else one atomic per lane.
+__device__ __forceinline__ void track_fg(uint32_t *maxfg, int cls, uint32_t key, int lane) {
+    const int c0 = __shfl_sync(0xffffffffu, cls, 0);
+    if (__all_sync(0xffffffffu, cls == c0)) {
+        if (c0 >= 0) {
+            const uint32_t v = __reduce_max_sync(0xffffffffu, key);
+            if (lane == 0) atomicMax(maxfg + c0, v);
+        }
+    } else if (cls >= 0) {
+        atomicMax(maxfg + cls, key);
+    }
+}
+constexpr int kSampleEvery = 16;    // tiles of an image whose keys feed the smallest-key sample
 
 // BWD = false: logits tile -> key tile (in place, 4 bytes each) -> keys.
 // BWD = true : logits tile + jacc tile -> gradient tile (in place) -> grads.
@@ -213,6 +246,9 @@ lovasz_tile_kernel(const TileArgs a, const __grid_constant__ CUtensorMap map_log
 
         if (!BWD) {
             uint32_t *kcol = reinterpret_cast<uint32_t *>(col);
+            const int64_t seg0 = g.per_image ? n * g.C : 0;
+            const bool sample = (t % g.tiles_per_image) % kSampleEvery == 0;
+            uint32_t kfg = 0;
             for (int j = ks; j < C; j += KS) {
                 uint32_t key = kKeyIgnored;
                 if (valid) {
@@ -222,9 +258,15 @@ lovasz_tile_kernel(const TileArgs a, const __grid_constant__ CUtensorMap map_log
                     uint32_t eb = __float_as_uint(fmaxf(err, 0.f));
                     eb = eb > kOneBits ? kOneBits : eb;
                     key = ((kOneBits - eb) << 1) | (fg ? 1u : 0u);
+                    if (fg) kfg = key;
                 }
                 kcol[j * TP] = key;
+                if (sample) {       // a warp shares its channel slice: same j in every lane
+                    const uint32_t v = __reduce_min_sync(0xffffffffu, key);
+                    if ((tid & 31) == 0 && v != kKeyIgnored) atomicMin(a.minkey + seg0 + j, v);
+                }
             }
+            track_fg(a.maxfg + seg0, kfg ? int(lb) : -1, kfg, tid & 31);
         } else {
             const float *jcol = jt + p;
             const int64_t gseg = g.per_image ? n * g.C : 0;
@@ -292,6 +334,7 @@ lovasz_tile_kernel(const TileArgs a, const __grid_constant__ CUtensorMap map_log
 
 constexpr int kPairTP = 256;               // pixels per TMA box
 constexpr int kPairTile = 2 * kPairTP;     // pixels per tile
+constexpr int kPairMaxC = 40;              // classes whose 256-pixel box stays within 40 KB
 
 struct PairLayout {
     int box_elems;          // floats of one box (C * 256)
@@ -325,6 +368,13 @@ lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUten
     const int64_t total_tiles = g.N * tiles_per_image;
     const int64_t first = blockIdx.x, stride = gridDim.x;
 
+    // keys: block-level trackers of the pruning bound, flushed to the segment's words when the
+    // block moves to another image (per-image segments) and at the end
+    __shared__ uint32_t blk_maxfg[kPairMaxC], blk_min[kPairMaxC];
+    if (!BWD && tid < kPairMaxC) {
+        blk_maxfg[tid] = 0u;
+        blk_min[tid] = kKeyIgnored;
+    }
     // keys: the storer frees the stage, as in backward
     pipe_init<kTileCompute, true>(bars, NS);
 
@@ -375,11 +425,25 @@ lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUten
         const int lane = tid & 31;
         const int pix = tid * 2;                                          // my pair inside the tile
         const int bxo = (pix / kPairTP) * lay.box_elems + (pix % kPairTP);   // its offset in channel 0
+        auto flush_trackers = [&](int64_t img) {
+            compute_sync(kTileCompute);
+            if (tid < C) {
+                const int64_t seg = (g.per_image ? img * C : 0) + tid;
+                if (blk_maxfg[tid]) atomicMax(a.maxfg + seg, blk_maxfg[tid]);
+                if (blk_min[tid] != kKeyIgnored) atomicMin(a.minkey + seg, blk_min[tid]);
+                blk_maxfg[tid] = 0u;
+                blk_min[tid] = kKeyIgnored;
+            }
+            compute_sync(kTileCompute);
+        };
+        int64_t cur_n = -1;
         int k = 0;
         for (int64_t t = first; t < total_tiles; t += stride, ++k) {
             const int s = k % NS;
             const int64_t n = t / tiles_per_image;
             const int64_t px0 = (t % tiles_per_image) * kPairTile + pix;
+            if (!BWD && g.per_image && n != cur_n && cur_n >= 0) flush_trackers(cur_n);
+            cur_n = n;
             bool ok = true;
             if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, a.status);
             if (!compute_all(ok, kTileCompute)) break;
@@ -429,7 +493,7 @@ lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUten
                 const uint32_t mul0 = valid[0] ? 0xFFFFFFFEu : 0u, add0 = valid[0] ? 2u * kOneBits : kKeyIgnored;
                 const uint32_t mul1 = valid[1] ? 0xFFFFFFFEu : 0u, add1 = valid[1] ? 2u * kOneBits : kKeyIgnored;
                 const pk_t pinv = pk2(inv);
-                {
+                auto key_sweep = [&](auto sampled) {
                     float *q = mine;
 #pragma unroll 4
                     for (int j = 0; j < C; ++j, q += kPairTP) {
@@ -440,15 +504,26 @@ lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUten
                         key.x = b0 * mul0 + add0;
                         key.y = b1 * mul1 + add1;
                         *reinterpret_cast<uint2 *>(q) = key;
+                        if (decltype(sampled)::value) {
+                            // (the label channel still holds its background-style key here; the
+                            // sample only matters for classes that have no label pixel at all)
+                            const uint32_t v = __reduce_min_sync(0xffffffffu, min(key.x, key.y));
+                            if (lane == 0) atomicMin(&blk_min[j], v);
+                        }
                     }
-                }
+                };
+                if ((t % tiles_per_image) % kSampleEvery == 0) key_sweep(std::true_type{});
+                else key_sweep(std::false_type{});
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
+                    uint32_t kf = 0u;
                     if (lbi[i] >= 0) {
                         const float err = fmaxf(1.f - e_lb[i] * (i ? inv.y : inv.x), 0.f);
                         const uint32_t eb = min(__float_as_uint(err), kOneBits);
-                        reinterpret_cast<uint32_t *>(mine)[lbi[i] * kPairTP + i] = ((kOneBits - eb) << 1) | 1u;
+                        kf = ((kOneBits - eb) << 1) | 1u;
+                        reinterpret_cast<uint32_t *>(mine)[lbi[i] * kPairTP + i] = kf;
                     }
+                    track_fg(blk_maxfg, lbi[i], kf, lane);
                 }
             } else {
                 float *jmine = reinterpret_cast<float *>(stage + lay.tile_bytes) + bxo;
@@ -486,6 +561,7 @@ lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUten
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.ready[s]);
         }
+        if (!BWD && cur_n >= 0) flush_trackers(cur_n);
     }
 }
 
@@ -507,12 +583,15 @@ __device__ __forceinline__ bool key_is_fg(uint32_t key) { return (key & 1u) && k
 template <bool LAST>
 __global__ void __launch_bounds__(kSortThreads)
 sort_hist_kernel(const uint32_t *__restrict__ keys, uint32_t *__restrict__ hist,
-                 uint32_t *__restrict__ fghist, int64_t L, int64_t T, int shift) {
+                 uint32_t *__restrict__ fghist, const uint32_t *__restrict__ Lp, int64_t L, int64_t T,
+                 int GY, int shift) {
     __shared__ uint32_t sh[kBins];
     __shared__ uint32_t shfg[LAST ? kBins : 1];
-    const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
+    const int64_t seg = blockIdx.x / GY;
+    const int64_t Lk = __ldg(Lp + seg);                 // kept elements of the segment
+  for (int64_t tile = blockIdx.x % GY; tile * kSortTile < Lk; tile += GY) {
     const int64_t t0 = tile * kSortTile;
-    const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
+    const int n = int(Lk - t0 < kSortTile ? Lk - t0 : kSortTile);
     const uint32_t *src = keys + seg * L + t0;
     for (int b = threadIdx.x; b < kBins; b += kSortThreads) {
         sh[b] = 0;
@@ -542,6 +621,8 @@ sort_hist_kernel(const uint32_t *__restrict__ keys, uint32_t *__restrict__ hist,
         hist[o + b] = sh[b];
         if (LAST) fghist[o + b] = shfg[b];
     }
+    __syncthreads();
+  }
 }
 
 // Exclusive scan of kBins per-thread values across a block of kBins threads.
@@ -577,24 +658,130 @@ __device__ __forceinline__ uint32_t block_excl_scan_1024(uint32_t v, uint32_t *w
 template <bool LAST>
 __global__ void __launch_bounds__(kBins)
 sort_scan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fghist,
-                 uint32_t *__restrict__ n_pos, int64_t T) {
+                 uint32_t *__restrict__ n_pos, const uint32_t *__restrict__ Lp, int64_t T) {
     __shared__ uint32_t warp_tot[32];
     __shared__ uint32_t grand;
     const int64_t seg = blockIdx.x;
     const int b = threadIdx.x;
+    const int64_t Tk = (int64_t(__ldg(Lp + seg)) + kSortTile - 1) / kSortTile;   // tiles in use
 #pragma unroll
     for (int which = 0; which < (LAST ? 2 : 1); ++which) {
         uint32_t *h = (which ? fghist : hist) + seg * T * kBins;
         uint32_t total = 0;
-        for (int64_t t = 0; t < T; ++t) total += h[t * kBins + b];
+        for (int64_t t = 0; t < Tk; ++t) total += h[t * kBins + b];
         uint32_t run = block_excl_scan_1024(total, warp_tot, &grand);
-        for (int64_t t = 0; t < T; ++t) {
+        for (int64_t t = 0; t < Tk; ++t) {
             const uint32_t c = h[t * kBins + b];
             h[t * kBins + b] = run;
             run += c;
         }
         if (which && b == 0) n_pos[seg] = grand;
         __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------ pruning
+//
+// Elements past the pruning bound (see track_fg) are dropped before the sort: a count per
+// sort tile, a scan per segment, and a stable compaction that also writes the dropped
+// elements' dJ (zero).  The sort then runs on the kept elements only (Lp per segment).
+
+__device__ __forceinline__ uint32_t prune_limit(const uint32_t *maxfg, const uint32_t *minkey, int64_t seg,
+                                                int prune) {
+    if (!prune) return 0x80000000u;                       // keep everything, ignored pixels included
+    const uint32_t mf = __ldg(maxfg + seg);
+    if (mf) return (mf >> 1) + 1u;                        // up to the last foreground element (ties too)
+    const uint32_t mk = __ldg(minkey + seg);
+    return mk != kKeyIgnored ? (mk >> 1) + 1u : 0x80000000u;
+}
+
+// kept[seg][tile] = number of elements of the tile with (key >> 1) < limit.
+__global__ void __launch_bounds__(kSortThreads)
+prune_count_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict__ maxfg,
+                   const uint32_t *__restrict__ minkey, uint32_t *__restrict__ kept, int64_t L, int64_t T,
+                   int prune) {
+    __shared__ uint32_t wsum[kSortWarps];
+    const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
+    const uint32_t limit = prune_limit(maxfg, minkey, seg, prune);
+    const int64_t t0 = tile * kSortTile;
+    const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
+    const uint32_t *src = keys + seg * L + t0;
+    uint32_t c = 0;
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = r * kSortThreads + threadIdx.x;
+        if (idx < n) c += (__ldg(src + idx) >> 1) < limit ? 1u : 0u;
+    }
+    c = __reduce_add_sync(0xffffffffu, c);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t tot = 0;
+        for (int w = 0; w < kSortWarps; ++w) tot += wsum[w];
+        kept[seg * T + tile] = tot;
+    }
+}
+
+// kept[seg][*] -> exclusive offsets, Lp[seg] = total.  One block of kBins threads per segment.
+__global__ void __launch_bounds__(kBins)
+prune_scan_kernel(uint32_t *__restrict__ kept, uint32_t *__restrict__ Lp, int64_t T) {
+    __shared__ uint32_t warp_tot[32];
+    __shared__ uint32_t grand;
+    const int64_t seg = blockIdx.x;
+    uint32_t carry = 0;
+    for (int64_t base = 0; base < T; base += kBins) {
+        const int64_t t = base + threadIdx.x;
+        const uint32_t v = t < T ? kept[seg * T + t] : 0u;
+        const uint32_t ex = block_excl_scan_1024(v, warp_tot, &grand);
+        if (t < T) kept[seg * T + t] = carry + ex;
+        carry += grand;
+    }
+    if (threadIdx.x == 0) Lp[seg] = carry;
+}
+
+// Kept (key, position) pairs of a tile, in order, to offsets[seg][tile]...; dJ = 0 everywhere
+// (the Jaccard kernel overwrites the kept ones).
+__global__ void __launch_bounds__(kSortThreads)
+prune_compact_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict__ maxfg,
+                     const uint32_t *__restrict__ minkey, const uint32_t *__restrict__ offsets,
+                     uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
+                     float *__restrict__ jacc, int64_t L, int64_t T, int prune) {
+    __shared__ uint32_t wtot[kSortWarps];
+    const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
+    const uint32_t limit = prune_limit(maxfg, minkey, seg, prune);
+    const int64_t t0 = tile * kSortTile;
+    const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
+    const int64_t sbase = seg * L;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wbase = warp * (32 * kSortItems);
+    const uint32_t lt = lanemask_lt();
+    uint32_t key[kSortItems];
+    uint32_t keepbits = 0;                       // bit r: my element of round r stays
+    uint32_t wc = 0;
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = wbase + r * 32 + lane;
+        key[r] = idx < n ? __ldg(keys + sbase + t0 + idx) : kKeyIgnored;
+        if (idx < n) jacc[sbase + t0 + idx] = 0.f;
+        if (idx < n && (key[r] >> 1) < limit) keepbits |= 1u << r;
+    }
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) wc += __popc(__ballot_sync(0xffffffffu, (keepbits >> r) & 1u));
+    if (lane == 0) wtot[warp] = wc;
+    __syncthreads();
+    uint32_t base = __ldg(offsets + seg * T + tile);
+    for (int w = 0; w < warp; ++w) base += wtot[w];
+    if (wc == 0) return;
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const bool keep = (keepbits >> r) & 1u;
+        const uint32_t m = __ballot_sync(0xffffffffu, keep);
+        if (keep) {
+            const uint32_t pos = base + __popc(m & lt);
+            keys_out[sbase + pos] = key[r];
+            vals_out[sbase + pos] = uint32_t(t0 + wbase + r * 32 + lane);
+        }
+        base += __popc(m);
     }
 }
 
@@ -648,7 +835,8 @@ __device__ __forceinline__ uint32_t rank_round(uint32_t d, uint32_t * /*unused*/
 __global__ void __launch_bounds__(kScatThreads, 2)
 sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__restrict__ vals_in,
                     uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
-                    const uint32_t *__restrict__ offsets, int64_t L, int64_t T, int shift) {
+                    const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ Lp, int64_t L,
+                    int64_t T, int GY, int shift) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t *match = reinterpret_cast<uint32_t *>(smem_raw);
     uint32_t *bufv = match;                                                  // after ranking
@@ -658,12 +846,16 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
     uint32_t *goff = binstart + kBins;
     __shared__ uint32_t warp_tot[32];
 
-    const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
-    const int64_t t0 = tile * kSortTile;
-    const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
+    const int64_t seg = blockIdx.x / GY;
+    const int64_t Lk = __ldg(Lp + seg);
     const int64_t sbase = seg * L;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wbase = warp * (32 * kScatItems);
+  // (a block that takes several tiles: the barrier after the key loads also separates the
+  // previous tile's write-out from this tile's first shared-memory writes that alias it)
+  for (int64_t tile = blockIdx.x % GY; tile * kSortTile < Lk; tile += GY) {
+    const int64_t t0 = tile * kSortTile;
+    const int n = int(Lk - t0 < kSortTile ? Lk - t0 : kSortTile);
 
     for (int i = tid; i < int(kScatCntBytes / 4); i += kScatThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
     uint32_t key[kScatItems];
@@ -769,6 +961,7 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
         keys_out[sbase + gp] = k;
         vals_out[sbase + gp] = bufv[i];
     }
+  }
 }
 
 // Last pass, fused with the Jaccard step.  Nothing is moved: the final rank of an element is
@@ -780,7 +973,8 @@ __global__ void __launch_bounds__(kSortThreads, 2)
 rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals,
                     const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ fgoffsets,
                     const uint32_t *__restrict__ n_pos_seg, float *__restrict__ jacc,
-                    double *__restrict__ partial, int64_t L, int64_t T, int shift) {
+                    double *__restrict__ partial, const uint32_t *__restrict__ Lp, int64_t L, int64_t T,
+                    int GY, int shift) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t *match = reinterpret_cast<uint32_t *>(smem_raw);
     uint16_t *wcnt_all = reinterpret_cast<uint16_t *>(smem_raw + kMatchBytes);
@@ -790,12 +984,14 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
     uint32_t *keybuf = fgoff + kBins;                  // [kSortTile] keys of the tile
     __shared__ double sh_d[32];
 
-    const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
-    const int64_t t0 = tile * kSortTile;
-    const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
+    const int64_t seg = blockIdx.x / GY;
+    const int64_t Lk = __ldg(Lp + seg);
     const int64_t sbase = seg * L;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wbase = warp * (32 * kSortItems);
+  for (int64_t tile = blockIdx.x % GY; tile * kSortTile < Lk; tile += GY) {
+    const int64_t t0 = tile * kSortTile;
+    const int n = int(Lk - t0 < kSortTile ? Lk - t0 : kSortTile);
 
     for (int i = tid; i < int(2 * kCntBytes / 4); i += kSortThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
     {
@@ -895,14 +1091,18 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
         for (int w = 0; w < kSortWarps; ++w) s += sh_d[w];
         partial[seg * T + tile] = s;
     }
+    __syncthreads();
+  }
 }
 
 // loss[seg] = sum of the segment's tile partials, fixed order.
 __global__ void __launch_bounds__(32)
-loss_kernel(const double *__restrict__ partial, float *__restrict__ loss, int64_t T) {
+loss_kernel(const double *__restrict__ partial, float *__restrict__ loss, const uint32_t *__restrict__ Lp,
+            int64_t T) {
     const int64_t seg = blockIdx.x;
+    const int64_t Tk = (int64_t(__ldg(Lp + seg)) + kSortTile - 1) / kSortTile;
     double s = 0.0;
-    for (int64_t t = threadIdx.x; t < T; t += 32) s += partial[seg * T + t];
+    for (int64_t t = threadIdx.x; t < Tk; t += 32) s += partial[seg * T + t];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if (threadIdx.x == 0) loss[seg] = float(s);
@@ -1046,12 +1246,18 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
         return B200_ERR_UNSUPPORTED;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(w.status, 0, 256, s) != cudaSuccess) return launch_status("lovasz status memset");
+    // status word and the foreground trackers start at 0, the smallest-key samples at all ones
+    if (cudaMemsetAsync(w.status, 0, reinterpret_cast<char *>(w.minkey) - reinterpret_cast<char *>(w.status), s) !=
+            cudaSuccess ||
+        cudaMemsetAsync(w.minkey, 0xFF, size_t(g.S) * 4, s) != cudaSuccess)
+        return launch_status("lovasz workspace memset");
 
     TileArgs ta{};
     ta.logits = static_cast<const float *>(logits);
     ta.labels = labels;
     ta.keys = w.keysA;
+    ta.maxfg = w.maxfg;
+    ta.minkey = w.minkey;
     ta.status = w.status;
     ta.ignore = ignore_index;
     ta.g = g;
@@ -1062,17 +1268,35 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
         cudaFuncSetAttribute(rank_jaccard_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              int(kJaccardSmem)) != cudaSuccess)
         return launch_status("cudaFuncSetAttribute(lovasz sort kernels)");
-    const unsigned nblk = unsigned(g.S * g.T);
-    const uint32_t *kin = w.keysA;
-    const uint32_t *vin = nullptr;
-    uint32_t *kout = w.keysB, *vout = w.valsB;
+    // drop the elements past the pruning bound
+    const unsigned nblk_all = unsigned(g.S * g.T);
+    const int prune = env_int("B200_LOVASZ_NO_PRUNE", 0) ? 0 : 1;
+    prune_count_kernel<<<nblk_all, kSortThreads, 0, s>>>(w.keysA, w.maxfg, w.minkey, w.kept, g.L, g.T, prune);
+    if ((rc = launch_status("lovasz prune count launch")) != B200_OK) return rc;
+    prune_scan_kernel<<<unsigned(g.S), kBins, 0, s>>>(w.kept, w.Lp, g.T);
+    if ((rc = launch_status("lovasz prune scan launch")) != B200_OK) return rc;
+    prune_compact_kernel<<<nblk_all, kSortThreads, 0, s>>>(w.keysA, w.maxfg, w.minkey, w.kept, w.keysB, w.valsB,
+                                                           jacc, g.L, g.T, prune);
+    if ((rc = launch_status("lovasz prune compact launch")) != B200_OK) return rc;
+
+    // The number of kept elements is known on the device only: every segment gets GY blocks,
+    // each striding over the tiles its segment turns out to have.
+    int64_t gy = (int64_t(sm_count()) * 16 + g.S - 1) / g.S;
+    if (gy > g.T) gy = g.T;
+    if (gy < 1) gy = 1;
+    const int GY = int(gy);
+    const unsigned nblk = unsigned(g.S * gy);
+    const uint32_t *kin = w.keysB;
+    const uint32_t *vin = w.valsB;
+    uint32_t *kout = w.keysA, *vout = w.valsA;
     for (int pass = 0; pass < kPasses - 1; ++pass) {
         const int shift = 1 + pass * kBits;
-        sort_hist_kernel<false><<<nblk, kSortThreads, 0, s>>>(kin, w.hist, nullptr, g.L, g.T, shift);
+        sort_hist_kernel<false><<<nblk, kSortThreads, 0, s>>>(kin, w.hist, nullptr, w.Lp, g.L, g.T, GY, shift);
         if ((rc = launch_status("lovasz sort histogram launch")) != B200_OK) return rc;
-        sort_scan_kernel<false><<<unsigned(g.S), kBins, 0, s>>>(w.hist, nullptr, nullptr, g.T);
+        sort_scan_kernel<false><<<unsigned(g.S), kBins, 0, s>>>(w.hist, nullptr, nullptr, w.Lp, g.T);
         if ((rc = launch_status("lovasz sort scan launch")) != B200_OK) return rc;
-        sort_scatter_kernel<<<nblk, kScatThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, g.L, g.T, shift);
+        sort_scatter_kernel<<<nblk, kScatThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, w.Lp, g.L, g.T,
+                                                                     GY, shift);
         if ((rc = launch_status("lovasz sort scatter launch")) != B200_OK) return rc;
         kin = kout;
         vin = vout;
@@ -1080,15 +1304,15 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
     }
     {
         const int shift = 1 + (kPasses - 1) * kBits;
-        sort_hist_kernel<true><<<nblk, kSortThreads, 0, s>>>(kin, w.hist, w.fghist, g.L, g.T, shift);
+        sort_hist_kernel<true><<<nblk, kSortThreads, 0, s>>>(kin, w.hist, w.fghist, w.Lp, g.L, g.T, GY, shift);
         if ((rc = launch_status("lovasz last histogram launch")) != B200_OK) return rc;
-        sort_scan_kernel<true><<<unsigned(g.S), kBins, 0, s>>>(w.hist, w.fghist, w.n_pos, g.T);
+        sort_scan_kernel<true><<<unsigned(g.S), kBins, 0, s>>>(w.hist, w.fghist, w.n_pos, w.Lp, g.T);
         if ((rc = launch_status("lovasz last scan launch")) != B200_OK) return rc;
         rank_jaccard_kernel<<<nblk, kSortThreads, kJaccardSmem, s>>>(kin, vin, w.hist, w.fghist, w.n_pos, jacc,
-                                                                      w.partial, g.L, g.T, shift);
+                                                                      w.partial, w.Lp, g.L, g.T, GY, shift);
         if ((rc = launch_status("lovasz rank+jaccard launch")) != B200_OK) return rc;
     }
-    loss_kernel<<<unsigned(g.S), 32, 0, s>>>(w.partial, loss, g.T);
+    loss_kernel<<<unsigned(g.S), 32, 0, s>>>(w.partial, loss, w.Lp, g.T);
     return launch_status("lovasz loss launch");
 }
 

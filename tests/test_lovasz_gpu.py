@@ -72,6 +72,41 @@ def test_multi_tile_segments_and_blocky_labels():
         assert_grad_close(grad, want_grad.float())
 
 
+def test_pruned_sort_cases(monkeypatch):
+    """The sort drops elements past the last foreground element of their class (their dJ is exactly
+    zero).  Cases that move that bound around: classes absent from some or all images, a saturated
+    foreground pixel (error 0: nothing can be dropped), an image that is ignored entirely, and the
+    unpruned path as a cross-check."""
+    import pytorch_loss as P
+    from oracle import losses as O
+    g = torch.Generator().manual_seed(2024)
+    n, c, h, w = 3, 7, 48, 44                                       # 2112 pixels per image: pipelined tiles
+    base = torch.randn(n, c, h, w, generator=g)
+    lab_few = torch.randint(0, 2, (n, h, w), generator=g)           # classes 2..6 absent everywhere
+    lab_mixed = labels_with_ignores(g, (n, h, w), c, 255, 0.2)
+    lab_mixed[1] = 255                                              # one image ignored entirely
+    lab_mixed[2][lab_mixed[2] == 3] = 4                             # class 3 absent from image 2 only
+    saturated = base.clone()
+    saturated[0, :, 0, 0] = -40.0
+    saturated[0, int(lab_mixed[0, 0, 0]) if lab_mixed[0, 0, 0] != 255 else 0, 0, 0] = 40.0
+    lab_sat = lab_mixed.clone()
+    if lab_sat[0, 0, 0] == 255:
+        lab_sat[0, 0, 0] = 0
+    cases = [(base, lab_few), (base * 6.0, lab_mixed), (saturated, lab_sat)]
+    for logits, labels in cases:
+        for per_image in (False, True):
+            want_loss, want_grad = O.lovasz_softmax(logits, labels, 255, 'none', per_image, dtype=torch.float64)
+            crit = P.LovaszSoftmaxV3('none', 255, per_image=per_image)
+            loss, grad = run_module(crit, logits.cuda(), labels.cuda())
+            assert_loss_close(loss, want_loss.float(), atol=1e-6)
+            assert_grad_close(grad, want_grad.float())
+            monkeypatch.setenv("B200_LOVASZ_NO_PRUNE", "1")
+            loss_full, grad_full = run_module(crit, logits.cuda(), labels.cuda())
+            monkeypatch.delenv("B200_LOVASZ_NO_PRUNE")
+            assert_loss_close(loss_full, loss, atol=1e-6)
+            assert torch.equal(grad_full, grad)                     # same ranks, same dJ, same gradient
+
+
 def test_sorted_order_properties():
     """Size-independent checks on the raw C-ABI outputs: per segment the Jaccard gradients
     are non-negative and sum to 1 (J runs from 0 to 1) and the loss lies in [0, 1]."""
