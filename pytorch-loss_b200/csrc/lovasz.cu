@@ -13,12 +13,22 @@
 //   keys     one tile kernel (TMA in, TMA out): softmax, then a 32-bit key per (pixel, class)
 //            key = ((0x3F800000 - bits(err)) << 1) | fg  -> ascending key order = descending err,
 //            ignored pixels get 0xFFFFFFFF.  err is in [0, 1] so 30 key bits carry it exactly.
-//   sort     segmented LSD radix sort of (key, pixel index) pairs on key bits 1..30, kBits per
-//            pass.  Each pass: per-tile digit histogram -> per-segment scan -> stable scatter.
-//            The scatter ranks with warp match-any + per-warp counters, reorders the tile in
-//            shared memory and writes each digit's run contiguously.  No kernel waits on another.
-//   jaccard  one pass over the sorted pairs: integer prefix count of fg (tile counts come from
-//            atomics in the last scatter), dJ from the integer counts
+//            The kernel also tracks, per segment, the largest foreground key and a sample of
+//            the smallest keys (see track_fg).
+//   prune    everything after the last foreground element of a segment in sorted order has
+//            dJ = 0 exactly, so only elements with key <= that foreground key are sorted:
+//            count per tile -> scan -> stable compaction of (key, pixel index), dJ = 0 written
+//            for the rest.  A segment that would keep more than 3/4 is sorted from the full
+//            array instead (`direct`).  What is kept depends on the data: ~7% for random
+//            logits over 19 classes, everything when some foreground pixel has error 0.
+//   sort     segmented LSD radix sort of the kept (key, pixel index) pairs on key bits 1..30,
+//            kBits per pass.  Each pass: per-tile digit histogram -> per-segment scan ->
+//            stable scatter.  The scatter ranks with kBits ballots per round + per-warp
+//            counters, reorders the tile in shared memory and writes each digit's run
+//            contiguously.  The kept counts exist on the device only: the kernels run over a
+//            device-built list of tiles in use.  No kernel waits on another.
+//   jaccard  the last pass ranks in place: integer prefix count of fg (from a foreground
+//            histogram), dJ from the integer counts
 //                fg step: dJ = 1/U,   bg step: dJ = I/(U*(U+1)),   U = 0 (no fg, first) -> 1
 //            with I = remaining fg, U = union before the step; accumulates err*dJ and scatters
 //            dJ to pixel order (the `jacc` output).
@@ -27,6 +37,7 @@
 #include "pipeline.cuh"
 
 #include <cstdlib>
+#include <utility>
 #include <type_traits>
 
 namespace b200 {
@@ -73,7 +84,10 @@ struct Workspace {
     uint32_t *maxfg;      // [S]  largest foreground key seen (0: none)
     uint32_t *minkey;     // [S]  smallest key among the sampled tiles (0xFFFFFFFF: none)
     uint32_t *kept;       // [S][T] kept elements per tile -> exclusive offsets
-    uint32_t *Lp;         // [S]  kept elements of the segment
+    uint32_t *Lp;         // [S]  elements of the segment that go through the sort
+    uint32_t *direct;     // [S]  1: the segment is sorted from the full key array (not compacted)
+    uint2 *tilemap;       // [S*T] (segment, tile) of every sort tile in use, segment-major
+    uint32_t *n_tiles;    // 1 word: sort tiles in use
     size_t bytes;
 };
 
@@ -94,6 +108,9 @@ Workspace carve(void *base, const LovaszGeom &g) {
     w.minkey = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
     w.kept = reinterpret_cast<uint32_t *>(take(size_t(g.S) * g.T * 4));
     w.Lp = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
+    w.direct = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
+    w.tilemap = reinterpret_cast<uint2 *>(take(size_t(g.S) * g.T * 8));
+    w.n_tiles = reinterpret_cast<uint32_t *>(take(256));
     w.keysA = reinterpret_cast<uint32_t *>(take(e * 4));
     w.keysB = reinterpret_cast<uint32_t *>(take(e * 4));
     w.valsA = reinterpret_cast<uint32_t *>(take(e * 4));
@@ -577,22 +594,68 @@ __device__ __forceinline__ uint32_t digit_of(uint32_t key, int shift) {
 }
 __device__ __forceinline__ bool key_is_fg(uint32_t key) { return (key & 1u) && key != kKeyIgnored; }
 
+// One entry of the list of sort tiles in use: everything a block needs to start on the tile,
+// in one 8-byte load.   x = segment,   y = tile | (elements - 1) << 18 | direct << 31
+struct TileRef {
+    int64_t seg, tile;
+    int n;
+    bool direct;       // the segment was not compacted: its buffers are used in swapped roles
+};
+__device__ __forceinline__ uint2 encode_tile(uint32_t seg, uint32_t tile, uint32_t n, bool direct) {
+    return make_uint2(seg, tile | ((n - 1u) << 18) | (direct ? 0x80000000u : 0u));
+}
+__device__ __forceinline__ TileRef decode_tile(uint2 e) {
+    TileRef t;
+    t.seg = e.x;
+    t.tile = e.y & 0x3FFFFu;
+    t.n = int((e.y >> 18) & 0x1FFFu) + 1;
+    t.direct = (e.y >> 31) != 0u;
+    return t;
+}
+// The block's next tile: thread 0 draws a ticket while the tile's key loads are in flight, and
+// later pulls the list entry into L2, so the next iteration starts without a chain of misses.
+__device__ __forceinline__ void draw_next_tile(uint32_t *next, unsigned *ticket) {
+    if (threadIdx.x == 0) *next = gridDim.x + atomicAdd(ticket, 1u);
+}
+__device__ __forceinline__ void prefetch_next_tile(const uint32_t *next, const uint2 *tilemap, uint32_t total) {
+    if (threadIdx.x == 0) {
+        const uint32_t w = *next;
+        if (w < total) asm volatile("prefetch.global.L2 [%0];" ::"l"(tilemap + w));
+    }
+}
+
+// Elements with (key >> 1) >= the segment's limit are past the pruning bound (see track_fg):
+// the first sort pass drops them.
+__device__ __forceinline__ uint32_t prune_limit(const uint32_t *maxfg, const uint32_t *minkey, int64_t seg,
+                                                int prune) {
+    if (!prune) return 0x80000000u;                       // keep everything, ignored pixels included
+    const uint32_t mf = __ldg(maxfg + seg);
+    if (mf) return (mf >> 1) + 1u;                        // up to the last foreground element (ties too)
+    const uint32_t mk = __ldg(minkey + seg);
+    return mk != kKeyIgnored ? (mk >> 1) + 1u : 0x80000000u;
+}
+
 // Per-tile digit histogram (plain shared-memory atomics: cost follows the multiplicity of a
 // digit inside a warp, which is low for the uniform low digits and bounded by 32 otherwise).
 // LAST: also a histogram of the foreground elements.   hist[seg][tile][bin]
+// Segments flagged in `direct` (sorted from the full array) use the two buffers in swapped roles:
+// their input of this pass is keys_alt.
 template <bool LAST>
 __global__ void __launch_bounds__(kSortThreads)
 sort_hist_kernel(const uint32_t *__restrict__ keys, uint32_t *__restrict__ hist,
-                 uint32_t *__restrict__ fghist, const uint32_t *__restrict__ Lp, int64_t L, int64_t T,
-                 int GY, int shift) {
+                 uint32_t *__restrict__ fghist, const uint32_t *__restrict__ Lp,
+                 const uint2 *__restrict__ tilemap, const uint32_t *__restrict__ n_tiles,
+                 const uint32_t *__restrict__ keys_alt, const uint32_t *__restrict__ direct, int64_t L, int64_t T,
+                 int shift) {
     __shared__ uint32_t sh[kBins];
     __shared__ uint32_t shfg[LAST ? kBins : 1];
-    const int64_t seg = blockIdx.x / GY;
-    const int64_t Lk = __ldg(Lp + seg);                 // kept elements of the segment
-  for (int64_t tile = blockIdx.x % GY; tile * kSortTile < Lk; tile += GY) {
+    const uint32_t total = __ldg(n_tiles);
+  for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
+    const TileRef tr = decode_tile(__ldg(tilemap + w));
+    const int64_t seg = tr.seg, tile = tr.tile;
     const int64_t t0 = tile * kSortTile;
-    const int n = int(Lk - t0 < kSortTile ? Lk - t0 : kSortTile);
-    const uint32_t *src = keys + seg * L + t0;
+    const int n = tr.n;
+    const uint32_t *src = (tr.direct ? keys_alt : keys) + seg * L + t0;
     for (int b = threadIdx.x; b < kBins; b += kSortThreads) {
         sh[b] = 0;
         if (LAST) shfg[b] = 0;
@@ -686,15 +749,6 @@ sort_scan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fghist,
 // sort tile, a scan per segment, and a stable compaction that also writes the dropped
 // elements' dJ (zero).  The sort then runs on the kept elements only (Lp per segment).
 
-__device__ __forceinline__ uint32_t prune_limit(const uint32_t *maxfg, const uint32_t *minkey, int64_t seg,
-                                                int prune) {
-    if (!prune) return 0x80000000u;                       // keep everything, ignored pixels included
-    const uint32_t mf = __ldg(maxfg + seg);
-    if (mf) return (mf >> 1) + 1u;                        // up to the last foreground element (ties too)
-    const uint32_t mk = __ldg(minkey + seg);
-    return mk != kKeyIgnored ? (mk >> 1) + 1u : 0x80000000u;
-}
-
 // kept[seg][tile] = number of elements of the tile with (key >> 1) < limit.
 __global__ void __launch_bounds__(kSortThreads)
 prune_count_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict__ maxfg,
@@ -723,8 +777,12 @@ prune_count_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict
 }
 
 // kept[seg][*] -> exclusive offsets, Lp[seg] = total.  One block of kBins threads per segment.
+// A segment that keeps more than 3/4 of its elements is not worth compacting: it is flagged
+// `direct`, Lp = L, and the first sort pass reads it from the full array (the ignored pixels'
+// keys sort last and the Jaccard kernel passes over them).
 __global__ void __launch_bounds__(kBins)
-prune_scan_kernel(uint32_t *__restrict__ kept, uint32_t *__restrict__ Lp, int64_t T) {
+prune_scan_kernel(uint32_t *__restrict__ kept, uint32_t *__restrict__ Lp, uint32_t *__restrict__ direct,
+                  int64_t L, int64_t T) {
     __shared__ uint32_t warp_tot[32];
     __shared__ uint32_t grand;
     const int64_t seg = blockIdx.x;
@@ -736,7 +794,11 @@ prune_scan_kernel(uint32_t *__restrict__ kept, uint32_t *__restrict__ Lp, int64_
         if (t < T) kept[seg * T + t] = carry + ex;
         carry += grand;
     }
-    if (threadIdx.x == 0) Lp[seg] = carry;
+    if (threadIdx.x == 0) {
+        const bool d = int64_t(carry) * 4 > L * 3;
+        Lp[seg] = d ? uint32_t(L) : carry;
+        direct[seg] = d ? 1u : 0u;
+    }
 }
 
 // Kept (key, position) pairs of a tile, in order, to offsets[seg][tile]...; dJ = 0 everywhere
@@ -744,10 +806,11 @@ prune_scan_kernel(uint32_t *__restrict__ kept, uint32_t *__restrict__ Lp, int64_
 __global__ void __launch_bounds__(kSortThreads)
 prune_compact_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict__ maxfg,
                      const uint32_t *__restrict__ minkey, const uint32_t *__restrict__ offsets,
-                     uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
-                     float *__restrict__ jacc, int64_t L, int64_t T, int prune) {
+                     const uint32_t *__restrict__ direct, uint32_t *__restrict__ keys_out,
+                     uint32_t *__restrict__ vals_out, float *__restrict__ jacc, int64_t L, int64_t T, int prune) {
     __shared__ uint32_t wtot[kSortWarps];
     const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
+    if (__ldg(direct + seg)) return;
     const uint32_t limit = prune_limit(maxfg, minkey, seg, prune);
     const int64_t t0 = tile * kSortTile;
     const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
@@ -763,6 +826,10 @@ prune_compact_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restri
         const int idx = wbase + r * 32 + lane;
         key[r] = idx < n ? __ldg(keys + sbase + t0 + idx) : kKeyIgnored;
         if (idx < n) jacc[sbase + t0 + idx] = 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < kSortItems; ++r) {
+        const int idx = wbase + r * 32 + lane;
         if (idx < n && (key[r] >> 1) < limit) keepbits |= 1u << r;
     }
 #pragma unroll
@@ -783,6 +850,32 @@ prune_compact_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restri
         }
         base += __popc(m);
     }
+}
+
+// The sort tiles in use, listed segment by segment (entries: encode_tile).  The kept
+// counts exist on the device only, so the sort kernels run a fixed grid whose blocks stride
+// over this list.  One block per segment; it finds its first slot by adding up the tiles of
+// the segments before it.
+__global__ void __launch_bounds__(256)
+tile_map_kernel(const uint32_t *__restrict__ Lp, const uint32_t *__restrict__ direct,
+                uint2 *__restrict__ tilemap, uint32_t *__restrict__ n_tiles, int64_t S) {
+    __shared__ uint32_t wsum[8];
+    const int64_t seg = blockIdx.x;
+    uint32_t before = 0;
+    for (int64_t q = threadIdx.x; q < seg; q += 256) before += (__ldg(Lp + q) + kSortTile - 1) / kSortTile;
+    before = __reduce_add_sync(0xffffffffu, before);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = before;
+    __syncthreads();
+    uint32_t first = 0;
+    for (int w = 0; w < 8; ++w) first += wsum[w];
+    const uint32_t Lk = __ldg(Lp + seg);
+    const uint32_t mine = (Lk + kSortTile - 1) / kSortTile;
+    const bool d = __ldg(direct + seg) != 0u;
+    for (uint32_t t = threadIdx.x; t < mine; t += 256) {
+        const uint32_t left = Lk - t * kSortTile;
+        tilemap[first + t] = encode_tile(uint32_t(seg), t, left < kSortTile ? left : uint32_t(kSortTile), d);
+    }
+    if (seg == S - 1 && threadIdx.x == 0) *n_tiles = first + mine;
 }
 
 // Shared-memory layout of the two ranking kernels.
@@ -830,56 +923,59 @@ __device__ __forceinline__ uint32_t rank_round(uint32_t d, uint32_t * /*unused*/
     return old + __popc(peers & lt);
 }
 
-// Stable scatter of one tile (passes that are not the last).  vals_in == nullptr: values are
-// the positions inside the segment (first pass).
-__global__ void __launch_bounds__(kScatThreads, 2)
-sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__restrict__ vals_in,
-                    uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
-                    const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ Lp, int64_t L,
-                    int64_t T, int GY, int shift) {
+// Stable scatter of one tile (passes that are not the last).  kin / vin point at the tile,
+// kout / vout at the segment, off at the tile's row of scanned offsets.  vin == nullptr: the
+// values are the positions pos0 + index (a segment that was not compacted, first pass).
+//
+// The n elements are dealt to the warps in contiguous chunks of R rounds of 32
+// (R = ceil(n / 512), at most kScatItems), so (warp, round, lane) order equals array order
+// and a partly filled tile skips the rounds it does not need.
+template <bool FULL>      // FULL: a tile of exactly kSortTile elements -- straight-line code, no round tests
+__device__ __forceinline__ void scatter_tile(const uint32_t *__restrict__ kin, const uint32_t *__restrict__ vin,
+                                             uint32_t *__restrict__ kout, uint32_t *__restrict__ vout,
+                                             const uint32_t *__restrict__ off, int n, int shift, uint32_t pos0,
+                                             uint32_t *next, unsigned *ticket, const uint2 *tilemap,
+                                             const uint32_t *n_tiles) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint32_t *match = reinterpret_cast<uint32_t *>(smem_raw);
-    uint32_t *bufv = match;                                                  // after ranking
+    uint32_t *bufv = reinterpret_cast<uint32_t *>(smem_raw);
     uint32_t *bufk = reinterpret_cast<uint32_t *>(smem_raw + kTileWordsBytes);
     uint16_t *wcnt_all = reinterpret_cast<uint16_t *>(smem_raw + 2 * kTileWordsBytes);
     uint32_t *binstart = reinterpret_cast<uint32_t *>(smem_raw + 2 * kTileWordsBytes + kScatCntBytes);
     uint32_t *goff = binstart + kBins;
     __shared__ uint32_t warp_tot[32];
-
-    const int64_t seg = blockIdx.x / GY;
-    const int64_t Lk = __ldg(Lp + seg);
-    const int64_t sbase = seg * L;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int wbase = warp * (32 * kScatItems);
-  // (a block that takes several tiles: the barrier after the key loads also separates the
-  // previous tile's write-out from this tile's first shared-memory writes that alias it)
-  for (int64_t tile = blockIdx.x % GY; tile * kSortTile < Lk; tile += GY) {
-    const int64_t t0 = tile * kSortTile;
-    const int n = int(Lk - t0 < kSortTile ? Lk - t0 : kSortTile);
+    const uint32_t lt = lanemask_lt();
 
     for (int i = tid; i < int(kScatCntBytes / 4); i += kScatThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
     uint32_t key[kScatItems];
+    const int cnt = n;
+    const int R = FULL ? kScatItems : (cnt + kScatThreads - 1) / kScatThreads;      // rounds in use
+    const int wbase = warp * (32 * R);
 #pragma unroll
     for (int r = 0; r < kScatItems; ++r) {
         const int idx = wbase + r * 32 + lane;
-        key[r] = idx < n ? __ldg(keys_in + sbase + t0 + idx) : 0xFFFFFFFFu;
+        key[r] = 0xFFFFFFFFu;
+        if (r < R && idx < cnt) key[r] = __ldg(kin + idx);
     }
+    draw_next_tile(next, ticket);
     __syncthreads();
     uint32_t rank2[kScatItems / 2];     // two 16-bit ranks per register
-    uint32_t *wmatch = match + warp * kBins;
     uint16_t *wcnt = wcnt_all + warp * kBins;
-    const uint32_t lt = lanemask_lt();
 #pragma unroll
     for (int r = 0; r < kScatItems; r += 2) {
-        uint32_t peers;
-        const uint32_t r0 = rank_round(digit_of(key[r], shift), wmatch, wcnt, lane, lt, peers);
-        const uint32_t r1 = rank_round(digit_of(key[r + 1], shift), wmatch, wcnt, lane, lt, peers);
-        rank2[r / 2] = r0 | (r1 << 16);
+        if (r < R) {
+            uint32_t peers;
+            const uint32_t r0 = rank_round(digit_of(key[r], shift), nullptr, wcnt, lane, lt, peers);
+            uint32_t r1 = 0;
+            if (r + 1 < R) r1 = rank_round(digit_of(key[r + 1], shift), nullptr, wcnt, lane, lt, peers);
+            rank2[r / 2] = r0 | (r1 << 16);
+        }
     }
     __syncthreads();
+    prefetch_next_tile(next, tilemap, __ldg(n_tiles));
     // per digit: exclusive prefix over warps (in place), then over digits
     constexpr int BPT = kBins / kScatThreads;
-    uint32_t cnt[BPT];
+    uint32_t cntb[BPT];
     uint32_t mine = 0;
 #pragma unroll
     for (int q = 0; q < BPT; ++q) {
@@ -891,7 +987,7 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
             wcnt_all[w * kBins + b] = uint16_t(run);
             run += c;
         }
-        cnt[q] = run;
+        cntb[q] = run;
         mine += run;
     }
     {
@@ -915,53 +1011,93 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
         }
         __syncthreads();
         uint32_t excl = warp_tot[warp] + incl - mine;
-        const uint32_t *off = offsets + (seg * T + tile) * kBins;
 #pragma unroll
         for (int q = 0; q < BPT; ++q) {
             const int b = BPT * tid + q;
             binstart[b] = excl;
             goff[b] = __ldg(off + b) - excl;
-            excl += cnt[q];
+            excl += cntb[q];
         }
     }
     __syncthreads();
     // local sorted position (kept in place of the rank); keys into the reorder buffer
 #pragma unroll
     for (int r = 0; r < kScatItems; ++r) {
-        const uint32_t d = digit_of(key[r], shift);
-        const uint32_t rk = (r & 1) ? (rank2[r / 2] >> 16) : (rank2[r / 2] & 0xffffu);
-        const uint32_t lp = binstart[d] + wcnt[d] + rk;
-        bufk[lp] = key[r];
-        rank2[r / 2] = (r & 1) ? ((rank2[r / 2] & 0xffffu) | (lp << 16)) : ((rank2[r / 2] & 0xffff0000u) | lp);
+        if (r < R) {
+            const uint32_t d = digit_of(key[r], shift);
+            const uint32_t rk = (r & 1) ? (rank2[r / 2] >> 16) : (rank2[r / 2] & 0xffffu);
+            const uint32_t lp = binstart[d] + wcnt[d] + rk;
+            bufk[lp] = key[r];
+            rank2[r / 2] = (r & 1) ? ((rank2[r / 2] & 0xffffu) | (lp << 16)) : ((rank2[r / 2] & 0xffff0000u) | lp);
+        }
     }
-    // values: all loads of a batch are issued before the first is used
-    constexpr int kBatch = 16;
+    // values: all loads are issued before the first is used
+    {
+        uint32_t v[kScatItems];
 #pragma unroll
-    for (int r0 = 0; r0 < kScatItems; r0 += kBatch) {
-        uint32_t v[kBatch];
-#pragma unroll
-        for (int r = 0; r < kBatch; ++r) {
-            const int idx = wbase + (r0 + r) * 32 + lane;
-            v[r] = uint32_t(t0 + idx);
-            if (vals_in && idx < n) v[r] = __ldg(vals_in + sbase + t0 + idx);
+        for (int r = 0; r < kScatItems; ++r) {
+            const int idx = wbase + r * 32 + lane;
+            v[r] = pos0 + uint32_t(idx);
+            if (vin && r < R && idx < cnt) v[r] = __ldg(vin + idx);
         }
 #pragma unroll
-        for (int r = 0; r < kBatch; ++r) {
-            const int rr = r0 + r;
-            const uint32_t lp = (rr & 1) ? (rank2[rr / 2] >> 16) : (rank2[rr / 2] & 0xffffu);
-            bufv[lp] = v[r];
+        for (int r = 0; r < kScatItems; ++r) {
+            if (r < R) {
+                const uint32_t lp = (r & 1) ? (rank2[r / 2] >> 16) : (rank2[r / 2] & 0xffffu);
+                bufv[lp] = v[r];
+            }
         }
     }
     __syncthreads();
     // each digit's run goes out contiguously
 #pragma unroll 4
-    for (int i = tid; i < n; i += kScatThreads) {
+    for (int i = tid; i < cnt; i += kScatThreads) {
         const uint32_t k = bufk[i];
         const uint32_t gp = goff[digit_of(k, shift)] + uint32_t(i);
-        keys_out[sbase + gp] = k;
-        vals_out[sbase + gp] = bufv[i];
+        kout[gp] = k;
+        vout[gp] = bufv[i];
     }
-  }
+}
+
+// The blocks take tiles from the list of sort tiles in use: the first by block index, the
+// following ones from a shared counter, so an uneven tile costs nobody a wait.  (The list
+// cursor lives in shared memory: the tile body needs all 64 registers of a thread.)
+// Segments flagged in `direct` were not compacted: they use the two buffer pairs in swapped
+// roles (segments occupy disjoint ranges of every buffer), and in the first pass their values
+// are their positions.
+__global__ void __launch_bounds__(kScatThreads, 2)
+sort_scatter_kernel(const uint32_t *keys_in, const uint32_t *vals_in, uint32_t *keys_out, uint32_t *vals_out,
+                    const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ Lp,
+                    const uint2 *__restrict__ tilemap, const uint32_t *__restrict__ n_tiles,
+                    const uint32_t *__restrict__ direct, unsigned *__restrict__ ticket, int64_t L, int64_t T,
+                    int shift, int first) {
+    __shared__ uint32_t cursor, cursor_next;
+    if (threadIdx.x == 0) cursor = blockIdx.x;
+    __syncthreads();
+    while (true) {
+        const uint32_t w = *const_cast<volatile uint32_t *>(&cursor);
+        if (w >= __ldg(n_tiles)) break;
+        const TileRef tr = decode_tile(__ldg(tilemap + w));
+        const int64_t seg = tr.seg, tile = tr.tile;
+        const int64_t sbase = seg * L, t0 = tile * kSortTile;
+        const int n = tr.n;
+        const bool d = tr.direct;
+        const uint32_t *ki = d ? keys_out : keys_in;
+        const uint32_t *vi = d ? vals_out : vals_in;
+        uint32_t *ko = d ? const_cast<uint32_t *>(keys_in) : keys_out;
+        uint32_t *vo = d ? const_cast<uint32_t *>(vals_in) : vals_out;
+        if (n == kSortTile)
+            scatter_tile<true>(ki + sbase + t0, (d && first) ? nullptr : vi + sbase + t0, ko + sbase, vo + sbase,
+                               offsets + (seg * T + tile) * kBins, n, shift, uint32_t(t0), &cursor_next, ticket,
+                               tilemap, n_tiles);
+        else
+            scatter_tile<false>(ki + sbase + t0, (d && first) ? nullptr : vi + sbase + t0, ko + sbase, vo + sbase,
+                                offsets + (seg * T + tile) * kBins, n, shift, uint32_t(t0), &cursor_next, ticket,
+                                tilemap, n_tiles);
+        __syncthreads();
+        if (threadIdx.x == 0) cursor = cursor_next;
+        __syncthreads();
+    }
 }
 
 // Last pass, fused with the Jaccard step.  Nothing is moved: the final rank of an element is
@@ -970,11 +1106,14 @@ sort_scatter_kernel(const uint32_t *__restrict__ keys_in, const uint32_t *__rest
 // (elements with a smaller top digit come first, equal digits keep the order of the previous
 // passes), which is all dJ needs.  Writes dJ to the pixel's slot and a loss partial per tile.
 __global__ void __launch_bounds__(kSortThreads, 2)
-rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict__ vals,
+rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__restrict__ vals_main,
+                    const uint32_t *__restrict__ keys_alt, const uint32_t *__restrict__ vals_alt,
+                    const uint32_t *__restrict__ direct,
                     const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ fgoffsets,
                     const uint32_t *__restrict__ n_pos_seg, float *__restrict__ jacc,
-                    double *__restrict__ partial, const uint32_t *__restrict__ Lp, int64_t L, int64_t T,
-                    int GY, int shift) {
+                    double *__restrict__ partial, const uint32_t *__restrict__ Lp,
+                    const uint2 *__restrict__ tilemap, const uint32_t *__restrict__ n_tiles,
+                    unsigned *__restrict__ ticket, int64_t L, int64_t T, int shift) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t *match = reinterpret_cast<uint32_t *>(smem_raw);
     uint16_t *wcnt_all = reinterpret_cast<uint16_t *>(smem_raw + kMatchBytes);
@@ -984,15 +1123,23 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
     uint32_t *keybuf = fgoff + kBins;                  // [kSortTile] keys of the tile
     __shared__ double sh_d[32];
 
-    const int64_t seg = blockIdx.x / GY;
-    const int64_t Lk = __ldg(Lp + seg);
-    const int64_t sbase = seg * L;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wbase = warp * (32 * kSortItems);
-  for (int64_t tile = blockIdx.x % GY; tile * kSortTile < Lk; tile += GY) {
+    __shared__ uint32_t cursor, cursor_next;  // position in the tile list (kept out of the registers)
+    if (tid == 0) cursor = blockIdx.x;
+    __syncthreads();
+  while (true) {
+    const uint32_t w = *const_cast<volatile uint32_t *>(&cursor);
+    if (w >= __ldg(n_tiles)) break;
+    const TileRef tr = decode_tile(__ldg(tilemap + w));
+    const int64_t seg = tr.seg, tile = tr.tile;
+    const int64_t sbase = seg * L;
     const int64_t t0 = tile * kSortTile;
-    const int n = int(Lk - t0 < kSortTile ? Lk - t0 : kSortTile);
+    const int n = tr.n;
 
+    const bool swapped = tr.direct;                      // (a direct segment: buffers in swapped roles)
+    const uint32_t *keys = (swapped ? keys_alt : keys_main) + sbase + t0;
+    const uint32_t *vals = (swapped ? vals_alt : vals_main) + sbase + t0;
     for (int i = tid; i < int(2 * kCntBytes / 4); i += kSortThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
     {
         const int64_t o = (seg * T + tile) * kBins;
@@ -1010,8 +1157,8 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
             const int idx = wbase + (r0 + r) * 32 + lane;
-            kk[r] = idx < n ? __ldg(keys + sbase + t0 + idx) : 0xFFFFFFFFu;
-            v[r] = idx < n ? __ldg(vals + sbase + t0 + idx) : 0u;
+            kk[r] = idx < n ? __ldg(keys + idx) : 0xFFFFFFFFu;
+            v[r] = idx < n ? __ldg(vals + idx) : 0u;
         }
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
@@ -1019,6 +1166,7 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
             match[wbase + (r0 + r) * 32 + lane] = v[r];
         }
     }
+    draw_next_tile(&cursor_next, ticket);
     __syncthreads();
     uint32_t rkfg[kSortItems];          // rank | fg rank << 16
     uint32_t *wmatch = match + warp * kBins;
@@ -1056,6 +1204,7 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
             runfg += f;
         }
     }
+    prefetch_next_tile(&cursor_next, tilemap, __ldg(n_tiles));
     __syncthreads();
     const uint32_t n_pos = __ldg(n_pos_seg + seg);
     float acc = 0.f;
@@ -1088,8 +1237,9 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restric
     __syncthreads();
     if (tid == 0) {
         double s = 0.0;
-        for (int w = 0; w < kSortWarps; ++w) s += sh_d[w];
+        for (int q = 0; q < kSortWarps; ++q) s += sh_d[q];
         partial[seg * T + tile] = s;
+        cursor = cursor_next;
     }
     __syncthreads();
   }
@@ -1176,7 +1326,9 @@ int launch_tile(const TileArgs &a, cudaStream_t stream) {
     const PairLayout lay = pair_layout(int(g.C), BWD);
     if (tma_ok && g.TP == kPairTP && g.nbox == 1 && g.M >= kPairTile && g.M % 4 == 0 && aligned16(a.labels) &&
         lay.stage_bytes <= 110u * 1024 && !env_int("B200_LOVASZ_NO_PAIR", 0)) {
-        int stages = env_int("B200_LOVASZ_STAGES", 1);
+        // measured at C = 19: keys 1 stage x 4 blocks per SM; backward (two tiles per stage)
+        // 2 stages in one block per SM beat 1 stage x 2 blocks (334 vs 371 us on 8 x 1 Mpixel)
+        int stages = env_int("B200_LOVASZ_STAGES", BWD ? 2 : 1);
         if (stages < 1) stages = 1;
         if (stages > kMaxStages) stages = kMaxStages;
         while (stages > 1 && size_t(stages) * lay.stage_bytes > 200u * 1024) --stages;
@@ -1273,43 +1425,52 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
     const int prune = env_int("B200_LOVASZ_NO_PRUNE", 0) ? 0 : 1;
     prune_count_kernel<<<nblk_all, kSortThreads, 0, s>>>(w.keysA, w.maxfg, w.minkey, w.kept, g.L, g.T, prune);
     if ((rc = launch_status("lovasz prune count launch")) != B200_OK) return rc;
-    prune_scan_kernel<<<unsigned(g.S), kBins, 0, s>>>(w.kept, w.Lp, g.T);
+    prune_scan_kernel<<<unsigned(g.S), kBins, 0, s>>>(w.kept, w.Lp, w.direct, g.L, g.T);
     if ((rc = launch_status("lovasz prune scan launch")) != B200_OK) return rc;
-    prune_compact_kernel<<<nblk_all, kSortThreads, 0, s>>>(w.keysA, w.maxfg, w.minkey, w.kept, w.keysB, w.valsB,
-                                                           jacc, g.L, g.T, prune);
+    prune_compact_kernel<<<nblk_all, kSortThreads, 0, s>>>(w.keysA, w.maxfg, w.minkey, w.kept, w.direct, w.keysB,
+                                                           w.valsB, jacc, g.L, g.T, prune);
     if ((rc = launch_status("lovasz prune compact launch")) != B200_OK) return rc;
 
-    // The number of kept elements is known on the device only: every segment gets GY blocks,
-    // each striding over the tiles its segment turns out to have.
-    int64_t gy = (int64_t(sm_count()) * 16 + g.S - 1) / g.S;
-    if (gy > g.T) gy = g.T;
-    if (gy < 1) gy = 1;
-    const int GY = int(gy);
-    const unsigned nblk = unsigned(g.S * gy);
-    const uint32_t *kin = w.keysB;
-    const uint32_t *vin = w.valsB;
-    uint32_t *kout = w.keysA, *vout = w.valsA;
+    // The number of sorted elements is known on the device only: fixed grids (a multiple of the
+    // SM count, by each kernel's blocks per SM) take tiles from the list of sort tiles in use.
+    tile_map_kernel<<<unsigned(g.S), 256, 0, s>>>(w.Lp, w.direct, w.tilemap, w.n_tiles, g.S);
+    if ((rc = launch_status("lovasz tile map launch")) != B200_OK) return rc;
+    auto grid_of = [&](int per_sm) {
+        // (measured on 8 x 19 x 1 Mpixel: a resident grid that loops costs 5.6 ms unpruned and 1.10 ms
+        // pruned, one block per possible tile 5.0 and 1.13 ms: many more blocks than fit, capped)
+        const int64_t want = int64_t(sm_count()) * per_sm * env_int("B200_LOVASZ_GRIDMULT", 32);
+        return unsigned(want < g.S * g.T ? want : g.S * g.T);
+    };
+    const unsigned nblk_hist = grid_of(8), nblk = grid_of(2);
+    unsigned *tickets = w.status + 16;           // zeroed with the status word; one per kernel
+
+    // compacted segments go B -> A -> B; segments that were not compacted A -> B -> A
+    uint32_t *kin = w.keysB, *vin = w.valsB, *kout = w.keysA, *vout = w.valsA;
     for (int pass = 0; pass < kPasses - 1; ++pass) {
         const int shift = 1 + pass * kBits;
-        sort_hist_kernel<false><<<nblk, kSortThreads, 0, s>>>(kin, w.hist, nullptr, w.Lp, g.L, g.T, GY, shift);
+        sort_hist_kernel<false><<<nblk_hist, kSortThreads, 0, s>>>(kin, w.hist, nullptr, w.Lp, w.tilemap, w.n_tiles,
+                                                                  kout, w.direct, g.L, g.T, shift);
         if ((rc = launch_status("lovasz sort histogram launch")) != B200_OK) return rc;
         sort_scan_kernel<false><<<unsigned(g.S), kBins, 0, s>>>(w.hist, nullptr, nullptr, w.Lp, g.T);
         if ((rc = launch_status("lovasz sort scan launch")) != B200_OK) return rc;
-        sort_scatter_kernel<<<nblk, kScatThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, w.Lp, g.L, g.T,
-                                                                     GY, shift);
+        sort_scatter_kernel<<<nblk, kScatThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, w.Lp, w.tilemap,
+                                                                     w.n_tiles, w.direct, tickets + pass, g.L, g.T,
+                                                                     shift, pass == 0 ? 1 : 0);
         if ((rc = launch_status("lovasz sort scatter launch")) != B200_OK) return rc;
-        kin = kout;
-        vin = vout;
-        if (kout == w.keysB) { kout = w.keysA; vout = w.valsA; } else { kout = w.keysB; vout = w.valsB; }
+        std::swap(kin, kout);
+        std::swap(vin, vout);
     }
     {
         const int shift = 1 + (kPasses - 1) * kBits;
-        sort_hist_kernel<true><<<nblk, kSortThreads, 0, s>>>(kin, w.hist, w.fghist, w.Lp, g.L, g.T, GY, shift);
+        sort_hist_kernel<true><<<nblk_hist, kSortThreads, 0, s>>>(kin, w.hist, w.fghist, w.Lp, w.tilemap, w.n_tiles,
+                                                                 kout, w.direct, g.L, g.T, shift);
         if ((rc = launch_status("lovasz last histogram launch")) != B200_OK) return rc;
         sort_scan_kernel<true><<<unsigned(g.S), kBins, 0, s>>>(w.hist, w.fghist, w.n_pos, w.Lp, g.T);
         if ((rc = launch_status("lovasz last scan launch")) != B200_OK) return rc;
-        rank_jaccard_kernel<<<nblk, kSortThreads, kJaccardSmem, s>>>(kin, vin, w.hist, w.fghist, w.n_pos, jacc,
-                                                                      w.partial, w.Lp, g.L, g.T, GY, shift);
+        rank_jaccard_kernel<<<nblk, kSortThreads, kJaccardSmem, s>>>(kin, vin, kout, vout, w.direct, w.hist, w.fghist,
+                                                                      w.n_pos, jacc,
+                                                                      w.partial, w.Lp, w.tilemap, w.n_tiles,
+                                                                      tickets + 2, g.L, g.T, shift);
         if ((rc = launch_status("lovasz rank+jaccard launch")) != B200_OK) return rc;
     }
     loss_kernel<<<unsigned(g.S), 32, 0, s>>>(w.partial, loss, w.Lp, g.T);
