@@ -250,6 +250,20 @@ def direct_calls(wl, sets, device):
         bwd = lambda i: _cabi.check(lib.b200_lovasz_backward(P(up), P(xs[i]), P(ys[i]), P(jacc), P(grads[i]),
                                                              n, c, m, dt, 255, 1, st))
         return fwd, bwd
+    if wl.name == "ohem":
+        nbytes = int(lib.b200_ohem_workspace_bytes(n, m))
+        ows = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        new_labels = [torch.empty_like(y) for y in ys]
+        n_min = (n * m) // 16
+
+        def fwd(i):
+            _cabi.check(lib.b200_ohem_label(P(xs[i]), P(ys[i]), P(new_labels[i]), P(ows), nbytes, n, c, m, dt, 255,
+                                            0.7, n_min, st))
+            _cabi.check(lib.b200_lsr_forward(P(xs[i]), P(new_labels[i]), None, P(recs[i]), P(ws), ws.numel(),
+                                             n, c, m, dt, 255, 0.0, st))
+        bwd = lambda i: _cabi.check(lib.b200_lsr_backward(P(xs[i]), P(new_labels[i]), P(one), 1, denoms[i],
+                                                          P(grads[i]), n, c, m, dt, 255, 0.0, st))
+        return fwd, bwd
     stem, hyper, ign = {"lsr": ("lsr", 0.1, 255), "lsr_rows": ("lsr", 0.1, -100), "lmargin": ("lmargin", 0.3, 255)}[wl.name]
     f_fwd, f_bwd = getattr(lib, "b200_%s_forward" % stem), getattr(lib, "b200_%s_backward" % stem)
     fwd = lambda i: _cabi.check(f_fwd(P(xs[i]), P(ys[i]), None, P(recs[i]), P(ws), ws.numel(), n, c, m, dt, ign, hyper, st))

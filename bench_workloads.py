@@ -1,5 +1,5 @@
 """Synthetic workloads of the benchmark: the five configurations of the task's baseline
-file, with their seeded generators, algorithmic byte counts and CPU-sample sizes.
+file (plus the OHEM relabelling in front of a loss), with their seeded generators, algorithmic byte counts and CPU-sample sizes.
 No dataset is involved: shapes and value distributions only.
 
 Draw order per configuration (one `torch.Generator().manual_seed(1234 + cfg)` on the CPU):
@@ -38,6 +38,10 @@ class Workload:
         e, p, s = self.elems, self.pixels, self.esize()
         if self.name == "focal":
             return 8 * e
+        if self.name == "ohem":
+            # relabelling: logits and labels read, labels written (4E + 16P; scores and the select
+            # passes over them, <= 16P more, not counted) + cross entropy forward 4E + 8P
+            return 8 * e + 24 * p
         if self.name == "lovasz":
             # the passes over ALL elements: keys (read logits, write keys) 8E, prune count 4E,
             # compaction (read keys, write dJ = 0) 8E.  The sort of the kept elements (~7% of E
@@ -63,7 +67,7 @@ class Workload:
     # that are still in the 126 MB L2 when the kernel ends are not counted by those counters.
     MEASURED_TRAFFIC = {
         "focal": (8.05, 9.95), "lsr": (4.45, 5.72), "lmargin": (4.10, 7.37),
-        "lovasz": (22.3, 11.5), "lsr_rows": (2.01, 3.15),
+        "lovasz": (22.3, 11.5), "lsr_rows": (2.01, 3.15), "ohem": (9.9, 5.72),
     }
 
     def traffic_forward(self):
@@ -73,6 +77,8 @@ class Workload:
         return self.MEASURED_TRAFFIC[self.name][1] * self.elems
 
     def entries(self):
+        if self.name == "ohem":
+            return "b200_ohem_label+b200_lsr_forward", "b200_lsr_backward"
         stem = {"lsr": "lsr", "lsr_rows": "lsr", "focal": "focal", "lmargin": "lmargin", "lovasz": "lovasz"}[self.name]
         return "b200_%s_forward" % stem, "b200_%s_backward" % stem
 
@@ -100,6 +106,15 @@ class Workload:
             labels = torch.randint(0, shape[1], [n] + shape[2:], **kw)
             labels[torch.rand([n] + shape[2:], **kw) < 0.10] = 255
             return logits, labels
+        if self.name == "ohem":
+            # a mostly trained network: 97% of the pixels score well above the threshold, so the
+            # n_min = P/16 hardest reach into the easy ones and the selection runs in full
+            logits = torch.randn(shape, **kw) * math.sqrt(2.0)
+            labels = torch.randint(0, shape[1], [n] + shape[2:], **kw)
+            easy = (torch.rand([n] + shape[2:], **kw) < 0.97).to(logits.dtype) * 9.0
+            logits.scatter_add_(1, labels.unsqueeze(1), easy.unsqueeze(1))
+            labels[torch.rand([n] + shape[2:], **kw) < 0.05] = 255
+            return logits, labels
         if self.name == "lovasz":
             logits = torch.randn(shape, **kw)
             h, w = shape[2], shape[3]
@@ -125,6 +140,8 @@ class Workload:
             return package.LargeMarginSoftmaxV3(0.3, 'mean', 255, process_group=process_group)
         if self.name == "lovasz":
             return package.LovaszSoftmaxV3('mean', 255, per_image=True, process_group=process_group)
+        if self.name == "ohem":
+            return package.OhemCELoss(0.7, None, 255)
         return package.LabelSmoothSoftmaxCEV3(0.1, 'mean', -100, process_group=process_group)
 
     def oracle(self, oracle_module):
@@ -138,6 +155,9 @@ class Workload:
             return lambda x, y: O.large_margin_softmax(x, y, 0.3, 255, 'mean')
         if self.name == "lovasz":
             return lambda x, y: O.lovasz_softmax(x, y, 255, 'mean', per_image=True)
+        if self.name == "ohem":
+            from oracle import ohem as OH
+            return lambda x, y: OH.ohem_ce_loss(x, y, 0.7, None, 255)
         return lambda x, y: O.label_smooth_ce(x, y, 0.1, -100, 'mean')
 
 
@@ -152,5 +172,8 @@ WORKLOADS = {
                        "LovaszSoftmaxV3 per image fp32 [8,19,1024,1024], 3% ignored, mean", 1),
     "lsr_rows": Workload("lsr_rows", 5, (16384, 32768, 1, 1), torch.float16,
                          "LabelSmoothSoftmaxCEV3 fp16 [16384,32768,1,1], mean", 1024),
+    # not one of the five baseline configurations: the relabelling step in front of the loss
+    "ohem": Workload("ohem", 6, (16, 19, 512, 512), torch.float32,
+                     "OhemCELoss fp32 [16,19,512,512], thresh 0.7, n_min P/16, 97% easy pixels, 5% ignored", 4),
 }
 HEADLINE = "focal"

@@ -181,6 +181,26 @@ int b200_lovasz_backward(const float *grad, const void *logits, const int64_t *l
                          int64_t M, int dtype, int64_t ignore_index, int per_image,
                          void *stream);
 
+/* ------------------------------------------------------------------- OHEM ---
+ * Online hard example mining by score: the relabelling step in front of a
+ * cross-entropy / large-margin loss.  Replaces ohem_cpp.score_ohem_label
+ * (reference csrc/ohem_label_kernel.cu:179-262, :265-281; kernels :53-176; callers
+ * pytorch_loss/ohem_loss.py:22-27,41-46).
+ *   score_i = softmax(logits_i)[labels_i]   (1 for ignored pixels)
+ *   out_i   = ignore_index  if score_i > max(score_thresh, t),  else labels_i,
+ * where t is the n_min-th smallest score: the n_min hardest pixels and every pixel
+ * scoring at most the threshold keep their label.  n_min >= N*M copies the labels;
+ * n_min <= 0 lets the threshold alone decide.  Pixels tied with t all stay (the
+ * reference's unstable sort keeps an unspecified subset of them).
+ * out_labels may alias labels.  workspace: b200_ohem_workspace_bytes(N, M) bytes,
+ * 256-byte aligned, contents irrelevant on entry.  At most 2^32 - 1 pixels.
+ */
+size_t b200_ohem_workspace_bytes(int64_t N, int64_t M);
+int b200_ohem_label(const void *logits, const int64_t *labels, int64_t *out_labels,
+                    void *workspace, size_t workspace_bytes, int64_t N, int64_t C, int64_t M,
+                    int dtype, int64_t ignore_index, float score_thresh, int64_t n_min,
+                    void *stream);
+
 #ifdef __cplusplus
 }
 #endif

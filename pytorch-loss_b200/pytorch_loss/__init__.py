@@ -19,3 +19,6 @@ __all__ = [
 from .lovasz_softmax import LovaszSoftmaxV3, LovaszSoftmaxFunctionV3
 
 __all__ += ["LovaszSoftmaxV3", "LovaszSoftmaxFunctionV3"]
+from .ohem_loss import OhemCELoss, OhemLargeMarginLoss
+
+__all__ += ["OhemCELoss", "OhemLargeMarginLoss"]

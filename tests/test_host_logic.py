@@ -102,3 +102,21 @@ def test_combine_mean_and_group_flags():
         _sharding.group_is_active(True)          # no process group initialised here
     with pytest.raises(RuntimeError):
         _sharding.allreduce_sum_count(torch.zeros(3, dtype=torch.float64), None)
+
+
+def test_ohem_oracle_rule():
+    """The oracle's relabelling on a hand-made case: the n_min hardest always stay, pixels at or
+    below the threshold stay, ignored pixels score 1 and stay ignored."""
+    import torch
+    from oracle import ohem as OH
+    logits = torch.zeros(1, 2, 1, 6)
+    # softmax score of class 0 per pixel: sigmoid(x0 - x1)
+    logits[0, 0, 0] = torch.tensor([-3.0, -1.0, 0.0, 1.0, 3.0, 5.0])
+    labels = torch.tensor([[[0, 0, 0, 0, 0, 255]]])
+    new, scores = OH.score_ohem_label(logits, labels, 255, 0.6, 0)
+    assert new.tolist() == [[[0, 0, 0, 255, 255, 255]]]          # scores .05 .27 .5 | .73 .95, ignored
+    new, _ = OH.score_ohem_label(logits, labels, 255, 0.1, 3)
+    assert new.tolist() == [[[0, 0, 0, 255, 255, 255]]]          # threshold keeps 1, n_min keeps 3
+    new, _ = OH.score_ohem_label(logits, labels, 255, 0.1, 6)
+    assert new.tolist() == labels.tolist()                       # n_min >= pixels: unchanged
+    assert float(scores[0, 0, 5]) == 1.0
