@@ -215,6 +215,16 @@ def try_capture(crit, sets):
         return None
 
 
+def reduction_collective(world):
+    """How the ranks' [sum, count] pairs were added in this run."""
+    if world <= 1:
+        return "none"
+    from pytorch_loss import _p2p
+    if any(ex is not None for ex in _p2p._contexts.values()):
+        return "in-kernel exchange: peer stores into IPC-mapped slots, bounded local wait"
+    return "16-byte NCCL all-reduce"
+
+
 def direct_calls(wl, sets, device):
     """(forward, backward) callables that launch the workload's two C-ABI entry points on
     input set i with preallocated outputs: what `roofline` times."""
@@ -459,7 +469,7 @@ def main():
             "dtype": "f16" if wl.dtype == torch.float16 else "f32", "data": "synthetic",
             "config": {"workload": wl.desc, "per_gpu_shape": list(wl.shape),
                        "l2": "3 rotating input sets, each larger than L2 with its gradient",
-                       "cuda_graph": h["graph"], "reduction_collective": "16-byte all-reduce" if world > 1 else "none"},
+                       "cuda_graph": h["graph"], "reduction_collective": reduction_collective(world)},
             "roofline": h["roofline"], "cpu_baseline": h.get("cpu_baseline"), "e2e": h["e2e"],
             "gpu_launches": h["launches_per_step"] * args.steps, "clocks": h["clocks"],
             "workloads": {k: v for k, v in results.items() if k != headline},

@@ -29,7 +29,8 @@
  * kernels leave them zero again, so one zero-initialised buffer per stream can
  * be reused forever.  Two calls that overlap on the GPU must not share one.
  * Byte 4..7 of the workspace is a status word: non-zero after a kernel gave up
- * a bounded wait (see b200_read_status).
+ * a bounded wait (see b200_read_status).  Bytes 8..15 hold the optional exchange
+ * context pointer (b200_reduce_attach_exchange; zero = none).
  */
 #ifndef B200LOSS_H_
 #define B200LOSS_H_
@@ -67,6 +68,42 @@ size_t b200_reduce_workspace_bytes(void);
 /* Synchronises `stream`, reads the workspace's status word, clears it, and returns
  * B200_OK or B200_ERR_STATUS.  For tests and debugging; never needed for results. */
 int b200_read_status(void *workspace, void *stream);
+
+/* ------------------------------------------------- cross-GPU sum (optional) ---
+ * No counterpart in the reference (it has no multi-GPU path for these losses).
+ * With one process per GPU and the batch sharded over the ranks, reduction 'mean'
+ * needs the global [sum, count].  Instead of a collective call between the forward
+ * and the backward kernel, the reducing forward kernel can exchange the pair
+ * itself: attach an exchange context to a reduction workspace, and every reducing
+ * forward that uses that workspace writes the GLOBAL sums into its record (all
+ * ranks get identical bits; rank order summation).  All ranks must then make the
+ * same sequence of reducing calls on their attached workspaces, like a collective.
+ *
+ * The context is `b200_exchange_ctx_bytes()` bytes of device memory laid out as
+ *     int32 world; int32 rank; uint32 poll_limit; uint32 reserved;
+ *     uint64 *seq;              // one zero-initialised uint64 in this rank's memory
+ *     void  *slots[16];         // slots[p]: rank p's slot array as mapped in THIS
+ *                               // process (p == rank: the local array); each array is
+ *                               // b200_exchange_slot_bytes(world) bytes, zero-initialised
+ * The peers' arrays are ordinary device allocations opened through CUDA IPC (or any
+ * other peer mapping); the kernel only STORES to them and polls its own array.  A
+ * wait that exceeds poll_limit polls sets status bit 0x100 (b200_read_status) and
+ * the record then holds the local sums.  exchange_ctx == NULL detaches.
+ */
+/* Lets kernels of the calling thread's current device store into `peer_device`'s memory
+ * (cudaDeviceEnablePeerAccess; already enabled counts as success). */
+int b200_enable_peer_access(int peer_device);
+/* CUDA IPC helpers for the slot arrays (each rank exports its array, every peer opens it
+ * with its own device current, which maps it for that device's kernels).
+ *   export: 64-byte handle of the allocation that contains dev_ptr + dev_ptr's offset in it
+ *   open  : the peer's dev_ptr as mapped in this process (lazy peer access enabled)
+ *   close : unmaps (pass the same offset) */
+int b200_ipc_export(const void *dev_ptr, void *handle64, uint64_t *offset);
+int b200_ipc_open(const void *handle64, uint64_t offset, void **mapped);
+int b200_ipc_close(void *mapped, uint64_t offset);
+size_t b200_exchange_ctx_bytes(void);
+size_t b200_exchange_slot_bytes(int world);
+int b200_reduce_attach_exchange(void *workspace, const void *exchange_ctx, void *stream);
 
 /* ------------------------------------------------------------------ focal ---
  * Sigmoid focal loss, elementwise over E elements.

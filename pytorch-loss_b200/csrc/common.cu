@@ -103,6 +103,12 @@ bool encode_tensor_map(CUtensorMap *map, int dtype, const void *base, int rank,
 
 }  // namespace b200
 
+namespace {
+__global__ void set_exchange_kernel(void *workspace, const void *ctx) {
+    *reinterpret_cast<const void **>(reinterpret_cast<char *>(workspace) + b200::kExchangeCtxOffset) = ctx;
+}
+}  // namespace
+
 extern "C" {
 
 int b200_abi_version(void) { return 1; }
@@ -130,6 +136,105 @@ int b200_read_status(void *workspace, void *stream) {
     cudaStreamSynchronize(s);
     b200::set_error("device status word = 0x%x: a kernel gave up a bounded wait", status);
     return B200_ERR_STATUS;
+}
+
+size_t b200_exchange_ctx_bytes(void) { return sizeof(b200::ExchangeCtx); }
+size_t b200_exchange_slot_bytes(int world) {
+    return world > 0 ? size_t(2) * size_t(world) * sizeof(b200::ExchangeSlot) : 0;
+}
+
+int b200_enable_peer_access(int peer_device) {
+    int current = -1, can = 0;
+    if (cudaGetDevice(&current) != cudaSuccess) return b200::launch_status("cudaGetDevice");
+    if (peer_device == current) return B200_OK;
+    if (cudaDeviceCanAccessPeer(&can, current, peer_device) != cudaSuccess || !can) {
+        cudaGetLastError();
+        b200::set_error("b200_enable_peer_access: device %d cannot access device %d", current, peer_device);
+        return B200_ERR_UNSUPPORTED;
+    }
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();
+        b200::set_error("b200_enable_peer_access: %s", cudaGetErrorString(e));
+        return B200_ERR_UNSUPPORTED;
+    }
+    cudaGetLastError();     // "already enabled" is not an error to keep
+    return B200_OK;
+}
+
+// CUDA IPC of the exchange slots.  The importer opens the handle with ITS OWN device current
+// (cudaIpcMemLazyEnablePeerAccess): that maps the exporter's allocation into the importing
+// device's address space, which is what kernels of that device need in order to store to it.
+int b200_ipc_export(const void *dev_ptr, void *handle64, uint64_t *offset) {
+    if (!dev_ptr || !handle64 || !offset) {
+        b200::set_error("b200_ipc_export: null argument");
+        return B200_ERR_ARG;
+    }
+    typedef CUresult (*RangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+    void *fp = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fp, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess || !fp) {
+        cudaGetLastError();
+        b200::set_error("b200_ipc_export: cuMemGetAddressRange is not available");
+        return B200_ERR_UNSUPPORTED;
+    }
+    cudaFree(nullptr);      // the driver call needs a context bound to this thread
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (reinterpret_cast<RangeFn>(fp)(&base, &size, reinterpret_cast<CUdeviceptr>(dev_ptr)) != CUDA_SUCCESS) {
+        b200::set_error("b200_ipc_export: not a device allocation");
+        return B200_ERR_ARG;
+    }
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "the handle travels as 64 bytes");
+    const cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void *>(base));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        b200::set_error("b200_ipc_export: %s", cudaGetErrorString(e));
+        return B200_ERR_UNSUPPORTED;
+    }
+    memcpy(handle64, &h, 64);
+    *offset = uint64_t(reinterpret_cast<CUdeviceptr>(dev_ptr) - base);
+    return B200_OK;
+}
+
+int b200_ipc_open(const void *handle64, uint64_t offset, void **mapped) {
+    if (!handle64 || !mapped) {
+        b200::set_error("b200_ipc_open: null argument");
+        return B200_ERR_ARG;
+    }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void *base = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        b200::set_error("b200_ipc_open: %s", cudaGetErrorString(e));
+        return B200_ERR_UNSUPPORTED;
+    }
+    *mapped = static_cast<char *>(base) + offset;
+    return B200_OK;
+}
+
+int b200_ipc_close(void *mapped, uint64_t offset) {
+    if (!mapped) return B200_OK;
+    const cudaError_t e = cudaIpcCloseMemHandle(static_cast<char *>(mapped) - offset);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        b200::set_error("b200_ipc_close: %s", cudaGetErrorString(e));
+        return B200_ERR_ARG;
+    }
+    return B200_OK;
+}
+
+int b200_reduce_attach_exchange(void *workspace, const void *exchange_ctx, void *stream) {
+    if (!workspace) {
+        b200::set_error("b200_reduce_attach_exchange: workspace is NULL");
+        return B200_ERR_ARG;
+    }
+    set_exchange_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(workspace, exchange_ctx);
+    return b200::launch_status("exchange attach launch");
 }
 
 }  // extern "C"

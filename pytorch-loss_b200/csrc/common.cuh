@@ -24,10 +24,37 @@ int sm_count();                         // SMs of the current device (cached per
 // Workspace layout shared by all reducing kernels.
 //   [0]   uint32  ticket   (must be zero between kernels; kernels reset it)
 //   [4]   uint32  status   (non-zero: a bounded wait gave up)
+//   [8]   ExchangeCtx*     (optional, see below; null: the record holds this GPU's sums)
 //   [64]  double2 partials[kMaxPartials]
 constexpr int kMaxPartials = 65536;
 constexpr size_t kPartialsOffset = 64;
 constexpr size_t kReduceWorkspaceBytes = kPartialsOffset + size_t(kMaxPartials) * 16;
+
+// Cross-GPU sum of [sum, count] inside the reducing kernel (one process per GPU, batch
+// sharded over the ranks).  Every rank owns an array of slots that its peers can write
+// (peer-mapped device memory); the block that finishes a rank's reduction stores its pair into
+// slot [seq & 1][rank] of EVERY rank (its own included), then waits -- bounded -- until all
+// `world` slots of its own array carry this call's sequence number, and adds them in rank
+// order, so all ranks get the same bits.  Plain peer stores and local polls: no peer loads,
+// no multicast, no atomics across GPUs.  The sequence number is a device-side counter, so
+// replaying a captured graph keeps working.  Two slot sets suffice: a rank cannot start call
+// k+2 before every peer has finished reading call k (it needs their call k+1 message first).
+struct ExchangeSlot {       // 32 bytes
+    double sum;
+    double count;
+    unsigned long long seq;
+    unsigned long long pad;
+};
+constexpr int kMaxExchangeRanks = 16;
+struct ExchangeCtx {        // lives in device memory; filled by the host once (layout is ABI)
+    int world;
+    int rank;
+    unsigned poll_limit;    // polls of one slot before the wait gives up (status bit 0x100)
+    unsigned reserved;
+    unsigned long long *seq;                    // this rank's call counter
+    ExchangeSlot *slots[kMaxExchangeRanks];     // slots[p]: rank p's array [2][world]
+};
+constexpr size_t kExchangeCtxOffset = 8;
 
 struct ReduceRecord {       // the 32-byte "out" record of the C ABI
     double sum;
@@ -144,6 +171,54 @@ __device__ __forceinline__ void grid_reduce_finish(double sum, double cnt, void 
         b += p.y;
     }
     block_sum2(a, b, sh);
+    ExchangeCtx *ex = *reinterpret_cast<ExchangeCtx **>(reinterpret_cast<char *>(workspace) + kExchangeCtxOffset);
+    if (ex) {
+        __shared__ double s_pair[2];
+        __shared__ unsigned long long s_seq;
+        __shared__ int s_fail;
+        if (threadIdx.x == 0) {
+            s_pair[0] = a;
+            s_pair[1] = b;
+            s_seq = ++(*ex->seq);
+            s_fail = 0;
+        }
+        __syncthreads();
+        const int world = ex->world;
+        const unsigned long long q = s_seq;
+        if (int(threadIdx.x) < world) {
+            // my pair to rank threadIdx.x: data, fence, then the sequence number
+            volatile ExchangeSlot *dst = ex->slots[threadIdx.x] + (q & 1ull) * world + ex->rank;
+            dst->sum = s_pair[0];
+            dst->count = s_pair[1];
+            __threadfence_system();
+            dst->seq = q;
+            // rank threadIdx.x's pair in my own array
+            volatile ExchangeSlot *src = ex->slots[ex->rank] + (q & 1ull) * world + threadIdx.x;
+            unsigned polls = 0;
+            while (src->seq != q) {
+                if (++polls > ex->poll_limit) {
+                    s_fail = 1;
+                    break;
+                }
+                __nanosleep(64);
+            }
+            __threadfence_system();
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            if (s_fail) {
+                atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, 0x100u);
+            } else {
+                const volatile ExchangeSlot *mine = ex->slots[ex->rank] + (q & 1ull) * world;
+                a = 0.0;
+                b = 0.0;
+                for (int p = 0; p < world; ++p) {
+                    a += mine[p].sum;
+                    b += mine[p].count;
+                }
+            }
+        }
+    }
     if (threadIdx.x == 0) {
         out->sum = a;
         out->count = b;

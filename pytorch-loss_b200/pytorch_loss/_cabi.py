@@ -27,6 +27,13 @@ SIGNATURES = {
     "b200_kernel_launch_count": (_c.c_uint64, []),
     "b200_reduce_workspace_bytes": (_sz, []),
     "b200_read_status": (_int, [_vp, _vp]),
+    "b200_enable_peer_access": (_int, [_int]),
+    "b200_ipc_export": (_int, [_vp, _vp, _vp]),
+    "b200_ipc_open": (_int, [_vp, _c.c_uint64, _vp]),
+    "b200_ipc_close": (_int, [_vp, _c.c_uint64]),
+    "b200_exchange_ctx_bytes": (_sz, []),
+    "b200_exchange_slot_bytes": (_sz, [_int]),
+    "b200_reduce_attach_exchange": (_int, [_vp, _vp, _vp]),
     "b200_focal_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _int, _f32, _f32, _vp]),
     "b200_focal_backward": (_int, [_vp, _vp, _vp, _int, _vp, _vp, _i64, _int, _f32, _f32, _vp]),
     "b200_focal_forward_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _f32, _f32, _vp]),

@@ -5,6 +5,7 @@ import torch
 import torch.amp as amp
 
 from . import _cabi
+from . import _p2p
 from . import _sharding
 
 _ENTRY = {
@@ -31,12 +32,14 @@ def forward_per_pixel(kind, logits, labels, ignore_index, hyper):
     return losses, logits, labels
 
 
-def forward_reduced(kind, logits, labels, ignore_index, hyper, want_losses=False):
-    """Runs the reducing forward; returns (record, per-pixel losses or None, logits, labels)."""
+def forward_reduced(kind, logits, labels, ignore_index, hyper, want_losses=False, exchange=None):
+    """Runs the reducing forward; returns (record, per-pixel losses or None, logits, labels).
+    With an `_p2p.Exchange` the kernel adds the sums over the ranks itself and the record is
+    the global one."""
     dev, logits, labels, n, c, m, dt = _prep(logits, labels)
     lib = _cabi.load_library()
     rec = _cabi.new_record(dev)
-    ws = _cabi.reduce_workspace(dev)
+    ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
     losses = torch.empty(labels.shape, dtype=logits.dtype, device=dev) if want_losses else None
     with torch.cuda.device(dev):
         _cabi.check(getattr(lib, _ENTRY[kind][0])(
@@ -70,15 +73,17 @@ class ReducedLossFunc(torch.autograd.Function):
     """'mean' / 'sum' over valid pixels as ONE reducing forward kernel (no per-pixel loss
     tensor, no separate count or sum pass) and ONE backward kernel that recomputes the
     softmax and applies grad_output / n_valid read from device memory.  With a process
-    group the [sum, count] pair is all-reduced first, so the result is the loss of the
-    concatenated batch.  Returns a 0-dim float32 loss."""
+    group the [sum, count] pair is summed over the ranks first -- inside the forward kernel
+    when the ranks can map each other's memory (`_p2p`), else by a 16-byte all-reduce -- so the
+    result is the loss of the concatenated batch.  Returns a 0-dim float32 loss."""
 
     @staticmethod
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
     def forward(ctx, logits, labels, kind, hyper, ignore_index, mean, group):
-        rec, _, logits, labels = forward_reduced(kind, logits, labels, ignore_index, hyper)
+        exchange = _p2p.get_exchange(group, logits.device) if logits.is_cuda else None
+        rec, _, logits, labels = forward_reduced(kind, logits, labels, ignore_index, hyper, exchange=exchange)
         sum_count = rec[:4].view(torch.float64)
-        if _sharding.group_is_active(group):
+        if exchange is None and _sharding.group_is_active(group):
             _sharding.allreduce_sum_count(sum_count, group)
             loss = _sharding.combine_mean(sum_count) if mean else sum_count[0].to(torch.float32)
         else:

@@ -12,6 +12,7 @@ import torch.nn as nn
 import torch.amp as amp
 
 from . import _cabi
+from . import _p2p
 from . import _sharding
 
 
@@ -105,13 +106,14 @@ class _FocalReducedFunc(torch.autograd.Function):
         dev, logits, labels, dt = _prep(logits, labels)
         lib = _cabi.load_library()
         rec = _cabi.new_record(dev)
-        ws = _cabi.reduce_workspace(dev)
+        exchange = _p2p.get_exchange(group, dev)      # sums over the ranks inside the kernel, if possible
+        ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
         with torch.cuda.device(dev):
             _cabi.check(lib.b200_focal_forward(
                 _cabi.ptr(logits), _cabi.ptr(labels), None, _cabi.ptr(rec), _cabi.ptr(ws),
                 ws.numel(), logits.numel(), dt, float(gamma), float(alpha), _cabi.stream_ptr(dev)))
         sum_count = rec[:4].view(torch.float64)
-        if _sharding.group_is_active(group):
+        if exchange is None and _sharding.group_is_active(group):
             _sharding.allreduce_sum_count(sum_count, group)
             loss = _sharding.combine_mean(sum_count) if mean else sum_count[0].to(torch.float32)
         else:

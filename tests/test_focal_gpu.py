@@ -102,3 +102,39 @@ def test_focal_deterministic_and_workspace_rearmed():
         assert crit(logits, labels).item() == first
     from pytorch_loss import _cabi
     _cabi.read_status(logits.device)
+
+
+def test_exchange_single_rank_and_bounded_wait():
+    """The in-kernel cross-GPU sum on one GPU: a world of one rank gives the local sums, and a
+    context whose peer never writes makes the bounded wait give up (status word, no hang)."""
+    import pytorch_loss  # noqa: F401  (loads the library)
+    from pytorch_loss import _cabi, _p2p
+    from oracle import losses as O
+    dev = torch.device("cuda", 0)
+    lib = _cabi.load_library()
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(3, 1, 40, 50, generator=g)
+    labels = (torch.rand(3, 1, 40, 50, generator=g) < 0.2).float()
+    want, _ = O.focal_loss(logits, labels, 0.25, 2.0, 'sum')
+    x, y = logits.to(dev), labels.to(dev)
+
+    def run(exchange):
+        rec = _cabi.new_record(dev)
+        ws = exchange.workspace()
+        for _ in range(3):              # both slot sets
+            _cabi.check(lib.b200_focal_forward(_cabi.ptr(x), _cabi.ptr(y), None, _cabi.ptr(rec), _cabi.ptr(ws),
+                                               ws.numel(), x.numel(), _cabi.F32, 2.0, 0.25, _cabi.stream_ptr(dev)))
+        return rec, ws
+
+    rec, ws = run(_p2p.local_exchange_for_tests(dev, 1, 0, 1000))
+    _cabi.check(lib.b200_read_status(_cabi.ptr(ws), _cabi.stream_ptr(dev)))
+    sums = rec[:4].view(torch.float64).cpu()
+    assert abs(float(sums[0]) - float(want)) <= 1e-5 * abs(float(want))
+    assert float(sums[1]) == x.numel()
+
+    rec, ws = run(_p2p.local_exchange_for_tests(dev, 2, 0, 200))     # rank 1 never shows up
+    rc = lib.b200_read_status(_cabi.ptr(ws), _cabi.stream_ptr(dev))
+    assert rc == 4, "expected B200_ERR_STATUS, got %d" % rc          # the wait ran out and said so
+    sums = rec[:4].view(torch.float64).cpu()
+    assert abs(float(sums[0]) - float(want)) <= 1e-5 * abs(float(want))   # the record holds the local sums
+    assert lib.b200_read_status(_cabi.ptr(ws), _cabi.stream_ptr(dev)) == 0    # cleared by the read

@@ -24,11 +24,12 @@ def _free_port():
     return port
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, p2p):
     for p in (ROOT, PKG_PARENT):
         if p not in sys.path:
             sys.path.insert(0, p)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      B200_LOSS_P2P="1" if p2p else "0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
@@ -59,17 +60,31 @@ def _worker(rank, world, port, out):
         loss.backward()
         errs.append((abs(float(loss) - float(want_loss)) / abs(float(want_loss)),
                      float((x.grad.cpu() - want_grad[lo:hi]).abs().max())))
-    torch.save(errs, "%s.%d" % (out, rank))
+    # run the sharded step a few more times: the exchange alternates between its two slot sets
+    crit, lab, (want_loss, _) = cases[0]
+    for _ in range(5):
+        loss = crit(logits[lo:hi].to(dev), lab[lo:hi].to(dev))
+    errs.append((abs(float(loss) - float(want_loss)) / abs(float(want_loss)), 0.0))
+    from pytorch_loss import _cabi, _p2p
+    _cabi.read_status(dev)
+    for ex in _p2p._contexts.values():
+        if ex is not None:
+            _cabi.check(_cabi.load_library().b200_read_status(_cabi.ptr(ex.workspace()), _cabi.stream_ptr(dev)))
+    mode = "p2p" if any(ex is not None for ex in _p2p._contexts.values()) else "nccl"
+    torch.save((mode, errs), "%s.%d" % (out, rank))
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_sharded_losses_match_concatenated_batch(tmp_path):
+@pytest.mark.parametrize("p2p", [True, False], ids=["peer_exchange", "nccl_allreduce"])
+def test_sharded_losses_match_concatenated_batch(tmp_path, p2p):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     out = str(tmp_path / "errs")
-    mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), out, p2p), nprocs=2, join=True)
     for rank in range(2):
-        for loss_err, grad_err in torch.load("%s.%d" % (out, rank)):
+        mode, errs = torch.load("%s.%d" % (out, rank))
+        assert mode == ("p2p" if p2p else "nccl"), "the sums went through %s" % mode
+        for loss_err, grad_err in errs:
             assert loss_err <= 1e-5, loss_err
             assert grad_err <= 1e-5, grad_err
