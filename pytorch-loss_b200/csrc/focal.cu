@@ -461,7 +461,8 @@ namespace b200 {
 namespace {
 
 constexpr int kFocalNoAllocMaxBlocks = 1024;
-constexpr size_t kFocalNoAllocScratchBytes = kPartialsOffset + size_t(kFocalNoAllocMaxBlocks) * 16;
+static_assert(sizeof(b200_focal_noalloc_scratch) == kPartialsOffset + size_t(kFocalNoAllocMaxBlocks) * 16,
+              "the scratch array holds the header and one partial per block");
 constexpr int64_t kFocalNoAllocMaxElems = int64_t(1) << 28;
 constexpr int kMaxDevices = 64;
 

@@ -643,9 +643,8 @@ __device__ __forceinline__ uint32_t prune_limit(const uint32_t *maxfg, const uin
 template <bool LAST>
 __global__ void __launch_bounds__(kSortThreads)
 sort_hist_kernel(const uint32_t *__restrict__ keys, uint32_t *__restrict__ hist,
-                 uint32_t *__restrict__ fghist, const uint32_t *__restrict__ Lp,
-                 const uint2 *__restrict__ tilemap, const uint32_t *__restrict__ n_tiles,
-                 const uint32_t *__restrict__ keys_alt, const uint32_t *__restrict__ direct, int64_t L, int64_t T,
+                 uint32_t *__restrict__ fghist, const uint2 *__restrict__ tilemap,
+                 const uint32_t *__restrict__ n_tiles, const uint32_t *__restrict__ keys_alt, int64_t L, int64_t T,
                  int shift) {
     __shared__ uint32_t sh[kBins];
     __shared__ uint32_t shfg[LAST ? kBins : 1];
@@ -902,7 +901,7 @@ constexpr size_t kJaccardSmem = kMatchBytes + 2 * kCntBytes + 2 * kBins * 4 + kT
 // shared-memory round trip (the leader's counter update) -- atomics or match.any on the digit
 // cost as much per round as there are equal / distinct digits and left the kernel waiting.
 // Returns the rank of this lane's element inside (warp, digit) counting all earlier rounds.
-__device__ __forceinline__ uint32_t rank_round(uint32_t d, uint32_t * /*unused*/, uint16_t *wcnt, int lane,
+__device__ __forceinline__ uint32_t rank_round(uint32_t d, uint16_t *wcnt, int lane,
                                                uint32_t lt, uint32_t &peers_out) {
     uint32_t peers = 0xffffffffu;
 #pragma unroll
@@ -965,9 +964,9 @@ __device__ __forceinline__ void scatter_tile(const uint32_t *__restrict__ kin, c
     for (int r = 0; r < kScatItems; r += 2) {
         if (r < R) {
             uint32_t peers;
-            const uint32_t r0 = rank_round(digit_of(key[r], shift), nullptr, wcnt, lane, lt, peers);
+            const uint32_t r0 = rank_round(digit_of(key[r], shift), wcnt, lane, lt, peers);
             uint32_t r1 = 0;
-            if (r + 1 < R) r1 = rank_round(digit_of(key[r + 1], shift), nullptr, wcnt, lane, lt, peers);
+            if (r + 1 < R) r1 = rank_round(digit_of(key[r + 1], shift), wcnt, lane, lt, peers);
             rank2[r / 2] = r0 | (r1 << 16);
         }
     }
@@ -1067,9 +1066,8 @@ __device__ __forceinline__ void scatter_tile(const uint32_t *__restrict__ kin, c
 // are their positions.
 __global__ void __launch_bounds__(kScatThreads, 2)
 sort_scatter_kernel(const uint32_t *keys_in, const uint32_t *vals_in, uint32_t *keys_out, uint32_t *vals_out,
-                    const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ Lp,
-                    const uint2 *__restrict__ tilemap, const uint32_t *__restrict__ n_tiles,
-                    const uint32_t *__restrict__ direct, unsigned *__restrict__ ticket, int64_t L, int64_t T,
+                    const uint32_t *__restrict__ offsets, const uint2 *__restrict__ tilemap,
+                    const uint32_t *__restrict__ n_tiles, unsigned *__restrict__ ticket, int64_t L, int64_t T,
                     int shift, int first) {
     __shared__ uint32_t cursor, cursor_next;
     if (threadIdx.x == 0) cursor = blockIdx.x;
@@ -1108,11 +1106,9 @@ sort_scatter_kernel(const uint32_t *keys_in, const uint32_t *vals_in, uint32_t *
 __global__ void __launch_bounds__(kSortThreads, 2)
 rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__restrict__ vals_main,
                     const uint32_t *__restrict__ keys_alt, const uint32_t *__restrict__ vals_alt,
-                    const uint32_t *__restrict__ direct,
                     const uint32_t *__restrict__ offsets, const uint32_t *__restrict__ fgoffsets,
                     const uint32_t *__restrict__ n_pos_seg, float *__restrict__ jacc,
-                    double *__restrict__ partial, const uint32_t *__restrict__ Lp,
-                    const uint2 *__restrict__ tilemap, const uint32_t *__restrict__ n_tiles,
+                    double *__restrict__ partial, const uint2 *__restrict__ tilemap, const uint32_t *__restrict__ n_tiles,
                     unsigned *__restrict__ ticket, int64_t L, int64_t T, int shift) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t *match = reinterpret_cast<uint32_t *>(smem_raw);
@@ -1169,7 +1165,6 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__re
     draw_next_tile(&cursor_next, ticket);
     __syncthreads();
     uint32_t rkfg[kSortItems];          // rank | fg rank << 16
-    uint32_t *wmatch = match + warp * kBins;
     uint16_t *wcnt = wcnt_all + warp * kBins;
     uint16_t *wfg = wfg_all + warp * kBins;
     const uint32_t lt = lanemask_lt();
@@ -1181,7 +1176,7 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__re
         const uint32_t fgball = __ballot_sync(0xffffffffu, fg);
         uint32_t peers;
         const uint32_t fgold_src = wfg[d];            // read before any leader updates it this round
-        const uint32_t rk = rank_round(d, wmatch, wcnt, lane, lt, peers);
+        const uint32_t rk = rank_round(d, wcnt, lane, lt, peers);
         const int leader = __ffs(peers) - 1;
         const uint32_t fgold = fgold_src;            // every peer read the same word
         if (lane == leader) wfg[d] = uint16_t(fgold + __popc(peers & fgball));
@@ -1448,28 +1443,28 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
     uint32_t *kin = w.keysB, *vin = w.valsB, *kout = w.keysA, *vout = w.valsA;
     for (int pass = 0; pass < kPasses - 1; ++pass) {
         const int shift = 1 + pass * kBits;
-        sort_hist_kernel<false><<<nblk_hist, kSortThreads, 0, s>>>(kin, w.hist, nullptr, w.Lp, w.tilemap, w.n_tiles,
-                                                                  kout, w.direct, g.L, g.T, shift);
+        sort_hist_kernel<false><<<nblk_hist, kSortThreads, 0, s>>>(kin, w.hist, nullptr, w.tilemap, w.n_tiles, kout,
+                                                                  g.L, g.T, shift);
         if ((rc = launch_status("lovasz sort histogram launch")) != B200_OK) return rc;
         sort_scan_kernel<false><<<unsigned(g.S), kBins, 0, s>>>(w.hist, nullptr, nullptr, w.Lp, g.T);
         if ((rc = launch_status("lovasz sort scan launch")) != B200_OK) return rc;
-        sort_scatter_kernel<<<nblk, kScatThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, w.Lp, w.tilemap,
-                                                                     w.n_tiles, w.direct, tickets + pass, g.L, g.T,
-                                                                     shift, pass == 0 ? 1 : 0);
+        sort_scatter_kernel<<<nblk, kScatThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, w.tilemap,
+                                                                     w.n_tiles, tickets + pass, g.L, g.T, shift,
+                                                                     pass == 0 ? 1 : 0);
         if ((rc = launch_status("lovasz sort scatter launch")) != B200_OK) return rc;
         std::swap(kin, kout);
         std::swap(vin, vout);
     }
     {
         const int shift = 1 + (kPasses - 1) * kBits;
-        sort_hist_kernel<true><<<nblk_hist, kSortThreads, 0, s>>>(kin, w.hist, w.fghist, w.Lp, w.tilemap, w.n_tiles,
-                                                                 kout, w.direct, g.L, g.T, shift);
+        sort_hist_kernel<true><<<nblk_hist, kSortThreads, 0, s>>>(kin, w.hist, w.fghist, w.tilemap, w.n_tiles, kout,
+                                                                 g.L, g.T, shift);
         if ((rc = launch_status("lovasz last histogram launch")) != B200_OK) return rc;
         sort_scan_kernel<true><<<unsigned(g.S), kBins, 0, s>>>(w.hist, w.fghist, w.n_pos, w.Lp, g.T);
         if ((rc = launch_status("lovasz last scan launch")) != B200_OK) return rc;
-        rank_jaccard_kernel<<<nblk, kSortThreads, kJaccardSmem, s>>>(kin, vin, kout, vout, w.direct, w.hist, w.fghist,
+        rank_jaccard_kernel<<<nblk, kSortThreads, kJaccardSmem, s>>>(kin, vin, kout, vout, w.hist, w.fghist,
                                                                       w.n_pos, jacc,
-                                                                      w.partial, w.Lp, w.tilemap, w.n_tiles,
+                                                                      w.partial, w.tilemap, w.n_tiles,
                                                                       tickets + 2, g.L, g.T, shift);
         if ((rc = launch_status("lovasz rank+jaccard launch")) != B200_OK) return rc;
     }
