@@ -357,6 +357,7 @@ struct PairLayout {
     int box_elems;          // floats of one box (C * 256)
     uint32_t tile_bytes;    // one C x 512 fp32 tile
     uint32_t label_off;     // byte offset of the labels inside a stage
+    uint32_t coord_off;     // (image, first pixel) of the tile, written by the loader
     uint32_t stage_bytes;
 };
 
@@ -365,7 +366,8 @@ __host__ __device__ inline PairLayout pair_layout(int C, bool bwd) {
     l.box_elems = C * kPairTP;
     l.tile_bytes = uint32_t(C) * kPairTile * 4u;
     l.label_off = (bwd ? 2u : 1u) * l.tile_bytes;          // multiples of 2 KB: 128-byte aligned
-    l.stage_bytes = l.label_off + kPairTile * 8u;
+    l.coord_off = l.label_off + kPairTile * 8u;
+    l.stage_bytes = l.coord_off + 128u;                     // stages stay 128-byte aligned
     return l;
 }
 
@@ -409,6 +411,7 @@ lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUten
             if (npix > kPairTile) npix = kPairTile;
             const int nbx = int((npix + kPairTP - 1) / kPairTP);
             const uint32_t label_bytes = uint32_t(npix) * 8u;        // M % 4 == 0: a multiple of 16
+            *reinterpret_cast<int2 *>(stage + lay.coord_off) = make_int2(int(n), int(p0));
             mbar_expect_tx(&bars.full[s], uint32_t(nbx) * (BWD ? 2u : 1u) * (lay.tile_bytes / 2) + label_bytes);
             for (int bx = 0; bx < nbx; ++bx) {
                 tma_load_3d(lt + size_t(bx) * lay.box_elems, &map_logits, int(p0) + bx * kPairTP, 0, int(n),
@@ -457,15 +460,22 @@ lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUten
         int k = 0;
         for (int64_t t = first; t < total_tiles; t += stride, ++k) {
             const int s = k % NS;
-            const int64_t n = t / tiles_per_image;
-            const int64_t px0 = (t % tiles_per_image) * kPairTile + pix;
-            if (!BWD && g.per_image && n != cur_n && cur_n >= 0) flush_trackers(cur_n);
-            cur_n = n;
             bool ok = true;
             if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, a.status);
-            if (!compute_all(ok, kTileCompute)) break;
-
+            // keys: the tracker flushes below meet at a block barrier, so the warps give up together;
+            // backward: a warp owns whole pixel columns and decides for itself
+            if (BWD) {
+                if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            } else if (!compute_all(ok, kTileCompute)) {
+                break;
+            }
             unsigned char *stage = base + size_t(s) * lay.stage_bytes;
+            const int2 coord = *reinterpret_cast<const int2 *>(stage + lay.coord_off);
+            const int64_t n = coord.x;
+            const int64_t px0 = int64_t(coord.y) + pix;
+            if (!BWD && g.per_image && n != cur_n && cur_n >= 0) flush_trackers(cur_n);
+            cur_n = n;
+
             const int64_t *tile_labels = reinterpret_cast<const int64_t *>(stage + lay.label_off);
             bool valid[2];
             int lbi[2];
@@ -529,7 +539,7 @@ lovasz_pair_kernel(const TileArgs a, const int NS, const __grid_constant__ CUten
                         }
                     }
                 };
-                if ((t % tiles_per_image) % kSampleEvery == 0) key_sweep(std::true_type{});
+                if ((coord.y / kPairTile) % kSampleEvery == 0) key_sweep(std::true_type{});
                 else key_sweep(std::false_type{});
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {

@@ -464,9 +464,12 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
     const int NBX = prm.nbx, TPT = TP * NBX;        // a tile is NBX boxes of TP pixels side by side
     const int box_elems = prm.rows * TP;            // elements of one box in shared memory
     unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
-    // a stage = the logits tile followed by the tile's TP labels (both arrive by bulk copy)
+    // a stage = the logits tile followed by the tile's TP labels (both arrive by bulk copy) and
+    // the tile's coordinates (image, first pixel), which the loader writes: the compute threads
+    // then need no 64-bit division per tile
     const size_t label_off = (size_t(prm.rows) * TPT * sizeof(T) + 127) & ~size_t(127);
-    const size_t stage_bytes = label_off + size_t(TPT) * sizeof(int64_t);
+    const size_t coord_off = label_off + size_t(TPT) * sizeof(int64_t);
+    const size_t stage_bytes = coord_off + 128;          // keeps every stage 128-byte aligned
     float *red = reinterpret_cast<float *>(base + NS * stage_bytes);   // [5 words][slices][TP]
     const int tid = threadIdx.x;
     unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
@@ -488,6 +491,7 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
             if (npix > TPT) npix = TPT;
             const int nbx = int((npix + TP - 1) / TP);                       // boxes that hold pixels
             const uint32_t label_bytes = uint32_t(npix) * sizeof(int64_t);   // M % 4 == 0: multiple of 16
+            *reinterpret_cast<int2 *>(base + s * stage_bytes + coord_off) = make_int2(int(n), int(p0));
             mbar_expect_tx(&bars.full[s], nbx * box_bytes + label_bytes);
             for (int bx = 0; bx < nbx; ++bx)
                 for (int b = 0; b < prm.nbox; ++b)
@@ -533,11 +537,18 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
         int k = 0;
         for (int64_t t = first; t < prm.total_tiles; t += stride, ++k) {
             const int s = k % NS;
-            const int64_t n = t / prm.tiles_per_image;
-            const int64_t px0 = (t % prm.tiles_per_image) * TPT + pix;
             bool ok = true;
             if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
-            if (!compute_all(ok, kTileCompute)) break;
+            // Slices that exchange statistics must give up together (their named barriers have
+            // no time limit); a warp that owns whole pixel columns can decide for itself.
+            if (KS == 1) {
+                if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            } else if (!compute_all(ok, kTileCompute)) {
+                break;
+            }
+            const int2 coord = *reinterpret_cast<const int2 *>(base + s * stage_bytes + coord_off);
+            const int64_t n = coord.x;
+            const int64_t px0 = int64_t(coord.y) + pix;
 
             const int64_t *tile_labels = reinterpret_cast<const int64_t *>(base + s * stage_bytes + label_off);
             int lbi[2];
@@ -1107,8 +1118,8 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
         if (tma_ok) {
             // statistics exchange area: 5 words x (slices * TP = 2 * 256) floats
             const size_t xchg_bytes = size_t(5) * kTileCompute * 2 * sizeof(float);
-            // a stage holds the logits tile and the tile's labels
-            const size_t stage_bytes = tile_bytes + size_t(TPT) * sizeof(int64_t);
+            // a stage holds the logits tile, the tile's labels and its coordinates
+            const size_t stage_bytes = tile_bytes + size_t(TPT) * sizeof(int64_t) + 128;
             int stages = tune_int("B200_STAGES", default_stages);
             while (stages > 1 && 128 + stages * stage_bytes + xchg_bytes > kSmemLimit) --stages;
             if (stages > kMaxStages) stages = kMaxStages;
