@@ -789,6 +789,223 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
     if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
 }
 
+// ---------------------------------------------------- many channels, forward: chunked sweep
+//
+// Forward for class counts whose full tile does not fit beside a second one in shared memory
+// (where tile_pair_kernel has to split the channels over warps and exchange statistics at
+// block barriers).  Here a tile is 512 pixels wide and streams through the ring in chunks of
+// kChunkCh channels; a thread owns two adjacent pixels over ALL channels and carries their
+// running statistics in registers (online softmax: when the maximum moves, the sums are
+// rescaled once per group of 8 channels), so there is no inter-warp exchange, no block
+// barrier, and every element is read from shared memory once.
+// Large margin leaves the target out of its sums: when the chunk with a pixel's label channel
+// arrives, the thread saves that logit and overwrites it with a copy of another channel
+// (channel 0, or 1 when the label is 0); the copy's terms are subtracted at the end, which
+// cannot cancel (s' contains that channel's own term, and all d*e terms have one sign).
+constexpr int kChunkCh = 16;
+constexpr int kChunkGroup = 8;
+constexpr int kChunkTP = 256;
+constexpr int kChunkTile = 2 * kChunkTP;
+
+struct ChunkLayout {
+    uint32_t box_elems;     // elements of one box (kChunkCh x 256)
+    uint32_t label_off, coord_off, stage_bytes;
+};
+template <typename T> __host__ __device__ inline ChunkLayout chunk_layout() {
+    ChunkLayout l;
+    l.box_elems = kChunkCh * kChunkTP;
+    l.label_off = 2u * l.box_elems * uint32_t(sizeof(T));       // a multiple of 128
+    l.coord_off = l.label_off + kChunkTile * 8u;
+    l.stage_bytes = l.coord_off + 128u;
+    return l;
+}
+
+template <typename T, int KIND, bool REDUCE>
+__global__ void __launch_bounds__(kTileBlock)
+tile_chunk_fwd_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap map_in) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ PipeBarriers bars;
+    __shared__ double sh_red[64];
+    const int C = static_cast<int>(prm.C), NS = prm.stages;
+    const ChunkLayout lay = chunk_layout<T>();
+    unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    const int tid = threadIdx.x;
+    unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
+    const int nchunks = (C + kChunkCh - 1) / kChunkCh;
+    const int64_t tiles_per_image = (prm.M + kChunkTile - 1) / kChunkTile;
+    const int64_t total_tiles = prm.N * tiles_per_image;
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+    double acc_loss = 0.0, acc_cnt = 0.0;
+
+    pipe_init<kTileCompute, false>(bars, NS);
+
+    if (tid == kTileCompute) {
+        int k = 0;
+        for (int64_t t = first; t < total_tiles; t += stride) {
+            const int64_t n = t / tiles_per_image;
+            const int64_t p0 = (t % tiles_per_image) * kChunkTile;
+            int64_t npix = prm.M - p0;
+            if (npix > kChunkTile) npix = kChunkTile;
+            const int nbx = int((npix + kChunkTP - 1) / kChunkTP);
+            const uint32_t label_bytes = uint32_t(npix) * 8u;       // M % 4 == 0: a multiple of 16
+            bool alive = true;
+            for (int c = 0; c < nchunks && alive; ++c, ++k) {
+                const int s = k % NS;
+                if (k >= NS && !mbar_wait_bounded(&bars.empty[s], ((k / NS) - 1) & 1, status)) {
+                    alive = false;
+                    break;
+                }
+                unsigned char *stage = base + size_t(s) * lay.stage_bytes;
+                *reinterpret_cast<int4 *>(stage + lay.coord_off) = make_int4(int(n), int(p0), c, 0);
+                mbar_expect_tx(&bars.full[s],
+                               uint32_t(nbx) * lay.box_elems * uint32_t(sizeof(T)) + (c == 0 ? label_bytes : 0u));
+                for (int bx = 0; bx < nbx; ++bx)
+                    tma_load_3d(reinterpret_cast<T *>(stage) + size_t(bx) * lay.box_elems, &map_in,
+                                int(p0) + bx * kChunkTP, c * kChunkCh, int(n), &bars.full[s]);
+                if (c == 0) bulk_load_1d(stage + lay.label_off, prm.labels + n * prm.M + p0, label_bytes, &bars.full[s]);
+            }
+            if (!alive) break;
+        }
+    } else if (tid < kTileCompute) {
+        const int lane = tid & 31;
+        const int pix = tid * 2;
+        const int bxo = (pix / kChunkTP) * int(lay.box_elems) + (pix % kChunkTP);
+        T *losses = static_cast<T *>(prm.losses);
+        const LossConsts kc = prm.k;
+        float acc32 = 0.f;
+        int cnt32 = 0;
+        int k = 0;
+        bool alive = true;
+        for (int64_t t = first; t < total_tiles && alive; t += stride) {
+            int lbi[2] = {-1, -1};
+            bool inb[2] = {false, false};
+            int64_t n = 0, px0 = 0;
+            float2 m = splat2(kNegInf), sum = splat2(0.f), sde = splat2(0.f), sx = splat2(0.f);
+            float2 xl = splat2(0.f), xo = splat2(0.f);
+            for (int c = 0; c < nchunks; ++c, ++k) {
+                const int s = k % NS;
+                bool ok = true;
+                if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
+                if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                    alive = false;
+                    break;
+                }
+                unsigned char *stage = base + size_t(s) * lay.stage_bytes;
+                T *mine = reinterpret_cast<T *>(stage) + bxo;
+                const int c0 = c * kChunkCh;
+                const int nch = min(kChunkCh, C - c0);
+                if (c == 0) {
+                    const int4 coord = *reinterpret_cast<const int4 *>(stage + lay.coord_off);
+                    n = coord.x;
+                    px0 = int64_t(coord.y) + pix;
+                    const int64_t *tile_labels = reinterpret_cast<const int64_t *>(stage + lay.label_off);
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        inb[i] = px0 + i < prm.M;
+                        const int64_t lb = inb[i] ? tile_labels[pix + i] : prm.ignore;
+                        const bool valid = inb[i] && lb != prm.ignore;
+                        lbi[i] = valid ? ((lb >= 0 && lb < C) ? int(lb) : -2) : -1;
+                    }
+                    if (KIND == kLMargin) {
+                        // the stand-in for the target: channel 0, or 1 when the label is 0
+                        xo.x = to_f32(mine[(lbi[0] == 0 ? 1 : 0) * kChunkTP]);
+                        xo.y = to_f32(mine[(lbi[1] == 0 ? 1 : 0) * kChunkTP + 1]);
+                    }
+                }
+                // the label channel of my pixels, if it is in this chunk
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int j = lbi[i] - c0;
+                    if (lbi[i] >= 0 && j >= 0 && j < kChunkCh) {
+                        T *e = mine + j * kChunkTP + i;
+                        if (i == 0) xl.x = to_f32(*e); else xl.y = to_f32(*e);
+                        if (KIND == kLMargin) *e = from_f32<T>(i == 0 ? xo.x : xo.y);
+                    }
+                }
+                for (int g0 = 0; g0 < nch; g0 += kChunkGroup) {
+                    const int ng = min(kChunkGroup, nch - g0);
+                    pk_t x[kChunkGroup];
+                    float2 mn = m;
+#pragma unroll
+                    for (int q = 0; q < kChunkGroup; ++q) {
+                        // (channels past the end of the group repeat its first one: harmless for
+                        // the maximum, and the sums below stop at ng)
+                        x[q] = ld_pk(mine + (g0 + (q < ng ? q : 0)) * kChunkTP);
+                        mn = max2(mn, upk2(x[q]));
+                    }
+                    // rescale what has been summed so far to the new maximum
+                    const float2 dm = make_float2(m.x - mn.x, m.y - mn.y);
+                    const float2 r = ex2_2(mul2(dm, splat2(kLog2e)));
+                    if (KIND == kLMargin) sde = mul2(r, fma2(dm, sum, sde));
+                    sum = mul2(sum, r);
+                    m = mn;
+                    const pk_t nml = pk2(mul2(mn, splat2(-kLog2e))), l2e = psplat(kLog2e), negm = pk2(make_float2(-mn.x, -mn.y));
+                    pk_t psum = pk2(sum), psde = pk2(sde), psx = pk2(sx);
+#pragma unroll
+                    for (int q = 0; q < kChunkGroup; ++q) {
+                        if (q < ng) {
+                            const pk_t e = pex2(pfma(x[q], l2e, nml));
+                            psum = padd(psum, e);
+                            if (KIND == kLMargin) psde = pfma(padd(x[q], negm), e, psde);
+                            psx = padd(psx, x[q]);
+                        }
+                    }
+                    sum = upk2(psum);
+                    sde = upk2(psde);
+                    sx = upk2(psx);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.empty[s]);
+            }
+            if (!alive) break;
+            // ---- per pixel: closed forms
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (!inb[i]) continue;
+                const float mi = i ? m.y : m.x, si = i ? sum.y : sum.x, sxi = i ? sx.y : sx.x;
+                const float xli = lbi[i] >= 0 ? (i ? xl.y : xl.x) : 0.f;
+                float l = 0.f;
+                if (lbi[i] != -1) {
+                    if (KIND == kLSR) {
+                        l = kc.sumy * (mi + __logf(si)) - kc.lb_neg * sxi - (kc.lb_pos - kc.lb_neg) * xli;
+                    } else {
+                        // take the stand-in's terms back out (no label channel: nothing was replaced)
+                        const bool repl = lbi[i] >= 0;
+                        const float ci = i ? xo.y : xo.x;
+                        const float dc = ci - mi;
+                        const float ec = repl ? ex2f(dc * kLog2e) : 0.f;
+                        const float s_no = si - ec;
+                        const float sde_no = (i ? sde.y : sde.x) - (repl ? dc * ec : 0.f);
+                        const float nother = repl ? float(C - 1) : float(C);
+                        const float sd = (sxi - (repl ? ci : 0.f)) - nother * mi;
+                        const float inv_s = __fdividef(1.f, s_no);
+                        const float sqx = sde_no * inv_s;
+                        const float mm = fmaxf(mi, xli);
+                        const float e_no = s_no * ex2f((mi - mm) * kLog2e);
+                        const float e_lb = repl ? ex2f((xli - mm) * kLog2e) : 0.f;
+                        const float s_all = e_no + e_lb;
+                        l = (mm + __logf(s_all)) - xli + kc.half_lam * (sqx - kc.a * sd);
+                    }
+                }
+                if (losses) losses[n * prm.M + px0 + i] = from_f32<T>(l);
+                if (REDUCE && lbi[i] != -1) {
+                    acc32 += l;
+                    cnt32 += 1;
+                }
+            }
+            if (REDUCE && cnt32 >= 32) {
+                acc_loss += double(acc32);
+                acc_cnt += double(cnt32);
+                acc32 = 0.f;
+                cnt32 = 0;
+            }
+        }
+        acc_loss += double(acc32);
+        acc_cnt += double(cnt32);
+    }
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+}
+
 // Pair q of a 16-byte register vector as two floats, and back.
 __device__ __forceinline__ float2 pair_of(const Vec16<float> &v, int q) { return make_float2(v.v[2 * q], v.v[2 * q + 1]); }
 __device__ __forceinline__ float2 pair_of(const Vec16<__half> &v, int q) {
@@ -1109,6 +1326,36 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
         prm.rows = prm.nbox * prm.CB;
         // few channels: two boxes side by side, so that one thread pair-column spans all channels
         prm.nbx = (tma_ok && TP == 256 && 2 * size_t(prm.rows) * TP * es <= size_t(40) * 1024 && prm.M > TP) ? 2 : 1;
+        if constexpr (!BWD) {
+            // many channels, forward: 512-pixel tiles streamed in channel chunks (no slice exchange)
+            if (tma_ok && (prm.nbx == 1 || getenv("B200_FORCE_CHUNK")) && prm.M >= kChunkTile &&
+                !getenv("B200_NO_CHUNK")) {
+                const ChunkLayout lay = chunk_layout<T>();
+                // measured on config 3 (C = 150): 2 stages x 3 blocks per SM 206 us, 3 stages x 2 blocks 222 us
+                int stages = tune_int("B200_CHUNK_STAGES", 2);
+                if (stages > kMaxStages) stages = kMaxStages;
+                prm.stages = stages;
+                const size_t smem = 128 + size_t(stages) * lay.stage_bytes;
+                int per_sm = int((224 * 1024) / (smem + 1024));
+                const int cap_sm = tune_int("B200_CHUNK_CTAS", 3);
+                if (per_sm > cap_sm) per_sm = cap_sm;
+                if (per_sm < 1) per_sm = 1;
+                const int64_t tiles = prm.N * ((prm.M + kChunkTile - 1) / kChunkTile);
+                int64_t grid = int64_t(sms) * per_sm;
+                if (grid > tiles) grid = tiles;
+                if (grid > kMaxPartials) grid = kMaxPartials;
+                CUtensorMap map_in{};
+                const uint64_t dims[3] = {uint64_t(prm.M), uint64_t(prm.C), uint64_t(prm.N)};
+                const uint64_t strides[3] = {es, uint64_t(prm.M) * es, uint64_t(prm.C) * prm.M * es};
+                const uint32_t box[3] = {uint32_t(kChunkTP), uint32_t(kChunkCh), 1u};
+                if (!encode_tensor_map(&map_in, dtype, prm.logits, 3, dims, strides, box)) return B200_ERR_LAUNCH;
+                auto kern = tile_chunk_fwd_kernel<T, KIND, REDUCE>;
+                int rc2;
+                if ((rc2 = set_smem(kern, smem)) != B200_OK) return rc2;
+                kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in);
+                return launch_status("softmax chunked forward kernel launch");
+            }
+        }
         const int TPT = TP * prm.nbx;
         prm.tiles_per_image = (prm.M + TPT - 1) / TPT;
         prm.total_tiles = prm.N * prm.tiles_per_image;

@@ -18,6 +18,9 @@ SHAPES = [
     (2, 33, (17,)), (2, 64, (8, 12)), (2, 150, (24, 24)), (1, 150, (13, 11)), (1, 256, (16, 8)),
     (1, 257, (8, 8)), (1, 500, (6, 10)), (4, 19, (300, 300)),
     (6, 5, ()), (16, 19, ()), (5, 300, ()), (3, 1000, ()), (2, 4099, ()), (2, 2000, (3, 5)),
+    # forward in channel chunks (more than 20 classes, >= 512 pixels): last chunk of 9 / 1 / 5 channels,
+    # ragged second box, several tiles per image
+    (2, 41, (20, 30)), (1, 33, (16, 36)), (3, 21, (26, 30)), (1, 150, (40, 52)),
 ]
 
 
@@ -138,8 +141,9 @@ def test_large_margin_fb_function_returns_count():
 
 
 @pytest.mark.parametrize("kind", ["lsr", "lmargin"])
-@pytest.mark.parametrize("shape", [(2, 19, (16, 24)), (3, 150, (8, 8)), (4, 4096, ()), (2, 21, (5, 7))],
-                         ids=["tile19", "tile150", "rows4096", "unaligned"])
+@pytest.mark.parametrize("shape", [(2, 19, (16, 24)), (3, 150, (8, 8)), (4, 4096, ()), (2, 21, (5, 7)),
+                                   (2, 150, (24, 28)), (1, 45, (32, 40))],
+                         ids=["tile19", "tile150", "rows4096", "unaligned", "chunks150", "chunks45"])
 def test_fp16_io(kind, shape):
     n, c, sp = shape
     g = torch.Generator().manual_seed(10)
