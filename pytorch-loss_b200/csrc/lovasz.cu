@@ -1185,7 +1185,7 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__re
         const bool fg = key_is_fg(kr);
         const uint32_t fgball = __ballot_sync(0xffffffffu, fg);
         uint32_t peers;
-        const uint32_t fgold_src = wfg[d];            // read before any leader updates it this round
+        const uint32_t fgold_src = wfg[d];            // read before any leader updates it in this ranking round
         const uint32_t rk = rank_round(d, wcnt, lane, lt, peers);
         const int leader = __ffs(peers) - 1;
         const uint32_t fgold = fgold_src;            // every peer read the same word

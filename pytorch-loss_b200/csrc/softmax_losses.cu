@@ -423,6 +423,18 @@ __device__ __forceinline__ float2 slice_combine(float2 v, float *area, int ks, i
     return r;
 }
 
+// The first exchange of a tile also carries the slices' decision on the tile's arrival: its
+// barrier is the AND-reducing one, so a timed-out wait is decided by all slices together
+// without a barrier of its own.  `ok` comes back as the common decision.
+__device__ __forceinline__ float2 slice_combine_max_first(float2 v, float *area, int ks, int KS, int TP, int pix,
+                                                          bool &ok) {
+    st_pair(area + ks * TP + pix, v);
+    ok = compute_all(ok, kTileCompute);
+    float2 r = ld_pair(area + pix);
+    for (int q = 1; q < KS; ++q) r = max2(r, ld_pair(area + q * TP + pix));
+    return r;
+}
+
 // Sums of two / three statistics across the slices with ONE barrier.
 __device__ __forceinline__ void slice_sum2(float2 &a, float2 &b, float *area, int plane, int ks, int KS,
                                            int TP, int pix) {
@@ -539,13 +551,11 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
             const int s = k % NS;
             bool ok = true;
             if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
-            // Slices that exchange statistics must give up together (their named barriers have
-            // no time limit); a warp that owns whole pixel columns can decide for itself.
-            if (KS == 1) {
-                if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-            } else if (!compute_all(ok, kTileCompute)) {
-                break;
-            }
+            // A warp that owns whole pixel columns decides for itself.  Slices that exchange
+            // statistics must give up together (their named barriers have no time limit): they
+            // agree at the tile's first exchange, whose barrier carries the decision.
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (KS == 1 && !ok) break;
             const int2 coord = *reinterpret_cast<const int2 *>(base + s * stage_bytes + coord_off);
             const int64_t n = coord.x;
             const int64_t px0 = int64_t(coord.y) + pix;
@@ -580,7 +590,10 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
 #pragma unroll 4
                     for (int j = ks; j < C; j += KS, q += step) m = max2(m, ld_pair(q));
                 }
-                if (KS > 1) m = slice_combine<true>(m, red, ks, KS, TPT, pix);
+                if (KS > 1) {
+                    m = slice_combine_max_first(m, red, ks, KS, TPT, pix, ok);
+                    if (!ok) break;
+                }
                 // target logits (forward only; backward overwrites the tile with e^{x-m})
                 float2 xl = splat2(0.f);
                 if (!BWD && ks == 0) {
@@ -678,7 +691,8 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     // the owner publishes x_lb ahead of the max exchange's barrier; all read it after
                     if (own0) red[plane + pix] = xl.x;
                     if (own1) red[plane + pix + 1] = xl.y;
-                    m = slice_combine<true>(m, red, ks, KS, TPT, pix);
+                    m = slice_combine_max_first(m, red, ks, KS, TPT, pix, ok);
+                    if (!ok) break;
                     xl.x = lbi[0] >= 0 ? red[plane + pix] : 0.f;
                     xl.y = lbi[1] >= 0 ? red[plane + pix + 1] : 0.f;
                 }
@@ -1134,12 +1148,23 @@ rows_pipe_kernel(const SoftmaxParams prm) {
             } else if (!BWD && tid == 0 && lbi >= 0) {
                 xl = to_f32(row[lbi]);
             }
-            // ---- phase 1: maximum
+            // ---- phase 1: maximum (half rows: on the packed halves, exact and four values per
+            // instruction-pair instead of a conversion and a compare each)
             float2 m2 = splat2(kNegInf);
-            for (int v = tid; v < nvec; v += kRowsCompute) {
-                const V xv = *reinterpret_cast<const V *>(row + v * VN);
+            if constexpr (sizeof(T) == 2) {
+                __half2 hm = __float2half2_rn(-65504.f);
+                for (int v = tid; v < nvec; v += kRowsCompute) {
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(row + v * VN);
+                    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+                    hm = __hmax2(__hmax2(hm, h[0]), __hmax2(h[1], __hmax2(h[2], h[3])));
+                }
+                m2 = __half22float2(hm);
+            } else {
+                for (int v = tid; v < nvec; v += kRowsCompute) {
+                    const V xv = *reinterpret_cast<const V *>(row + v * VN);
 #pragma unroll
-                for (int q = 0; q < NP; ++q) m2 = max2(m2, pair_of(xv, q));
+                    for (int q = 0; q < NP; ++q) m2 = max2(m2, pair_of(xv, q));
+                }
             }
             float red1[2] = {fmaxf(m2.x, m2.y), xl};
             if (KIND == kLMargin) {

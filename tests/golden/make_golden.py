@@ -66,7 +66,9 @@ def labels_with_ignores(gen, shape, n_classes, ignore_index, frac):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PYTORCH_LOSS_REFERENCE", "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PYTORCH_LOSS_REFERENCE")
+    if not root:
+        sys.exit("usage: make_golden.py <checkout of CoinCheung/pytorch-loss>  (or set PYTORCH_LOSS_REFERENCE)")
     ref = load_reference(root)
     torch.set_num_threads(1)
     out = {}
