@@ -58,8 +58,9 @@ def test_golden(golden_dir):
         assert_grad_close(grad, torch.from_numpy(z[f"c{i}_grad_per_image"]), what=f"c{i} per-image grad")
 
 
-def test_multi_tile_segments_and_blocky_labels():
-    """Segments longer than one sort tile (8192 pixels), realistic label maps, absent classes."""
+def test_multi_tile_segments_and_blocky_labels(monkeypatch):
+    """Segments longer than one sort tile (8192 pixels), realistic label maps, absent classes; the
+    pruned sort against the sort of every element."""
     import pytorch_loss as P
     from oracle import losses as O
     g = torch.Generator().manual_seed(77)
@@ -67,9 +68,15 @@ def test_multi_tile_segments_and_blocky_labels():
     labels = _blocky_labels(g, 2, 17, 160, 200, 32, 255, 0.03)      # classes 17, 18 never occur
     for per_image in (False, True):
         want_loss, want_grad = O.lovasz_softmax(logits, labels, 255, 'none', per_image, dtype=torch.float64)
-        loss, grad = run_module(P.LovaszSoftmaxV3('none', 255, per_image=per_image), logits.cuda(), labels.cuda())
+        crit = P.LovaszSoftmaxV3('none', 255, per_image=per_image)
+        loss, grad = run_module(crit, logits.cuda(), labels.cuda())
         assert_loss_close(loss, want_loss.float(), atol=1e-6)
         assert_grad_close(grad, want_grad.float())
+        monkeypatch.setenv("B200_LOVASZ_NO_PRUNE", "1")
+        loss_full, grad_full = run_module(crit, logits.cuda(), labels.cuda())
+        monkeypatch.delenv("B200_LOVASZ_NO_PRUNE")
+        assert_loss_close(loss_full, loss, atol=1e-6)
+        assert torch.equal(grad_full, grad)
 
 
 def test_pruned_sort_cases(monkeypatch):
