@@ -238,6 +238,20 @@ int b200_ohem_label(const void *logits, const int64_t *labels, int64_t *out_labe
                     int dtype, int64_t ignore_index, float score_thresh, int64_t n_min,
                     void *stream);
 
+/* ---------------------------------------------------------- Taylor softmax ---
+ * Softmax with e^x replaced by its Taylor polynomial of even order n,
+ * f(x) = sum_{i<=n} x^i / i!, over the middle dimension of feat viewed as [N, C, M]:
+ * out = f / sum_C f (use_log: its logarithm).  Replaces
+ * taylor_softmax_cpp.taylor_softmax_forward / taylor_softmax_backward (reference
+ * csrc/taylor_softmax.cu:391-421; kernels :50-265).  2 <= n <= 16, n even.
+ * backward: grad_feat = d sum(out * grad) / d feat; grad has the shape and dtype of feat.
+ */
+int b200_taylor_softmax_forward(const void *feat, void *out, int64_t N, int64_t C, int64_t M,
+                                int dtype, int n, int use_log, void *stream);
+int b200_taylor_softmax_backward(const void *grad, const void *feat, void *grad_feat, int64_t N,
+                                 int64_t C, int64_t M, int dtype, int n, int use_log,
+                                 void *stream);
+
 #ifdef __cplusplus
 }
 #endif

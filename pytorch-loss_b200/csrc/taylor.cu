@@ -1,0 +1,251 @@
+// Taylor softmax / log-Taylor softmax over one dimension of a tensor (sm_100a).
+//
+// What is computed (reference csrc/taylor_softmax.cu:50-265, host side :268-417; Python
+// taylor_softmax.py:15-50): with f(x) = sum_{i=0..n} x^i / i!  (n even, so f > 0),
+//   forward   out_j = f(x_j) / S,  S = sum_j f(x_j)           (use_log: log f(x_j) - log S)
+//   backward  softmax: dx_k = f'(x_k)/S * (g_k - sum_j g_j out_j)
+//             log    : dx_k = f'(x_k) * (g_k / f(x_k) - (sum_j g_j) / S),   f' = sum_{i<n} x^i/i!
+// over the dimension `dim` of a tensor viewed as [N, C, M] (N = product of the leading
+// sizes, C = size(dim), M = product of the trailing sizes).
+//
+// How: the op streams x (and g) once from HBM and writes once; there is no exponential.
+//   M > 1   a thread owns 4 adjacent positions along M (16-byte accesses when the layout
+//           allows, else one position) and walks the C channels twice: sums first, outputs
+//           second; the second walk finds its lines in L1/L2 (a block's working set is C x 4 KB).
+//   M == 1  a warp owns a row: lanes stride over the channels, warp-shuffle sums.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kTaylorThreads = 256;
+constexpr int kMaxOrder = 16;
+
+struct TaylorParams {
+    const void *x;
+    const void *g;        // backward only
+    void *out;
+    int64_t N, C, M;
+    int order;            // n
+};
+
+// f (degree n) and, if wanted, f' (degree n - 1) by Horner's rule.  ORDER > 0: compile-time
+// order (the loops unroll and 1/i become immediates); ORDER == 0: the order comes from p.
+template <int ORDER, bool WANT_D>
+__device__ __forceinline__ void taylor_poly(float x, const TaylorParams &p, float &f, float &d) {
+    if constexpr (ORDER > 0) {
+        float a = 1.f;
+#pragma unroll
+        for (int i = ORDER; i >= 1; --i) a = fmaf(a, x * (1.f / float(i)), 1.f);
+        f = a;
+        if (WANT_D) {
+            float b = 1.f;
+#pragma unroll
+            for (int i = ORDER - 1; i >= 1; --i) b = fmaf(b, x * (1.f / float(i)), 1.f);
+            d = b;
+        }
+    } else {
+        float a = 1.f;
+        for (int i = p.order; i >= 1; --i) a = fmaf(a, x * __frcp_rn(float(i)), 1.f);
+        f = a;
+        if (WANT_D) {
+            float b = 1.f;
+            for (int i = p.order - 1; i >= 1; --i) b = fmaf(b, x * __frcp_rn(float(i)), 1.f);
+            d = b;
+        }
+    }
+}
+
+template <typename T, int VEC> struct Pack;
+template <> struct Pack<float, 4> {
+    static __device__ __forceinline__ void load(const float *p, float (&v)[4]) {
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(p));
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[4]) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
+    }
+};
+template <typename T> struct Pack<T, 1> {
+    static __device__ __forceinline__ void load(const T *p, float (&v)[1]) { v[0] = to_f32(*p); }
+    static __device__ __forceinline__ void store(T *p, const float (&v)[1]) { *p = from_f32<T>(v[0]); }
+};
+
+// M > 1: VEC adjacent positions per thread, two walks over the channels.
+template <typename T, int VEC, bool BWD, bool LOG, int ORDER>
+__global__ void __launch_bounds__(kTaylorThreads)
+taylor_spatial_kernel(const TaylorParams p) {
+    const T *x = static_cast<const T *>(p.x);
+    const T *g = static_cast<const T *>(p.g);
+    T *out = static_cast<T *>(p.out);
+    const int64_t groups_per_row = p.M / VEC;          // VEC > 1 only when M % VEC == 0
+    const int64_t groups = p.N * groups_per_row;
+    const int64_t stride = int64_t(gridDim.x) * kTaylorThreads;
+    for (int64_t gi = int64_t(blockIdx.x) * kTaylorThreads + threadIdx.x; gi < groups; gi += stride) {
+        const int64_t n = gi / groups_per_row, m0 = (gi % groups_per_row) * VEC;
+        const int64_t base = n * p.C * p.M + m0;
+        float S[VEC], A[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) S[v] = A[v] = 0.f;
+#pragma unroll 4
+        for (int64_t j = 0; j < p.C; ++j) {
+            float xv[VEC], gv[VEC];
+            Pack<T, VEC>::load(x + base + j * p.M, xv);
+            if (BWD) Pack<T, VEC>::load(g + base + j * p.M, gv);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                float f, d;
+                taylor_poly<ORDER, false>(xv[v], p, f, d);
+                S[v] += f;
+                if (BWD) A[v] += LOG ? gv[v] : gv[v] * f;      // log: sum g;  softmax: sum g f
+            }
+        }
+        float invS[VEC], logS[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            invS[v] = 1.f / S[v];
+            logS[v] = LOG && !BWD ? logf(S[v]) : 0.f;
+        }
+#pragma unroll 4
+        for (int64_t j = 0; j < p.C; ++j) {
+            float xv[VEC], gv[VEC], ov[VEC];
+            Pack<T, VEC>::load(x + base + j * p.M, xv);
+            if (BWD) Pack<T, VEC>::load(g + base + j * p.M, gv);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+                float f, d;
+                taylor_poly<ORDER, BWD>(xv[v], p, f, d);
+                if (!BWD) ov[v] = LOG ? logf(f) - logS[v] : f * invS[v];
+                else if (LOG) ov[v] = d * (gv[v] / f - A[v] * invS[v]);
+                else ov[v] = d * invS[v] * (gv[v] - A[v] * invS[v]);
+            }
+            Pack<T, VEC>::store(out + base + j * p.M, ov);
+        }
+    }
+}
+
+// M == 1: one warp per row.
+template <typename T, bool BWD, bool LOG, int ORDER>
+__global__ void __launch_bounds__(kTaylorThreads)
+taylor_rows_kernel(const TaylorParams p) {
+    const T *x = static_cast<const T *>(p.x);
+    const T *g = static_cast<const T *>(p.g);
+    T *out = static_cast<T *>(p.out);
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = int64_t(gridDim.x) * (kTaylorThreads / 32);
+    for (int64_t r = int64_t(blockIdx.x) * (kTaylorThreads / 32) + (threadIdx.x >> 5); r < p.N; r += warps) {
+        const T *xr = x + r * p.C;
+        const T *gr = BWD ? g + r * p.C : nullptr;
+        float S = 0.f, A = 0.f;
+#pragma unroll 8
+        for (int64_t j = lane; j < p.C; j += 32) {
+            float f, d;
+            taylor_poly<ORDER, false>(to_f32(xr[j]), p, f, d);
+            S += f;
+            if (BWD) A += LOG ? to_f32(gr[j]) : to_f32(gr[j]) * f;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            S += __shfl_xor_sync(0xffffffffu, S, o);
+            A += __shfl_xor_sync(0xffffffffu, A, o);
+        }
+        const float invS = 1.f / S, logS = LOG && !BWD ? logf(S) : 0.f;
+#pragma unroll 8
+        for (int64_t j = lane; j < p.C; j += 32) {
+            float f, d;
+            taylor_poly<ORDER, BWD>(to_f32(xr[j]), p, f, d);
+            float o;
+            if (!BWD) o = LOG ? logf(f) - logS : f * invS;
+            else if (LOG) o = d * (to_f32(gr[j]) / f - A * invS);
+            else o = d * invS * (to_f32(gr[j]) - A * invS);
+            out[r * p.C + j] = from_f32<T>(o);
+        }
+    }
+}
+
+inline bool aligned16(const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
+
+template <typename T, bool BWD, bool LOG, int ORDER>
+int launch_taylor(const TaylorParams &p, cudaStream_t stream) {
+    if (p.M == 1) {
+        int64_t grid = (p.N + kTaylorThreads / 32 - 1) / (kTaylorThreads / 32);
+        const int64_t cap = int64_t(sm_count()) * 8;
+        if (grid > cap) grid = cap;
+        taylor_rows_kernel<T, BWD, LOG, ORDER><<<unsigned(grid), kTaylorThreads, 0, stream>>>(p);
+        return launch_status("taylor softmax rows kernel launch");
+    }
+    const bool vec4 = sizeof(T) == 4 && p.M % 4 == 0 && aligned16(p.x) && aligned16(p.out) && (!BWD || aligned16(p.g));
+    const int64_t groups = p.N * (vec4 ? p.M / 4 : p.M);
+    int64_t grid = (groups + kTaylorThreads - 1) / kTaylorThreads;
+    // few resident blocks: the second walk over the channels should find the first walk's lines
+    // in L1 (a block's working set is C x 4 KB (x 2 in backward))
+    const int64_t cap = int64_t(sm_count()) * 3;
+    if (grid > cap) grid = cap;
+    if constexpr (sizeof(T) == 4) {
+        if (vec4) {
+            taylor_spatial_kernel<T, 4, BWD, LOG, ORDER><<<unsigned(grid), kTaylorThreads, 0, stream>>>(p);
+            return launch_status("taylor softmax kernel launch");
+        }
+    }
+    taylor_spatial_kernel<T, 1, BWD, LOG, ORDER><<<unsigned(grid), kTaylorThreads, 0, stream>>>(p);
+    return launch_status("taylor softmax kernel launch");
+}
+
+template <typename T, bool BWD, bool LOG>
+int launch_taylor_order(const TaylorParams &p, cudaStream_t stream) {
+    switch (p.order) {
+        case 2: return launch_taylor<T, BWD, LOG, 2>(p, stream);
+        case 4: return launch_taylor<T, BWD, LOG, 4>(p, stream);
+        case 6: return launch_taylor<T, BWD, LOG, 6>(p, stream);
+        default: return launch_taylor<T, BWD, LOG, 0>(p, stream);
+    }
+}
+
+template <bool BWD>
+int dispatch_taylor(TaylorParams &p, int dtype, int order, int use_log, const char *who, cudaStream_t stream) {
+    if (p.N < 0 || p.C < 1 || p.M < 0) {
+        set_error("%s: bad shape N=%lld C=%lld M=%lld", who, (long long)p.N, (long long)p.C, (long long)p.M);
+        return B200_ERR_ARG;
+    }
+    if (order < 2 || order > kMaxOrder || (order & 1)) {
+        set_error("%s: n must be even, 2 <= n <= %d (got %d)", who, kMaxOrder, order);
+        return B200_ERR_ARG;
+    }
+    if (p.N * p.M == 0) return B200_OK;
+    if (!p.x || !p.out || (BWD && !p.g)) {
+        set_error("%s: null pointer", who);
+        return B200_ERR_ARG;
+    }
+    p.order = order;
+    if (dtype == B200_F32)
+        return use_log ? launch_taylor_order<float, BWD, true>(p, stream) : launch_taylor_order<float, BWD, false>(p, stream);
+    if (dtype == B200_F16)
+        return use_log ? launch_taylor_order<__half, BWD, true>(p, stream)
+                       : launch_taylor_order<__half, BWD, false>(p, stream);
+    set_error("%s: unknown dtype code %d", who, dtype);
+    return B200_ERR_ARG;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_taylor_softmax_forward(const void *feat, void *out, int64_t N, int64_t C, int64_t M, int dtype,
+                                           int n, int use_log, void *stream) {
+    TaylorParams p{};
+    p.x = feat;
+    p.out = out;
+    p.N = N; p.C = C; p.M = M;
+    return dispatch_taylor<false>(p, dtype, n, use_log, "b200_taylor_softmax_forward", static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_taylor_softmax_backward(const void *grad, const void *feat, void *grad_feat, int64_t N, int64_t C,
+                                            int64_t M, int dtype, int n, int use_log, void *stream) {
+    TaylorParams p{};
+    p.x = feat;
+    p.g = grad;
+    p.out = grad_feat;
+    p.N = N; p.C = C; p.M = M;
+    return dispatch_taylor<true>(p, dtype, n, use_log, "b200_taylor_softmax_backward", static_cast<cudaStream_t>(stream));
+}

@@ -22,3 +22,8 @@ __all__ += ["LovaszSoftmaxV3", "LovaszSoftmaxFunctionV3"]
 from .ohem_loss import OhemCELoss, OhemLargeMarginLoss
 
 __all__ += ["OhemCELoss", "OhemLargeMarginLoss"]
+from .taylor_softmax import (TaylorSoftmaxV3, LogTaylorSoftmaxV3, TaylorCrossEntropyLossV3, TaylorSoftmaxFunc,
+                             taylor_softmax_v3)
+
+__all__ += ["TaylorSoftmaxV3", "LogTaylorSoftmaxV3", "TaylorCrossEntropyLossV3", "TaylorSoftmaxFunc",
+            "taylor_softmax_v3"]

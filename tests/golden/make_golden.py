@@ -29,7 +29,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def load_reference(root):
-    for name in ("lsr_cpp", "focal_cpp", "large_margin_cpp", "lovasz_softmax_cpp"):
+    for name in ("lsr_cpp", "focal_cpp", "large_margin_cpp", "lovasz_softmax_cpp", "taylor_softmax_cpp"):
         sys.modules.setdefault(name, types.ModuleType(name))
 
     def load(rel, alias):
@@ -46,6 +46,7 @@ def load_reference(root):
         "lm_v1": load("pytorch_loss/large_margin_softmax.py", "ref_large_margin_installed"),
         "lm_v2": load("large_margin_softmax.py", "ref_large_margin_root"),
         "lovasz": load("lovasz_softmax.py", "ref_lovasz"),
+        "taylor": load("pytorch_loss/taylor_softmax.py", "ref_taylor_softmax"),
     }
 
 
@@ -144,7 +145,37 @@ def main():
     d["n_cases"] = np.array(len(cases))
     out["lovasz"] = d
 
+    # ---- taylor softmax (V1 function: activation and its autograd gradient for a random upstream
+    # gradient), and the cross entropy built on it: (shape, dim, n, use_log)
+    cases = [((2, 7, 5, 6), 1, 2, False), ((2, 7, 5, 6), 1, 4, True), ((3, 4, 6), 2, 6, False),
+             ((5, 3, 4, 2), 0, 2, True), ((4, 19), 1, 8, True), ((2, 33, 3, 5), 1, 4, False)]
+    d = {}
+    for i, (shape, dim, order, use_log) in enumerate(cases):
+        g = torch.Generator().manual_seed(500 + i)
+        x = (torch.randn(shape, generator=g) * 1.5).requires_grad_(True)
+        up = torch.randn(shape, generator=g)
+        y = ref["taylor"].taylor_softmax_v1(x, dim, order, use_log)
+        y.backward(up)
+        d.update({f"c{i}_x": x.detach().numpy(), f"c{i}_up": up.numpy(), f"c{i}_out": y.detach().numpy(),
+                  f"c{i}_grad": x.grad.numpy(), f"c{i}_hyper": np.array([dim, order, int(use_log)])})
+    d["n_cases"] = np.array(len(cases))
+    ce_cases = [((3, 6, 5, 4), 4, 255, 0.2, 'mean'), ((2, 19, 4, 4), 2, -1, 0.0, 'sum')]
+    for i, (shape, order, ign, frac, red) in enumerate(ce_cases):
+        g = torch.Generator().manual_seed(550 + i)
+        logits = torch.randn(shape, generator=g)
+        labels = labels_with_ignores(g, (shape[0],) + shape[2:], shape[1], ign, frac)
+        crit = ref["taylor"].TaylorCrossEntropyLossV1(n=order, ignore_index=ign, reduction=red)
+        l1, g1 = run(crit, logits, labels)
+        d.update({f"ce{i}_logits": logits.numpy(), f"ce{i}_labels": labels.numpy(),
+                  f"ce{i}_hyper": np.array([order, ign]), f"ce{i}_reduction": np.array(red),
+                  f"ce{i}_loss": l1, f"ce{i}_grad": g1})
+    d["n_ce_cases"] = np.array(len(ce_cases))
+    out["taylor"] = d
+
+    only = os.environ.get("GOLDEN_ONLY")               # e.g. GOLDEN_ONLY=taylor rewrites one file
     for name, d in out.items():
+        if only and name != only:
+            continue
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **d)
         print("wrote", path, os.path.getsize(path), "bytes")

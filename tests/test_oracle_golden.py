@@ -89,3 +89,21 @@ def test_unreduced_shapes_follow_v3():
         loss, grad = fn(logits, labels, ignore_index=255, reduction='none')
         assert loss.shape == (2, 3, 4)
         assert (loss[0, 0, :2] == 0).all() and (grad[0, :, 0, :2] == 0).all()
+
+
+def test_taylor_oracle(golden_dir):
+    """oracle/taylor.py against the reference's taylor_softmax_v1 / TaylorCrossEntropyLossV1."""
+    from oracle import taylor as OT
+    z = np.load(os.path.join(golden_dir, "taylor.npz"))
+    for i in range(int(z["n_cases"])):
+        dim, order, use_log = (int(v) for v in z[f"c{i}_hyper"])
+        x, up = torch.from_numpy(z[f"c{i}_x"]), torch.from_numpy(z[f"c{i}_up"])
+        out, grad = OT.taylor_softmax(x, dim, order, bool(use_log), upstream=up)
+        assert torch.allclose(out, torch.from_numpy(z[f"c{i}_out"]), atol=1e-6, rtol=1e-5), i
+        assert torch.allclose(grad, torch.from_numpy(z[f"c{i}_grad"]), atol=1e-5, rtol=1e-4), i
+    for i in range(int(z["n_ce_cases"])):
+        order, ign = (int(v) for v in z[f"ce{i}_hyper"])
+        logits, labels = torch.from_numpy(z[f"ce{i}_logits"]), torch.from_numpy(z[f"ce{i}_labels"])
+        loss, grad = OT.taylor_cross_entropy(logits, labels, order, ign, str(z[f"ce{i}_reduction"]))
+        assert torch.allclose(loss, torch.from_numpy(z[f"ce{i}_loss"]), atol=1e-6, rtol=1e-5), i
+        assert torch.allclose(grad, torch.from_numpy(z[f"ce{i}_grad"]), atol=1e-6, rtol=1e-5), i
