@@ -348,11 +348,20 @@ def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
         run_steps(args.steps)
         end.record()
         barrier()
-    ms_total = start.elapsed_time(end)
-    if world > 1:
-        t = torch.tensor([ms_total], dtype=torch.float64, device=device)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms_total = float(t.item())
+        ms_total = start.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms_total], dtype=torch.float64, device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms_total = float(t.item())
+        # The K timed steps last about a millisecond, less than one nvidia-smi sample: keep the
+        # same steps running (untimed) for about half a second so the clocks are sampled under
+        # this load.  The count derives from the agreed time: every rank runs the same number of
+        # extra steps (they may contain a cross-rank exchange).
+        t_load = time.perf_counter()
+        for _ in range(min(2000, max(1, int(500.0 / max(1e-3, ms_total))))):
+            run_steps(args.steps)
+        torch.cuda.synchronize()
+        clock_window_s = time.perf_counter() - t_load
     ms_step = ms_total / args.steps
     value = world * wl.elems / (ms_step / 1e3)
 
@@ -402,7 +411,7 @@ def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
     res = {
         "workload": wl.desc, "value": value, "ms_per_step": ms_step, "graph": graphs is not None,
         "launches_per_step": int(launches_per_step), "roofline": roofline, "e2e": e2e,
-        "clocks": clocks.summary(),
+        "clocks": dict(clocks.summary(), window="the K timed steps + %.2f s of the same steps" % clock_window_s),
     }
     if with_cpu and rank == 0:
         res["cpu_baseline"] = cpu_baseline(wl)
