@@ -249,20 +249,23 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
                  "r"(bytes)
                  : "memory");
 }
+constexpr uint32_t kMbarSuspendNs = 2000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
+    // the suspend-time hint lets the thread sleep inside the instruction for up to that many
+    // nanoseconds instead of returning to spin, which would take issue slots from working warps
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kMbarSuspendNs)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after kMbarSpinLimit polls (each poll itself blocks for a
-// hardware-defined short time), records it in the status word and reports false.
-constexpr uint32_t kMbarSpinLimit = 1u << 20;
+// Bounded wait: gives up after kMbarSpinLimit polls (each poll blocks for at most the
+// suspend-time hint: about a second in total), records it in the status word and reports false.
+constexpr uint32_t kMbarSpinLimit = 1u << 19;
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
                                                   unsigned *status_word) {
     for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
