@@ -275,6 +275,17 @@ def direct_calls(wl, sets, device):
                                                           P(grads[i]), n, c, m, dt, 255, 0.0, st))
         return fwd, bwd
     stem, hyper, ign = {"lsr": ("lsr", 0.1, 255), "lsr_rows": ("lsr", 0.1, -100), "lmargin": ("lmargin", 0.3, 255)}[wl.name]
+    if lib.b200_softmax_stats_path(P(xs[0]), P(ys[0]), P(grads[0]), n, c, m, dt):
+        # many classes: the module hands per-pixel statistics from forward to backward
+        f_fwd, f_bwd = getattr(lib, "b200_%s_forward_ex" % stem), getattr(lib, "b200_%s_backward_ex" % stem)
+        stats = [torch.empty((n * m, 4), dtype=torch.float32, device=device) for _ in sets]
+        fwd = lambda i: _cabi.check(f_fwd(P(xs[i]), P(ys[i]), None, P(recs[i]), P(ws), ws.numel(), P(stats[i]),
+                                          n, c, m, dt, ign, hyper, st))
+        bwd = lambda i: _cabi.check(f_bwd(P(xs[i]), P(ys[i]), P(stats[i]), P(one), 1, denoms[i], P(grads[i]),
+                                          n, c, m, dt, ign, hyper, st))
+        for i in range(len(sets)):
+            fwd(i)                      # backward launches below read these statistics
+        return fwd, bwd
     f_fwd, f_bwd = getattr(lib, "b200_%s_forward" % stem), getattr(lib, "b200_%s_backward" % stem)
     fwd = lambda i: _cabi.check(f_fwd(P(xs[i]), P(ys[i]), None, P(recs[i]), P(ws), ws.numel(), n, c, m, dt, ign, hyper, st))
     bwd = lambda i: _cabi.check(f_bwd(P(xs[i]), P(ys[i]), P(one), 1, denoms[i], P(grads[i]), n, c, m, dt, ign, hyper, st))

@@ -51,6 +51,8 @@ class Workload:
         return s * e + 8 * p
 
     def bytes_backward(self):
+        # (with many classes backward also reads 16 bytes of saved statistics per pixel: 0.1 byte per
+        # element at 150 classes, not counted)
         e, p, s = self.elems, self.pixels, self.esize()
         if self.name == "focal":
             return 12 * e

@@ -218,6 +218,38 @@ int b200_lovasz_backward(const float *grad, const void *logits, const int64_t *l
                          int64_t M, int dtype, int64_t ignore_index, int per_image,
                          void *stream);
 
+/* ---------------------------------- label smooth / large margin with statistics ---
+ * No counterpart in the reference (its backward recomputes the softmax from scratch).
+ * For many classes the forward kernel can leave 16 bytes of statistics per pixel
+ * (maximum, 1 / sum, and for large margin two gradient coefficients) from which the
+ * backward kernel produces every gradient element in one streaming pass.
+ *   b200_softmax_stats_path(...) == 1 : the layout takes that path (more classes than a
+ *       512-pixel resident tile holds, M >= 512, 16-byte aligned rows and pointers);
+ *       pass grad_logits = NULL when asking on behalf of the forward.
+ *   *_forward_ex : as *_forward, plus `stats` (float[N*M][4], 16-byte aligned, may be NULL);
+ *       written only when the path applies to (logits, labels).
+ *   *_backward_ex: as *_backward, plus the `stats` of the forward of the same inputs; used only
+ *       when the path applies to (logits, labels, grad_logits), else the gradient is
+ *       recomputed as in *_backward.  Pass stats only if the forward's query returned 1.
+ */
+int b200_softmax_stats_path(const void *logits, const int64_t *labels, const void *grad_logits,
+                            int64_t N, int64_t C, int64_t M, int dtype);
+int b200_lsr_forward_ex(const void *logits, const int64_t *labels, void *losses, void *out,
+                        void *workspace, size_t workspace_bytes, void *stats, int64_t N, int64_t C,
+                        int64_t M, int dtype, int64_t ignore_index, float smooth, void *stream);
+int b200_lsr_backward_ex(const void *logits, const int64_t *labels, const void *stats,
+                         const void *grad_out, int grad_mode, const void *denom, void *grad_logits,
+                         int64_t N, int64_t C, int64_t M, int dtype, int64_t ignore_index,
+                         float smooth, void *stream);
+int b200_lmargin_forward_ex(const void *logits, const int64_t *labels, void *losses, void *out,
+                            void *workspace, size_t workspace_bytes, void *stats, int64_t N,
+                            int64_t C, int64_t M, int dtype, int64_t ignore_index, float lam,
+                            void *stream);
+int b200_lmargin_backward_ex(const void *logits, const int64_t *labels, const void *stats,
+                             const void *grad_out, int grad_mode, const void *denom,
+                             void *grad_logits, int64_t N, int64_t C, int64_t M, int dtype,
+                             int64_t ignore_index, float lam, void *stream);
+
 /* ------------------------------------------------------------------- OHEM ---
  * Online hard example mining by score: the relabelling step in front of a
  * cross-entropy / large-margin loss.  Replaces ohem_cpp.score_ohem_label

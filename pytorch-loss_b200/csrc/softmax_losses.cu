@@ -40,6 +40,8 @@ struct SoftmaxParams {
     const double *denom;
     void *workspace;
     ReduceRecord *out;
+    float4 *stats;           // [N*M] per-pixel statistics: written by the chunked forward, read by
+                             // the chunked backward (null: not wanted / not available)
     int64_t N, C, M;
     int64_t ignore;
     LossConsts k;
@@ -979,9 +981,11 @@ tile_chunk_fwd_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorM
                 const float mi = i ? m.y : m.x, si = i ? sum.y : sum.x, sxi = i ? sx.y : sx.x;
                 const float xli = lbi[i] >= 0 ? (i ? xl.y : xl.x) : 0.f;
                 float l = 0.f;
+                float4 st = make_float4(mi, 0.f, 0.f, 0.f);
                 if (lbi[i] != -1) {
                     if (KIND == kLSR) {
                         l = kc.sumy * (mi + __logf(si)) - kc.lb_neg * sxi - (kc.lb_pos - kc.lb_neg) * xli;
+                        st.y = __fdividef(1.f, si);
                     } else {
                         // take the stand-in's terms back out (no label channel: nothing was replaced)
                         const bool repl = lbi[i] >= 0;
@@ -999,8 +1003,13 @@ tile_chunk_fwd_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorM
                         const float e_lb = repl ? ex2f((xli - mm) * kLog2e) : 0.f;
                         const float s_all = e_no + e_lb;
                         l = (mm + __logf(s_all)) - xli + kc.half_lam * (sqx - kc.a * sd);
+                        const float rr = __fdividef(e_no, s_all);
+                        st.y = inv_s;
+                        st.z = rr + kc.half_lam * (1.f - sqx);
+                        st.w = rr;
                     }
                 }
+                if (prm.stats) prm.stats[n * prm.M + px0 + i] = st;
                 if (losses) losses[n * prm.M + px0 + i] = from_f32<T>(l);
                 if (REDUCE && lbi[i] != -1) {
                     acc32 += l;
@@ -1018,6 +1027,178 @@ tile_chunk_fwd_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorM
         acc_cnt += double(cnt32);
     }
     if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+}
+
+// ---------------------------------------------- many channels, backward from saved statistics
+//
+// The chunked forward leaves four floats per pixel (maximum, 1 / sum and, for large margin, the
+// two per-pixel coefficients of its gradient).  With them every gradient element depends on its
+// own logit only, so backward is one more streaming pass in the same chunks: TMA in, gradient
+// in place, TMA out -- no resident tile, no slices, no block barrier.
+//   label smooth : g_j = (sumy * e^{x_j - m} / s - eps/C) * sc,            target: - (1 - eps - eps/C) * sc
+//   large margin : g_j = q_j * (A + lam/2 * d_j) * sc - lam/2 * a * sc,    target: - r * sc
+//                  q_j = e^{d_j} / s',  d_j = x_j - m',  A = r + lam/2 * (1 - sum q d)
+struct ChunkBwdLayout {
+    uint32_t box_elems, label_off, stats_off, coord_off, stage_bytes;
+};
+template <typename T> __host__ __device__ inline ChunkBwdLayout chunk_bwd_layout() {
+    ChunkBwdLayout l;
+    l.box_elems = kChunkCh * kChunkTP;
+    l.label_off = 2u * l.box_elems * uint32_t(sizeof(T));
+    l.stats_off = l.label_off + kChunkTile * 8u;
+    l.coord_off = l.stats_off + kChunkTile * 16u;
+    l.stage_bytes = l.coord_off + 128u;
+    return l;
+}
+
+template <typename T, int KIND>
+__global__ void __launch_bounds__(kTileBlock)
+tile_chunk_bwd_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap map_in,
+                      const __grid_constant__ CUtensorMap map_out) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ PipeBarriers bars;
+    const int C = static_cast<int>(prm.C), NS = prm.stages;
+    const ChunkBwdLayout lay = chunk_bwd_layout<T>();
+    unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    const int tid = threadIdx.x;
+    unsigned *status = nullptr;                       // backward has no workspace: waits are bounded only
+    const int nchunks = (C + kChunkCh - 1) / kChunkCh;
+    const int64_t tiles_per_image = (prm.M + kChunkTile - 1) / kChunkTile;
+    const int64_t total_tiles = prm.N * tiles_per_image;
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+
+    pipe_init<kTileCompute, true>(bars, NS);
+
+    if (tid == kTileCompute) {
+        int k = 0;
+        bool alive = true;
+        for (int64_t t = first; t < total_tiles && alive; t += stride) {
+            const int64_t n = t / tiles_per_image;
+            const int64_t p0 = (t % tiles_per_image) * kChunkTile;
+            int64_t npix = prm.M - p0;
+            if (npix > kChunkTile) npix = kChunkTile;
+            const int nbx = int((npix + kChunkTP - 1) / kChunkTP);
+            const uint32_t label_bytes = uint32_t(npix) * 8u, stats_bytes = uint32_t(npix) * 16u;
+            for (int c = 0; c < nchunks; ++c, ++k) {
+                const int s = k % NS;
+                if (k >= NS && !mbar_wait_bounded(&bars.empty[s], ((k / NS) - 1) & 1, status)) {
+                    alive = false;
+                    break;
+                }
+                unsigned char *stage = base + size_t(s) * lay.stage_bytes;
+                *reinterpret_cast<int4 *>(stage + lay.coord_off) = make_int4(int(n), int(p0), c, nbx);
+                mbar_expect_tx(&bars.full[s], uint32_t(nbx) * lay.box_elems * uint32_t(sizeof(T)) +
+                                                  (c == 0 ? label_bytes + stats_bytes : 0u));
+                for (int bx = 0; bx < nbx; ++bx)
+                    tma_load_3d(reinterpret_cast<T *>(stage) + size_t(bx) * lay.box_elems, &map_in,
+                                int(p0) + bx * kChunkTP, c * kChunkCh, int(n), &bars.full[s]);
+                if (c == 0) {
+                    bulk_load_1d(stage + lay.label_off, prm.labels + n * prm.M + p0, label_bytes, &bars.full[s]);
+                    bulk_load_1d(stage + lay.stats_off, prm.stats + n * prm.M + p0, stats_bytes, &bars.full[s]);
+                }
+            }
+        }
+    } else if (tid == kTileCompute + 32) {
+        const int64_t total_chunks = ((total_tiles - first + stride - 1) / stride) * nchunks;
+        for (int64_t k = 0; k < total_chunks; ++k) {
+            const int s = int(k % NS);
+            if (!mbar_wait_bounded(&bars.ready[s], uint32_t(k / NS) & 1u, status)) break;
+            const unsigned char *stage = base + size_t(s) * lay.stage_bytes;
+            const int4 coord = *reinterpret_cast<const int4 *>(stage + lay.coord_off);
+            for (int bx = 0; bx < coord.w; ++bx)
+                tma_store_3d(&map_out, coord.y + bx * kChunkTP, coord.z * kChunkCh, coord.x,
+                             reinterpret_cast<const T *>(stage) + size_t(bx) * lay.box_elems);
+            bulk_commit();
+            bulk_wait_read_all();
+            mbar_arrive(&bars.empty[s]);
+        }
+        bulk_wait_all();
+    } else if (tid < kTileCompute) {
+        const int lane = tid & 31;
+        const int pix = tid * 2;
+        const int bxo = (pix / kChunkTP) * int(lay.box_elems) + (pix % kChunkTP);
+        const T *gout = static_cast<const T *>(prm.grad_out);
+        const LossConsts kc = prm.k;
+        const float gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
+        int k = 0;
+        bool alive = true;
+        for (int64_t t = first; t < total_tiles && alive; t += stride) {
+            int lbi[2] = {-1, -1};
+            pk_t pa = 0, pb = 0, pc = 0, pm = 0;       // per-pixel coefficients, packed
+            float tgt[2] = {0.f, 0.f};                 // value of the target element
+            for (int c = 0; c < nchunks; ++c, ++k) {
+                const int s = k % NS;
+                bool ok = true;
+                if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
+                if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                    alive = false;
+                    break;
+                }
+                unsigned char *stage = base + size_t(s) * lay.stage_bytes;
+                T *mine = reinterpret_cast<T *>(stage) + bxo;
+                const int c0 = c * kChunkCh;
+                const int nch = min(kChunkCh, C - c0);
+                if (c == 0) {
+                    const int4 coord = *reinterpret_cast<const int4 *>(stage + lay.coord_off);
+                    const int64_t n = coord.x, px0 = int64_t(coord.y) + pix;
+                    const int64_t *tile_labels = reinterpret_cast<const int64_t *>(stage + lay.label_off);
+                    const float4 *tile_stats = reinterpret_cast<const float4 *>(stage + lay.stats_off);
+                    float a2[2], b2[2], c2[2], m2[2];
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const bool inb = px0 + i < prm.M;
+                        const int64_t lb = inb ? tile_labels[pix + i] : prm.ignore;
+                        const bool valid = inb && lb != prm.ignore;
+                        lbi[i] = valid ? ((lb >= 0 && lb < C) ? int(lb) : -2) : -1;
+                        float sc = valid ? gscale : 0.f;
+                        if (valid && prm.grad_mode == 2) sc *= to_f32(gout[n * prm.M + px0 + i]);
+                        const float4 st = inb ? tile_stats[pix + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                        m2[i] = st.x;
+                        if (KIND == kLSR) {
+                            // g = e * (sumy * sc / s) - eps/C * sc
+                            a2[i] = kc.sumy * sc * st.y;
+                            b2[i] = -kc.lb_neg * sc;
+                            c2[i] = 0.f;
+                            tgt[i] = -(kc.lb_pos - kc.lb_neg) * sc;            // added to the target element
+                        } else {
+                            // g = (e / s') * (A sc + lam/2 sc d) - lam/2 a sc
+                            a2[i] = st.z * sc * st.y;
+                            b2[i] = kc.half_lam * sc * st.y;
+                            c2[i] = -kc.half_lam * kc.a * sc;
+                            tgt[i] = -st.w * sc;                               // replaces the target element
+                        }
+                    }
+                    pa = pk2(make_float2(a2[0], a2[1]));
+                    pb = pk2(make_float2(b2[0], b2[1]));
+                    pc = pk2(make_float2(c2[0], c2[1]));
+                    pm = pk2(make_float2(m2[0], m2[1]));
+                }
+                {
+                    const pk_t l2e = psplat(kLog2e);
+                    const pk_t nml = pmul(pm, psplat(-kLog2e)), negm = pmul(pm, psplat(-1.f));
+                    T *q = mine;
+#pragma unroll 4
+                    for (int j = 0; j < nch; ++j, q += kChunkTP) {
+                        const pk_t x = ld_pk(q);
+                        const pk_t e = pex2(pfma(x, l2e, nml));
+                        if (KIND == kLSR) st_pk(q, pfma(e, pa, pb));
+                        else st_pk(q, pfma(e, pfma(pb, padd(x, negm), pa), pc));
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int j = lbi[i] - c0;
+                    if (lbi[i] >= 0 && j >= 0 && j < kChunkCh) {
+                        T *e = mine + j * kChunkTP + i;
+                        *e = from_f32<T>(KIND == kLSR ? to_f32(*e) + tgt[i] : tgt[i]);
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.ready[s]);
+            }
+        }
+    }
 }
 
 // Pair q of a 16-byte register vector as two floats, and back.
@@ -1318,6 +1499,20 @@ template <typename K> int set_smem(K kernel, size_t bytes) {
     return B200_OK;
 }
 
+// True when the chunked kernels (tile_chunk_fwd_kernel / tile_chunk_bwd_kernel) take the call:
+// tile regime, TMA-capable layout, at least one 512-pixel tile, and more classes than the
+// 512-pixel-wide resident tile of tile_pair_kernel holds.  `io`: the gradient (backward) or
+// the logits again (forward).
+inline bool chunk_eligible(size_t es, const void *logits, const void *io, const void *labels, int64_t N, int64_t C,
+                           int64_t M) {
+    if (M <= 1 || size_t(C) * 32 * es + 8192 > kSmemLimit) return false;
+    const bool tma_ok = (M * es) % 16 == 0 && aligned16(logits) && aligned16(io) && M < (int64_t(1) << 31) &&
+                        N < (int64_t(1) << 31) && aligned16(labels);
+    if (!tma_ok || M < kChunkTile || getenv("B200_NO_CHUNK")) return false;
+    const int64_t nbox = (C + 255) / 256, rows = nbox * ((C + nbox - 1) / nbox);
+    return 2 * size_t(rows) * 256 * es > size_t(40) * 1024;
+}
+
 template <typename T, int KIND, bool BWD, bool REDUCE>
 int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
     const size_t es = sizeof(T);
@@ -1353,8 +1548,7 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
         prm.nbx = (tma_ok && TP == 256 && 2 * size_t(prm.rows) * TP * es <= size_t(40) * 1024 && prm.M > TP) ? 2 : 1;
         if constexpr (!BWD) {
             // many channels, forward: 512-pixel tiles streamed in channel chunks (no slice exchange)
-            if (tma_ok && (prm.nbx == 1 || getenv("B200_FORCE_CHUNK")) && prm.M >= kChunkTile &&
-                !getenv("B200_NO_CHUNK")) {
+            if (chunk_eligible(es, prm.logits, prm.logits, prm.labels, prm.N, prm.C, prm.M)) {
                 const ChunkLayout lay = chunk_layout<T>();
                 // measured on config 3 (C = 150): 2 stages x 3 blocks per SM 206 us, 3 stages x 2 blocks 222 us
                 int stages = tune_int("B200_CHUNK_STAGES", 2);
@@ -1379,6 +1573,37 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
                 if ((rc2 = set_smem(kern, smem)) != B200_OK) return rc2;
                 kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in);
                 return launch_status("softmax chunked forward kernel launch");
+            }
+        }
+        if constexpr (BWD) {
+            // many channels, backward from the statistics the chunked forward saved
+            if (prm.stats && aligned16(prm.stats) &&
+                chunk_eligible(es, prm.logits, prm.grads, prm.labels, prm.N, prm.C, prm.M)) {
+                const ChunkBwdLayout lay = chunk_bwd_layout<T>();
+                // a stage is busy from its load to the end of its store: backward wants a deeper ring
+                // than forward (config 3: 3 stages in one block per SM 396 us, 2 stages x 2 blocks 430 us)
+                int stages = tune_int("B200_CHUNK_BWD_STAGES", 3);
+                if (stages > kMaxStages) stages = kMaxStages;
+                prm.stages = stages;
+                const size_t smem = 128 + size_t(stages) * lay.stage_bytes;
+                int per_sm = int((224 * 1024) / (smem + 1024));
+                const int cap_sm = tune_int("B200_CHUNK_CTAS", 3);
+                if (per_sm > cap_sm) per_sm = cap_sm;
+                if (per_sm < 1) per_sm = 1;
+                const int64_t tiles = prm.N * ((prm.M + kChunkTile - 1) / kChunkTile);
+                int64_t grid = int64_t(sms) * per_sm;
+                if (grid > tiles) grid = tiles;
+                CUtensorMap map_in{}, map_out{};
+                const uint64_t dims[3] = {uint64_t(prm.M), uint64_t(prm.C), uint64_t(prm.N)};
+                const uint64_t strides[3] = {es, uint64_t(prm.M) * es, uint64_t(prm.C) * prm.M * es};
+                const uint32_t box[3] = {uint32_t(kChunkTP), uint32_t(kChunkCh), 1u};
+                if (!encode_tensor_map(&map_in, dtype, prm.logits, 3, dims, strides, box)) return B200_ERR_LAUNCH;
+                if (!encode_tensor_map(&map_out, dtype, prm.grads, 3, dims, strides, box)) return B200_ERR_LAUNCH;
+                auto kern = tile_chunk_bwd_kernel<T, KIND>;
+                int rc2;
+                if ((rc2 = set_smem(kern, smem)) != B200_OK) return rc2;
+                kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in, map_out);
+                return launch_status("softmax chunked backward kernel launch");
             }
         }
         const int TPT = TP * prm.nbx;
@@ -1504,7 +1729,7 @@ int check_shape(const char *who, int64_t N, int64_t C, int64_t M) {
 template <int KIND>
 int forward(const char *who, const void *logits, const int64_t *labels, void *losses, void *out,
             void *workspace, size_t workspace_bytes, int64_t N, int64_t C, int64_t M, int dtype,
-            int64_t ignore_index, float hp, void *stream) {
+            int64_t ignore_index, float hp, void *stream, void *stats = nullptr) {
     int rc = check_shape(who, N, C, M);
     if (rc != B200_OK) return rc;
     const int64_t P = N * M;
@@ -1527,6 +1752,7 @@ int forward(const char *who, const void *logits, const int64_t *labels, void *lo
     prm.losses = losses;
     prm.workspace = workspace;
     prm.out = static_cast<ReduceRecord *>(out);
+    prm.stats = static_cast<float4 *>(stats);
     prm.N = N;
     prm.C = C;
     prm.M = M;
@@ -1538,7 +1764,7 @@ int forward(const char *who, const void *logits, const int64_t *labels, void *lo
 template <int KIND>
 int backward(const char *who, const void *logits, const int64_t *labels, const void *grad_out,
              int grad_mode, const void *denom, void *grad_logits, int64_t N, int64_t C, int64_t M,
-             int dtype, int64_t ignore_index, float hp, void *stream) {
+             int dtype, int64_t ignore_index, float hp, void *stream, const void *stats = nullptr) {
     int rc = check_shape(who, N, C, M);
     if (rc != B200_OK) return rc;
     if (grad_mode < 0 || grad_mode > 2 || (grad_mode != 0 && !grad_out)) {
@@ -1557,6 +1783,7 @@ int backward(const char *who, const void *logits, const int64_t *labels, const v
     prm.grad_out = grad_out;
     prm.grad_mode = grad_mode;
     prm.denom = static_cast<const double *>(denom);
+    prm.stats = static_cast<float4 *>(const_cast<void *>(stats));
     prm.N = N;
     prm.C = C;
     prm.M = M;
@@ -1597,4 +1824,38 @@ extern "C" int b200_lmargin_backward(const void *logits, const int64_t *labels,
                                      int64_t ignore_index, float lam, void *stream) {
     return backward<kLMargin>("b200_lmargin_backward", logits, labels, grad_out, grad_mode, denom,
                               grad_logits, N, C, M, dtype, ignore_index, lam, stream);
+}
+
+// ---- the same four entry points with per-pixel statistics handed from forward to backward
+extern "C" int b200_softmax_stats_path(const void *logits, const int64_t *labels, const void *grad_logits,
+                                       int64_t N, int64_t C, int64_t M, int dtype) {
+    const size_t es = dtype == B200_F16 ? 2 : 4;
+    return chunk_eligible(es, logits, grad_logits ? grad_logits : logits, labels, N, C, M) ? 1 : 0;
+}
+extern "C" int b200_lsr_forward_ex(const void *logits, const int64_t *labels, void *losses, void *out,
+                                   void *workspace, size_t workspace_bytes, void *stats, int64_t N, int64_t C,
+                                   int64_t M, int dtype, int64_t ignore_index, float smooth, void *stream) {
+    return forward<kLSR>("b200_lsr_forward_ex", logits, labels, losses, out, workspace, workspace_bytes, N, C, M,
+                         dtype, ignore_index, smooth, stream, stats);
+}
+extern "C" int b200_lsr_backward_ex(const void *logits, const int64_t *labels, const void *stats,
+                                    const void *grad_out, int grad_mode, const void *denom, void *grad_logits,
+                                    int64_t N, int64_t C, int64_t M, int dtype, int64_t ignore_index,
+                                    float smooth, void *stream) {
+    return backward<kLSR>("b200_lsr_backward_ex", logits, labels, grad_out, grad_mode, denom, grad_logits, N, C, M,
+                          dtype, ignore_index, smooth, stream, stats);
+}
+extern "C" int b200_lmargin_forward_ex(const void *logits, const int64_t *labels, void *losses, void *out,
+                                       void *workspace, size_t workspace_bytes, void *stats, int64_t N,
+                                       int64_t C, int64_t M, int dtype, int64_t ignore_index, float lam,
+                                       void *stream) {
+    return forward<kLMargin>("b200_lmargin_forward_ex", logits, labels, losses, out, workspace, workspace_bytes, N,
+                             C, M, dtype, ignore_index, lam, stream, stats);
+}
+extern "C" int b200_lmargin_backward_ex(const void *logits, const int64_t *labels, const void *stats,
+                                        const void *grad_out, int grad_mode, const void *denom, void *grad_logits,
+                                        int64_t N, int64_t C, int64_t M, int dtype, int64_t ignore_index,
+                                        float lam, void *stream) {
+    return backward<kLMargin>("b200_lmargin_backward_ex", logits, labels, grad_out, grad_mode, denom, grad_logits, N,
+                              C, M, dtype, ignore_index, lam, stream, stats);
 }

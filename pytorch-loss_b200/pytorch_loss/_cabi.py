@@ -42,6 +42,11 @@ SIGNATURES = {
     "b200_lsr_backward": (_int, [_vp, _vp, _vp, _int, _vp, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
     "b200_lmargin_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
     "b200_lmargin_backward": (_int, [_vp, _vp, _vp, _int, _vp, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
+    "b200_softmax_stats_path": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int]),
+    "b200_lsr_forward_ex": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
+    "b200_lsr_backward_ex": (_int, [_vp, _vp, _vp, _vp, _int, _vp, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
+    "b200_lmargin_forward_ex": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
+    "b200_lmargin_backward_ex": (_int, [_vp, _vp, _vp, _vp, _int, _vp, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
     "b200_lovasz_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
     "b200_lovasz_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _int, _i64, _int, _vp]),
     "b200_lovasz_backward": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _i64, _int, _vp]),

@@ -12,6 +12,11 @@ _ENTRY = {
     "lsr": ("b200_lsr_forward", "b200_lsr_backward"),
     "lmargin": ("b200_lmargin_forward", "b200_lmargin_backward"),
 }
+# the same with per-pixel statistics handed from forward to backward (many classes)
+_ENTRY_EX = {
+    "lsr": ("b200_lsr_forward_ex", "b200_lsr_backward_ex"),
+    "lmargin": ("b200_lmargin_forward_ex", "b200_lmargin_backward_ex"),
+}
 
 
 def _prep(logits, labels):
@@ -32,25 +37,40 @@ def forward_per_pixel(kind, logits, labels, ignore_index, hyper):
     return losses, logits, labels
 
 
-def forward_reduced(kind, logits, labels, ignore_index, hyper, want_losses=False, exchange=None):
-    """Runs the reducing forward; returns (record, per-pixel losses or None, logits, labels).
-    With an `_p2p.Exchange` the kernel adds the sums over the ranks itself and the record is
-    the global one."""
+def forward_reduced(kind, logits, labels, ignore_index, hyper, want_losses=False, exchange=None,
+                    want_stats=False):
+    """Runs the reducing forward; returns (record, per-pixel losses or None, logits, labels
+    [, statistics or None when `want_stats`]).  With an `_p2p.Exchange` the kernel adds the sums
+    over the ranks itself and the record is the global one.  The statistics (16 bytes per pixel,
+    only for layouts with many classes) let backward skip its own softmax pass."""
     dev, logits, labels, n, c, m, dt = _prep(logits, labels)
     lib = _cabi.load_library()
     rec = _cabi.new_record(dev)
     ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
     losses = torch.empty(labels.shape, dtype=logits.dtype, device=dev) if want_losses else None
+    stats = None
+    if want_stats and n * m > 0 and lib.b200_softmax_stats_path(_cabi.ptr(logits), _cabi.ptr(labels), None,
+                                                                n, c, m, dt):
+        stats = torch.empty((n * m, 4), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        _cabi.check(getattr(lib, _ENTRY[kind][0])(
-            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), _cabi.ptr(rec), _cabi.ptr(ws),
-            ws.numel(), n, c, m, dt, int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+        if stats is not None:
+            _cabi.check(getattr(lib, _ENTRY_EX[kind][0])(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), _cabi.ptr(rec), _cabi.ptr(ws),
+                ws.numel(), _cabi.ptr(stats), n, c, m, dt, int(ignore_index), float(hyper),
+                _cabi.stream_ptr(dev)))
+        else:
+            _cabi.check(getattr(lib, _ENTRY[kind][0])(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), _cabi.ptr(rec), _cabi.ptr(ws),
+                ws.numel(), n, c, m, dt, int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+    if want_stats:
+        return rec, losses, logits, labels, stats
     return rec, losses, logits, labels
 
 
-def backward(kind, logits, labels, grad_output, denom, ignore_index, hyper):
+def backward(kind, logits, labels, grad_output, denom, ignore_index, hyper, stats=None):
     """d(loss)/d(logits); the upstream gradient (None = ones, a broadcast scalar, or one
-    value per pixel) and the optional device-resident divisor are applied in the kernel."""
+    value per pixel) and the optional device-resident divisor are applied in the kernel.
+    `stats`: what the forward of the same inputs returned, if anything."""
     dev = logits.device
     n, c, m = _cabi.split_shape(logits)
     lib = _cabi.load_library()
@@ -61,11 +81,16 @@ def backward(kind, logits, labels, grad_output, denom, ignore_index, hyper):
         mode, g = _cabi.grad_mode_of(grad_output, labels.shape)
         if mode == 2:
             g = g.to(logits.dtype)
+    dptr = None if denom is None else _cabi._vp(denom.data_ptr())
     with torch.cuda.device(dev):
-        _cabi.check(getattr(lib, _ENTRY[kind][1])(
-            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(g), mode,
-            None if denom is None else _cabi._vp(denom.data_ptr()), _cabi.ptr(grads),
-            n, c, m, _cabi.dtype_code(logits), int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+        if stats is not None:
+            _cabi.check(getattr(lib, _ENTRY_EX[kind][1])(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(stats), _cabi.ptr(g), mode, dptr, _cabi.ptr(grads),
+                n, c, m, _cabi.dtype_code(logits), int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+        else:
+            _cabi.check(getattr(lib, _ENTRY[kind][1])(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(g), mode, dptr, _cabi.ptr(grads),
+                n, c, m, _cabi.dtype_code(logits), int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
     return grads
 
 
@@ -81,19 +106,20 @@ class ReducedLossFunc(torch.autograd.Function):
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
     def forward(ctx, logits, labels, kind, hyper, ignore_index, mean, group):
         exchange = _p2p.get_exchange(group, logits.device) if logits.is_cuda else None
-        rec, _, logits, labels = forward_reduced(kind, logits, labels, ignore_index, hyper, exchange=exchange)
+        rec, _, logits, labels, stats = forward_reduced(kind, logits, labels, ignore_index, hyper,
+                                                        exchange=exchange, want_stats=True)
         sum_count = rec[:4].view(torch.float64)
         if exchange is None and _sharding.group_is_active(group):
             _sharding.allreduce_sum_count(sum_count, group)
             loss = _sharding.combine_mean(sum_count) if mean else sum_count[0].to(torch.float32)
         else:
             loss = rec[4] if mean else rec[5]
-        ctx.variables = logits, labels, kind, hyper, ignore_index, (sum_count[1:] if mean else None)
+        ctx.variables = logits, labels, kind, hyper, ignore_index, (sum_count[1:] if mean else None), stats
         return loss
 
     @staticmethod
     @amp.custom_bwd(device_type='cuda')
     def backward(ctx, grad_output):
-        logits, labels, kind, hyper, ignore_index, denom = ctx.variables
-        grads = backward(kind, logits, labels, grad_output, denom, ignore_index, hyper)
+        logits, labels, kind, hyper, ignore_index, denom, stats = ctx.variables
+        grads = backward(kind, logits, labels, grad_output, denom, ignore_index, hyper, stats)
         return grads, None, None, None, None, None, None
