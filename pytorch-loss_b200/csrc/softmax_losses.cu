@@ -1482,6 +1482,193 @@ rows_pipe_kernel(const SoftmaxParams prm) {
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ------------------------------------------------- rows regime, forward: one warp per row
+//
+// Forward for M == 1 and long rows.  Every warp streams its own rows through its own small
+// ring of shared-memory stages (lane 0 issues the bulk copies and re-arms a stage as soon as
+// the warp has read it), each lane keeps running statistics of the vectors it reads (online
+// softmax: one rescale per chunk), and the 32 lanes combine them with shuffles at the end of
+// a row.  Warps never wait for each other: no block barrier, no whole-row residency (so no
+// limit on the row length), and each element is read from shared memory once.
+constexpr int kWarpRowWarps = 8;                         // warps per block
+constexpr int kWarpRowVecs = 8;                          // 16-byte vectors per lane and chunk
+constexpr int kWarpRowChunk = 32 * 16 * kWarpRowVecs;    // 4 KB
+constexpr int kWarpRowStages = 2;
+
+template <typename T, int KIND, bool REDUCE>
+__global__ void __launch_bounds__(kWarpRowWarps * 32)
+rows_warp_fwd_kernel(const SoftmaxParams prm) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char(*ring)[kWarpRowStages][kWarpRowChunk] = reinterpret_cast<unsigned char(*)[kWarpRowStages][kWarpRowChunk]>(
+        smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u));
+    __shared__ __align__(8) uint64_t full[kWarpRowWarps][kWarpRowStages];
+    __shared__ double sh_red[64];
+    using V = Vec16<T>;
+    constexpr int VN = V::N, NP = VN / 2, NS = kWarpRowStages;
+    const int C = static_cast<int>(prm.C);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
+    const uint32_t row_bytes = uint32_t(C) * sizeof(T);                 // a multiple of 16
+    const int nchunks = int((row_bytes + kWarpRowChunk - 1) / kWarpRowChunk);
+    const int64_t gw = int64_t(blockIdx.x) * kWarpRowWarps + warp, nw = int64_t(gridDim.x) * kWarpRowWarps;
+    const int64_t my_rows = gw < prm.N ? (prm.N - gw + nw - 1) / nw : 0;
+    const int64_t my_chunks = my_rows * nchunks;
+    T *losses = static_cast<T *>(prm.losses);
+    const LossConsts kc = prm.k;
+    double acc_loss = 0.0, acc_cnt = 0.0;
+
+    if (lane == 0) {
+        for (int s = 0; s < NS; ++s) mbar_init(&full[warp][s], 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    // chunk q of this warp's stream: row gw + (q / nchunks) * nw, chunk q % nchunks
+    auto issue = [&](int64_t q) {
+        const int s = int(q % NS);
+        const int64_t r = gw + (q / nchunks) * nw;
+        const uint32_t off = uint32_t(q % nchunks) * kWarpRowChunk;
+        const uint32_t nb = row_bytes - off < uint32_t(kWarpRowChunk) ? row_bytes - off : uint32_t(kWarpRowChunk);
+        const unsigned char *src = static_cast<const unsigned char *>(prm.logits) + r * prm.C * sizeof(T) + off;
+        mbar_expect_tx(&full[warp][s], nb);
+        bulk_load_1d(ring[warp][s], src, nb, &full[warp][s]);
+    };
+    if (lane == 0)
+        for (int64_t q = 0; q < NS && q < my_chunks; ++q) issue(q);
+
+    int64_t q = 0;
+    bool alive = true;
+    for (int64_t ri = 0; ri < my_rows && alive; ++ri) {
+        const int64_t r = gw + ri * nw;
+        const int64_t lb = __ldg(prm.labels + r);
+        const bool valid = lb != prm.ignore;
+        const int lbi = valid ? ((lb >= 0 && lb < C) ? int(lb) : -2) : -1;
+        float m = kNegInf, sum = 0.f, sde = 0.f, sx = 0.f, xl = kNegInf;
+        for (int c = 0; c < nchunks; ++c, ++q) {
+            const int s = int(q % NS);
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(&full[warp][s], uint32_t(q / NS) & 1u, status);
+            if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                alive = false;
+                break;
+            }
+            const int ebase = c * (kWarpRowChunk / int(sizeof(T)));     // first element of the chunk
+            // my vectors of this chunk into registers; their maximum first
+            V xv[kWarpRowVecs];
+            float vmax = kNegInf;
+            const int jt = lbi - ebase;                                  // target's offset in the chunk, if inside
+#pragma unroll
+            for (int v = 0; v < kWarpRowVecs; ++v) {
+                const int e0 = ebase + (v * 32 + lane) * VN;
+                if (e0 < C) {
+                    xv[v] = *reinterpret_cast<const V *>(ring[warp][s] + (v * 32 + lane) * 16);
+#pragma unroll
+                    for (int p = 0; p < NP; ++p) {
+                        const float2 x = pair_of(xv[v], p);
+                        vmax = fmaxf(vmax, fmaxf(x.x, x.y));
+                    }
+                }
+            }
+            __syncwarp();                       // every lane has its data: the stage can be refilled
+            if (lane == 0 && q + NS < my_chunks) issue(q + NS);
+            // the target element (at most one lane, one vector): remember it; large margin takes
+            // it out of the statistics, so that lane redoes its maximum without it
+            const bool in_chunk = lbi >= 0 && jt >= 0 && jt < kWarpRowChunk / int(sizeof(T));
+            const int tv = in_chunk ? (jt / VN) / 32 : -1, tl = in_chunk ? (jt / VN) % 32 : -1, tq = in_chunk ? jt % VN : -1;
+            const bool mine = in_chunk && tl == lane;
+            if (mine) {
+#pragma unroll
+                for (int v = 0; v < kWarpRowVecs; ++v)
+#pragma unroll
+                    for (int e = 0; e < VN; ++e)
+                        if (v == tv && e == tq) xl = to_f32(xv[v].v[e]);
+                if (KIND == kLMargin) {
+                    vmax = kNegInf;
+#pragma unroll
+                    for (int v = 0; v < kWarpRowVecs; ++v) {
+                        const int e0 = ebase + (v * 32 + lane) * VN;
+                        if (e0 < C) {
+#pragma unroll
+                            for (int e = 0; e < VN; ++e)
+                                if (!(v == tv && e == tq)) vmax = fmaxf(vmax, to_f32(xv[v].v[e]));
+                        }
+                    }
+                }
+            }
+            const float mn = fmaxf(m, vmax);
+            const float dm = m - mn;
+            const float rs = ex2f(dm * kLog2e);
+            if (KIND == kLMargin) sde = rs * fmaf(dm, sum, sde);
+            sum *= rs;
+            m = mn;
+            const float2 nml = splat2(-mn * kLog2e), negm = splat2(-mn);
+            float2 sum2 = make_float2(sum, 0.f), sde2 = make_float2(sde, 0.f), sx2 = make_float2(sx, 0.f);
+#pragma unroll
+            for (int v = 0; v < kWarpRowVecs; ++v) {
+                const int e0 = ebase + (v * 32 + lane) * VN;
+                if (e0 < C) {
+#pragma unroll
+                    for (int p = 0; p < NP; ++p) {
+                        float2 x = pair_of(xv[v], p);
+                        float2 e = ex2_2(fma2(x, splat2(kLog2e), nml));
+                        if (KIND == kLMargin && mine && v == tv && p == tq / 2) {
+                            // drop the target from the pair
+                            if (tq & 1) { e.y = 0.f; x.y = mn; } else { e.x = 0.f; x.x = mn; }
+                            sx2 = add2(sx2, make_float2((tq & 1) ? x.x : 0.f, (tq & 1) ? 0.f : x.y));
+                        } else {
+                            sx2 = add2(sx2, x);
+                        }
+                        sum2 = add2(sum2, e);
+                        if (KIND == kLMargin) sde2 = fma2(add2(x, negm), e, sde2);
+                    }
+                }
+            }
+            sum = sum2.x + sum2.y;
+            sde = sde2.x + sde2.y;
+            sx = sx2.x + sx2.y;
+        }
+        if (!alive) break;
+        // ---- the warp's statistics: common maximum, then the rescaled sums
+        float M = m, xlw = xl;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+            xlw = fmaxf(xlw, __shfl_xor_sync(0xffffffffu, xlw, o));
+        }
+        const float dmt = m - M;
+        const float f = ex2f(dmt * kLog2e);
+        float ssum = sum * f, ssde = (KIND == kLMargin) ? f * fmaf(dmt, sum, sde) : 0.f, ssx = sx;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+            ssx += __shfl_xor_sync(0xffffffffu, ssx, o);
+            if (KIND == kLMargin) ssde += __shfl_xor_sync(0xffffffffu, ssde, o);
+        }
+        if (lane == 0) {
+            const float xlv = lbi >= 0 ? xlw : 0.f;
+            float l = 0.f;
+            if (lbi != -1) {
+                if (KIND == kLSR) {
+                    l = kc.sumy * (M + __logf(ssum)) - kc.lb_neg * ssx - (kc.lb_pos - kc.lb_neg) * xlv;
+                } else {
+                    const float nother = lbi >= 0 ? float(C - 1) : float(C);
+                    const float sd = ssx - nother * M;
+                    const float sqx = ssde * __fdividef(1.f, ssum);
+                    const float mm = fmaxf(M, xlv);
+                    const float e_no = ssum * ex2f((M - mm) * kLog2e);
+                    const float e_lb = lbi >= 0 ? ex2f((xlv - mm) * kLog2e) : 0.f;
+                    l = (mm + __logf(e_no + e_lb)) - xlv + kc.half_lam * (sqx - kc.a * sd);
+                }
+            }
+            if (losses) losses[r] = from_f32<T>(l);
+            if (REDUCE && lbi != -1) {
+                acc_loss += double(l);
+                acc_cnt += 1.0;
+            }
+        }
+    }
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+}
+
 // Integer tuning override from the environment (tile size, ring depth, blocks per SM);
 // unset or unparsable -> the default.
 inline int tune_int(const char *name, int dflt) {
@@ -1652,6 +1839,25 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             kern<<<dim3(unsigned(grid)), kThreads, smem, stream>>>(prm, unused, unused);
         }
         return launch_status("softmax tile kernel launch");
+    }
+    if constexpr (!BWD) {
+        // ---- rows regime, forward, long rows: one warp per row, streamed (any row length)
+        if (prm.M == 1 && (size_t(prm.C) * es) % 16 == 0 && size_t(prm.C) * es >= 2 * size_t(kWarpRowChunk) &&
+            aligned_io && !getenv("B200_NO_ROWWARP")) {
+            const size_t smem = 128 + size_t(kWarpRowWarps) * kWarpRowStages * kWarpRowChunk;
+            // measured on config 5: 2 stages x 3 blocks per SM 223 us, 3 stages x 2 blocks 237 us,
+            // 2 KB chunks x 5 blocks 246 us (whole-row kernel below: 251 us)
+            const int per_sm = tune_int("B200_ROWWARP_CTAS", 3);
+            int64_t grid = int64_t(sms) * per_sm;
+            const int64_t need = (prm.N + kWarpRowWarps - 1) / kWarpRowWarps;
+            if (grid > need) grid = need;
+            if (grid > kMaxPartials) grid = kMaxPartials;
+            auto kern = rows_warp_fwd_kernel<T, KIND, REDUCE>;
+            int rc2;
+            if ((rc2 = set_smem(kern, smem)) != B200_OK) return rc2;
+            kern<<<dim3(unsigned(grid)), kWarpRowWarps * 32, smem, stream>>>(prm);
+            return launch_status("softmax warp-per-row forward kernel launch");
+        }
     }
     if (prm.M == 1 && prm.C >= 256 && size_t(prm.C) * es + 1024 <= kSmemLimit) {
         // ---- rows regime

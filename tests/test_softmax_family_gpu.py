@@ -21,6 +21,9 @@ SHAPES = [
     # forward in channel chunks (more than 20 classes, >= 512 pixels): last chunk of 9 / 1 / 5 channels,
     # ragged second box, several tiles per image
     (2, 41, (20, 30)), (1, 33, (16, 36)), (3, 21, (26, 30)), (1, 150, (40, 52)),
+    # long rows (M == 1, >= 8 KB): one warp per row, 4 KB chunks; whole chunks, ragged last chunk,
+    # more rows than warps in flight
+    (5, 4096, ()), (3, 5000, ()), (700, 2048, ()),
 ]
 
 
