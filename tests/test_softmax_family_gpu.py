@@ -218,3 +218,39 @@ def test_deterministic_and_status_clean():
             assert again.item() == first.item()
             assert torch.equal(g1, g2)
     _cabi.read_status(logits.device)
+
+
+@pytest.mark.parametrize("kind", ["lsr", "lmargin"])
+def test_statistics_backward_equals_recomputing_backward(kind):
+    """Many classes: the backward that uses the forward's saved statistics against the one that
+    recomputes the softmax, for every upstream-gradient mode (none, device scalar, per pixel)."""
+    from pytorch_loss import _cabi
+    lib = _cabi.load_library()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(21)
+    n, c, h, w = 2, 70, 24, 28                      # 672 pixels per image, 5 chunks (last of 6 channels)
+    x = (torch.randn(n, c, h, w, generator=g) * 2).to(dev)
+    y = labels_with_ignores(g, (n, h, w), c, 255, 0.1).to(dev)
+    m = h * w
+    hp = 0.1 if kind == "lsr" else 0.3
+    P, st = _cabi.ptr, _cabi.stream_ptr(dev)
+    assert lib.b200_softmax_stats_path(P(x), P(y), None, n, c, m, _cabi.F32) == 1
+    stats = torch.empty(n * m, 4, device=dev)
+    losses = torch.empty(n, h, w, device=dev)
+    fwd = getattr(lib, "b200_%s_forward_ex" % kind)
+    _cabi.check(fwd(P(x), P(y), P(losses), None, None, 0, P(stats), n, c, m, _cabi.F32, 255, hp, st))
+    ref_losses = torch.empty_like(losses)
+    _cabi.check(getattr(lib, "b200_%s_forward" % kind)(P(x), P(y), P(ref_losses), None, None, 0, n, c, m,
+                                                       _cabi.F32, 255, hp, st))
+    assert torch.allclose(losses, ref_losses, atol=1e-6, rtol=1e-6)
+    scalar = torch.tensor([0.37], device=dev)
+    per_px = torch.randn(n, h, w, generator=g).to(dev)
+    denom = torch.tensor([3.0], dtype=torch.float64, device=dev)
+    for mode, gout, dn in ((0, None, None), (1, scalar, denom), (2, per_px, None)):
+        got, want = torch.empty_like(x), torch.empty_like(x)
+        _cabi.check(getattr(lib, "b200_%s_backward_ex" % kind)(
+            P(x), P(y), P(stats), P(gout), mode, P(dn), P(got), n, c, m, _cabi.F32, 255, hp, st))
+        _cabi.check(getattr(lib, "b200_%s_backward" % kind)(
+            P(x), P(y), P(gout), mode, P(dn), P(want), n, c, m, _cabi.F32, 255, hp, st))
+        assert torch.allclose(got, want, atol=2e-6, rtol=1e-5), (kind, mode, float((got - want).abs().max()))
+    _cabi.read_status(dev)
