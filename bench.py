@@ -244,10 +244,11 @@ def direct_calls(wl, sets, device):
     denoms = [_cabi._vp(r.data_ptr() + 8) for r in recs]
     if wl.name == "focal":
         e = wl.elems
-        fwd = lambda i: _cabi.check(lib.b200_focal_forward(P(xs[i]), P(ys[i]), None, P(recs[i]), P(ws), ws.numel(),
-                                                           e, dt, 2.0, 0.25, st))
-        bwd = lambda i: _cabi.check(lib.b200_focal_backward(P(xs[i]), P(ys[i]), P(one), 1, denoms[i], P(grads[i]),
-                                                            e, dt, 2.0, 0.25, st))
+        # the module's training step: fused forward+backward kernel, then the rescale kernel that
+        # leaves at once for an upstream gradient of 1
+        fwd = lambda i: _cabi.check(lib.b200_focal_forward_backward_reduced(
+            P(xs[i]), P(ys[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(), None, 1.0 / e, e, dt, 2.0, 0.25, st))
+        bwd = lambda i: _cabi.check(lib.b200_rescale_gradient(P(grads[i]), P(one), e, dt, st))
         return fwd, bwd
     if wl.name == "lovasz":
         nbytes = int(lib.b200_lovasz_workspace_bytes(n, c, m, 1))

@@ -69,6 +69,26 @@ size_t b200_reduce_workspace_bytes(void);
  * B200_OK or B200_ERR_STATUS.  For tests and debugging; never needed for results. */
 int b200_read_status(void *workspace, void *stream);
 
+/* ---------------------------------------------------- fused training step ---
+ * The reference fuses forward and backward of the focal loss in
+ * focal_cpp.focalloss_forward_backward (csrc/focal_kernel.cu:246-297, unscaled gradient, then a
+ * `grads * grad_output` pass in Python, focal_loss.py:169).  For a REDUCED loss the final
+ * gradient can be written directly:
+ *   b200_focal_forward_backward_reduced: one pass; out = reduction record, grad_logits =
+ *       dloss/dlogits * grad_scale / *denom (denom: optional device double, e.g. the global
+ *       element count from b200_exchange_count; grad_scale: e.g. 1/E for 'mean').
+ *   b200_rescale_gradient: grad *= *grad_out in place (grad_out: device float); every block
+ *       leaves at once when *grad_out == 1, the upstream gradient of `loss.backward()`.
+ *   b200_exchange_count: out->count = count summed over the ranks attached to the workspace
+ *       (cross-GPU sum below); with nothing attached, out->count = count.
+ */
+int b200_focal_forward_backward_reduced(const void *logits, const void *labels, void *grad_logits,
+                                        void *out, void *workspace, size_t workspace_bytes,
+                                        const void *denom, float grad_scale, int64_t E, int dtype,
+                                        float gamma, float alpha, void *stream);
+int b200_rescale_gradient(void *grad, const float *grad_out, int64_t E, int dtype, void *stream);
+int b200_exchange_count(double count, void *out, void *workspace, size_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------- cross-GPU sum (optional) ---
  * No counterpart in the reference (it has no multi-GPU path for these losses).
  * With one process per GPU and the batch sharded over the ranks, reduction 'mean'

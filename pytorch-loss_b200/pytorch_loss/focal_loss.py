@@ -7,6 +7,8 @@ runs one forward kernel that reads logits and labels once and emits only the sum
 per-element loss tensor, no separate `.mean()` pass), and one backward kernel that
 recomputes the sigmoid and writes the already-scaled gradient.
 """
+import os
+
 import torch
 import torch.nn as nn
 import torch.amp as amp
@@ -97,14 +99,54 @@ class FocalSigmoidLossFuncV3FB(torch.autograd.Function):
 
 
 class _FocalReducedFunc(torch.autograd.Function):
-    """'mean' / 'sum' focal loss as one reducing kernel + one recomputing backward.
-    Returns a 0-dim float32 loss."""
+    """'mean' / 'sum' focal loss.  Returns a 0-dim float32 loss.
+
+    When the logits need a gradient, forward is the fused step: ONE kernel reads logits and
+    labels once, reduces the loss and writes the final gradient (already divided by the
+    element count for 'mean'); backward then only multiplies by the upstream gradient, and the
+    kernel that does so leaves at once when that gradient is 1, as it is for `loss.backward()`.
+    This is the reference's forward-backward fusion (FocalSigmoidLossFuncV3FB, focal_loss.py:152-171)
+    without its separate `grads * grad_output` pass.  A second backward through the same graph
+    (retain_graph) recomputes the gradient from the inputs.  Without a gradient to produce,
+    forward is the reducing kernel alone."""
+
+    @staticmethod
+    def _fused_forward(ctx, logits, labels, alpha, gamma, mean, group, dev, dt):
+        lib = _cabi.load_library()
+        rec = _cabi.new_record(dev)
+        exchange = _p2p.get_exchange(group, dev)
+        ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
+        grads = torch.empty_like(logits)
+        n = logits.numel()
+        denom = None
+        scale = 1.0
+        with torch.cuda.device(dev):
+            if mean and exchange is not None:
+                # the global element count has to be known before the gradients are written
+                cnt = _cabi.new_record(dev)
+                _cabi.check(lib.b200_exchange_count(float(n), _cabi.ptr(cnt), _cabi.ptr(ws), ws.numel(),
+                                                    _cabi.stream_ptr(dev)))
+                denom = cnt[:4].view(torch.float64)[1:]
+            elif mean:
+                scale = 1.0 / max(n, 1)
+            _cabi.check(lib.b200_focal_forward_backward_reduced(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
+                None if denom is None else _cabi._vp(denom.data_ptr()), float(scale), n, dt, float(gamma),
+                float(alpha), _cabi.stream_ptr(dev)))
+        ctx.fused = [grads]                  # handed out by the first backward
+        ctx.variables = logits, labels, alpha, gamma, (rec[:4].view(torch.float64)[1:] if mean else None)
+        return rec[4] if mean else rec[5]
 
     @staticmethod
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
     def forward(ctx, logits, labels, alpha, gamma, mean, group):
         dev, logits, labels, dt = _prep(logits, labels)
         lib = _cabi.load_library()
+        ctx.fused = None
+        nccl_group = _sharding.group_is_active(group) and _p2p.get_exchange(group, dev) is None
+        if ctx.needs_input_grad[0] and logits.numel() > 0 and not nccl_group and \
+                os.environ.get("B200_FOCAL_FUSED", "1") != "0":
+            return _FocalReducedFunc._fused_forward(ctx, logits, labels, alpha, gamma, mean, group, dev, dt)
         rec = _cabi.new_record(dev)
         exchange = _p2p.get_exchange(group, dev)      # sums over the ranks inside the kernel, if possible
         ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
@@ -125,6 +167,14 @@ class _FocalReducedFunc(torch.autograd.Function):
     @amp.custom_bwd(device_type='cuda')
     def backward(ctx, grad_output):
         logits, labels, alpha, gamma, denom = ctx.variables
+        if ctx.fused:
+            grads = ctx.fused.pop()
+            g = grad_output.to(torch.float32).reshape(-1)[:1].contiguous()
+            with torch.cuda.device(logits.device):
+                _cabi.check(_cabi.load_library().b200_rescale_gradient(
+                    _cabi.ptr(grads), _cabi.ptr(g), grads.numel(), _cabi.dtype_code(grads),
+                    _cabi.stream_ptr(logits.device)))
+            return grads, None, None, None, None, None
         grads = _focal_backward(logits, labels, grad_output, denom, alpha, gamma)
         return grads, None, None, None, None, None
 

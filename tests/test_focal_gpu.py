@@ -82,6 +82,41 @@ def test_focal_fp16_io():
     assert_grad_close(grad, want_grad, atol=TOL_F16 * float(want_grad.abs().max()), rtol=TOL_F16)
 
 
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_focal_fused_step(reduction, dtype, monkeypatch):
+    """The training step whose forward kernel already writes the gradient: an upstream gradient
+    other than 1 (rescale kernel, vector body and ragged tail), a second backward through the
+    same graph (recomputing kernel), a forward that needs no gradient, and equality with the
+    two-kernel path."""
+    P, O = _mods()
+    g = torch.Generator().manual_seed(16)
+    shape = (3, 2, 41, 67)                                   # 16482 elements: not a multiple of 4 or 8
+    logits = (torch.randn(shape, generator=g) * 2).to(dtype)
+    labels = (torch.rand(shape, generator=g) < 0.2).to(dtype)
+    want_loss, want_grad = O.focal_loss(logits.float(), labels.float(), 0.25, 2.0, reduction)
+    tol = dict(atol=TOL_F16 * float(want_grad.abs().max()) * 3, rtol=TOL_F16) if dtype == torch.float16 else {}
+    crit = P.FocalLossV3(reduction=reduction)
+
+    x = logits.cuda().requires_grad_(True)
+    loss = crit(x, labels.cuda())
+    (loss * 3.0).backward(retain_graph=True)
+    assert_loss_close(loss, want_loss, rtol=TOL_F16 if dtype == torch.float16 else 1e-5)
+    assert_grad_close(x.grad.float(), want_grad * 3.0, **({k: v * 3 if k == "atol" else v for k, v in tol.items()}))
+    x.grad = None
+    loss.backward()                                          # second trip: recomputed, not the saved tensor
+    assert_grad_close(x.grad.float(), want_grad, **tol)
+
+    with torch.no_grad():
+        assert_loss_close(crit(logits.cuda(), labels.cuda()), want_loss, rtol=TOL_F16 if dtype == torch.float16 else 1e-5)
+
+    fused_loss, fused_grad = run_module(crit, logits.cuda(), labels.cuda())
+    monkeypatch.setenv("B200_FOCAL_FUSED", "0")
+    plain_loss, plain_grad = run_module(crit, logits.cuda(), labels.cuda())
+    assert float(fused_loss) == float(plain_loss)
+    assert_grad_close(fused_grad.float(), plain_grad.float(), atol=1e-9 if dtype == torch.float32 else 1e-6, rtol=2e-3 if dtype == torch.float16 else 1e-6)
+
+
 def test_focal_rejects_cpu_and_bad_dtype():
     P, _ = _mods()
     crit = P.FocalLossV3()
