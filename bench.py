@@ -248,7 +248,7 @@ def direct_calls(wl, sets, device):
         # leaves at once for an upstream gradient of 1
         fwd = lambda i: _cabi.check(lib.b200_focal_forward_backward_reduced(
             P(xs[i]), P(ys[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(), None, 1.0 / e, e, dt, 2.0, 0.25, st))
-        bwd = lambda i: _cabi.check(lib.b200_rescale_gradient(P(grads[i]), P(one), e, dt, st))
+        bwd = lambda i: _cabi.check(lib.b200_rescale_gradient(P(grads[i]), P(one), None, e, dt, st))
         return fwd, bwd
     if wl.name == "lovasz":
         nbytes = int(lib.b200_lovasz_workspace_bytes(n, c, m, 1))

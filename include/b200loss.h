@@ -77,8 +77,14 @@ int b200_read_status(void *workspace, void *stream);
  *   b200_focal_forward_backward_reduced: one pass; out = reduction record, grad_logits =
  *       dloss/dlogits * grad_scale / *denom (denom: optional device double, e.g. the global
  *       element count from b200_exchange_count; grad_scale: e.g. 1/E for 'mean').
- *   b200_rescale_gradient: grad *= *grad_out in place (grad_out: device float); every block
- *       leaves at once when *grad_out == 1, the upstream gradient of `loss.backward()`.
+ *   b200_focal_forward_backward_predicted: the same for a 'mean' over a batch sharded across
+ *       GPUs, without a count exchange before it: the gradient is divided by *denom_state (device
+ *       double: the global count the previous call found; initialise with b200_exchange_count),
+ *       and after its cross-GPU sum the kernel stores predicted/actual count in *correction
+ *       (device float; exactly 1 while shapes do not change) and the actual count in *denom_state.
+ *   b200_rescale_gradient: grad *= *grad_out * *correction in place (device floats; correction
+ *       may be null); every block leaves at once when the product is 1, as it is for
+ *       `loss.backward()` in the steady state.
  *   b200_exchange_count: out->count = count summed over the ranks attached to the workspace
  *       (cross-GPU sum below); with nothing attached, out->count = count.
  */
@@ -86,7 +92,12 @@ int b200_focal_forward_backward_reduced(const void *logits, const void *labels, 
                                         void *out, void *workspace, size_t workspace_bytes,
                                         const void *denom, float grad_scale, int64_t E, int dtype,
                                         float gamma, float alpha, void *stream);
-int b200_rescale_gradient(void *grad, const float *grad_out, int64_t E, int dtype, void *stream);
+int b200_focal_forward_backward_predicted(const void *logits, const void *labels, void *grad_logits,
+                                          void *out, void *workspace, size_t workspace_bytes,
+                                          void *denom_state, float *correction, int64_t E, int dtype,
+                                          float gamma, float alpha, void *stream);
+int b200_rescale_gradient(void *grad, const float *grad_out, const float *correction, int64_t E, int dtype,
+                          void *stream);
 int b200_exchange_count(double count, void *out, void *workspace, size_t workspace_bytes, void *stream);
 
 /* ------------------------------------------------- cross-GPU sum (optional) ---

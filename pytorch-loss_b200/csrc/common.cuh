@@ -148,7 +148,8 @@ __device__ __forceinline__ void block_sum2(double &a, double &b, double *sh) {
 // partial (sum, count).  The block that takes the last ticket adds all partials
 // in a fixed order, writes the record and re-arms the ticket: deterministic,
 // no spinning, no second launch.  blockDim.x must be a multiple of 32, <= 1024.
-__device__ __forceinline__ void grid_reduce_finish(double sum, double cnt, void *workspace,
+// Returns true in exactly one thread of the grid: the one that has just written the record.
+__device__ __forceinline__ bool grid_reduce_finish(double sum, double cnt, void *workspace,
                                                    ReduceRecord *out, double *sh) {
     block_sum2(sum, cnt, sh);
     unsigned *ticket = reinterpret_cast<unsigned *>(workspace);
@@ -162,7 +163,7 @@ __device__ __forceinline__ void grid_reduce_finish(double sum, double cnt, void 
         s_last = (t == gridDim.x - 1) ? 1u : 0u;
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) return false;
     __threadfence();
     double a = 0.0, b = 0.0;
     for (unsigned i = threadIdx.x; i < gridDim.x; i += blockDim.x) {
@@ -227,7 +228,9 @@ __device__ __forceinline__ void grid_reduce_finish(double sum, double cnt, void 
         out->pad[0] = 0.f;
         out->pad[1] = 0.f;
         *ticket = 0u;
+        return true;
     }
+    return false;
 }
 
 // ------------------------------------------------- mbarrier + bulk-async (TMA)

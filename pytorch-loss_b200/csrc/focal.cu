@@ -38,7 +38,22 @@ struct FocalParams {
     int64_t E;
     float gamma, alpha;
     float host_scale;    // extra factor on the gradient (0 is read as 1): 1/E of a fused 'mean' step
+    double *denom_state; // optional: predicted divisor, replaced by the reduced count after the sum
+    float *correction;   // with denom_state: predicted / actual divisor of this call
 };
+
+// The fused step of a batch sharded over GPUs divides by the GLOBAL element count, which the
+// kernel only knows after its own cross-GPU sum.  It therefore divides by the count the previous
+// call found (*denom_state), and the thread that writes the record stores predicted / actual for
+// the rescale kernel and the actual count for the next call.  With unchanged shapes the
+// correction is exactly 1.  Every block has read *denom_state before it took its ticket, so
+// the overwrite cannot be seen by this launch.
+__device__ __forceinline__ void publish_denominator(const FocalParams &prm) {
+    if (!prm.denom_state) return;
+    const double used = *prm.denom_state, actual = prm.out->count;
+    *prm.correction = static_cast<float>(used / actual);
+    *prm.denom_state = actual;
+}
 
 template <bool GAMMA2>
 __device__ __forceinline__ void focal_core(float x, float y, float gamma, float alpha, float &loss,
@@ -142,7 +157,7 @@ __global__ void __launch_bounds__(kThreads) focal_kernel(const FocalParams prm) 
     if (REDUCE) {
         __shared__ double sh[64];
         const double cnt = (blockIdx.x == 0 && threadIdx.x == 0) ? double(prm.E) : 0.0;
-        grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh);
+        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh)) publish_denominator(prm);
     }
 }
 
@@ -303,7 +318,7 @@ __global__ void __launch_bounds__(kThreads) focal_kernel_unaligned(const FocalPa
     if (REDUCE) {
         __shared__ double sh[64];
         const double cnt = (blockIdx.x == 0 && threadIdx.x == 0) ? double(prm.E) : 0.0;
-        grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh);
+        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh)) publish_denominator(prm);
     }
 }
 
@@ -483,13 +498,49 @@ extern "C" int b200_focal_forward_backward_reduced(const void *logits, const voi
     return dispatch_focal<kFwdBwd, true>(prm, dtype, static_cast<cudaStream_t>(stream));
 }
 
+// The same step for a 'mean' over a batch sharded across GPUs (workspace with an exchange
+// attached).  The gradient is divided by *denom_state, the global element count the previous call
+// found (initialise it with b200_exchange_count); after the cross-GPU sum the kernel stores
+// predicted / actual count in *correction (1 while the shapes do not change; pass it to
+// b200_rescale_gradient) and the actual count in *denom_state.
+extern "C" int b200_focal_forward_backward_predicted(const void *logits, const void *labels, void *grad_logits,
+                                                     void *out, void *workspace, size_t workspace_bytes,
+                                                     void *denom_state, float *correction, int64_t E, int dtype,
+                                                     float gamma, float alpha, void *stream) {
+    if (E < 0 || !out || !denom_state || !correction) {
+        set_error("b200_focal_forward_backward_predicted: need E >= 0, out, denom_state and correction");
+        return B200_ERR_ARG;
+    }
+    if (!workspace || workspace_bytes < kReduceWorkspaceBytes) {
+        set_error("b200_focal_forward_backward_predicted: workspace of %zu bytes required", kReduceWorkspaceBytes);
+        return B200_ERR_WORKSPACE;
+    }
+    if (E > 0 && (!logits || !labels || !grad_logits)) {
+        set_error("b200_focal_forward_backward_predicted: null pointer");
+        return B200_ERR_ARG;
+    }
+    FocalParams prm{};
+    prm.logits = logits;
+    prm.labels = labels;
+    prm.grads = grad_logits;
+    prm.denom = static_cast<const double *>(denom_state);
+    prm.denom_state = static_cast<double *>(denom_state);
+    prm.correction = correction;
+    prm.workspace = workspace;
+    prm.out = static_cast<ReduceRecord *>(out);
+    prm.E = E;
+    prm.gamma = gamma;
+    prm.alpha = alpha;
+    return dispatch_focal<kFwdBwd, true>(prm, dtype, static_cast<cudaStream_t>(stream));
+}
+
 namespace b200 {
 namespace {
 // grad *= *g unless *g == 1 (the usual upstream gradient of a scalar loss): then every block
 // leaves at once and the stored gradient is already the answer.
 template <typename T>
-__global__ void __launch_bounds__(256) rescale_kernel(T *grad, const float *g, int64_t E) {
-    const float f = *g;
+__global__ void __launch_bounds__(256) rescale_kernel(T *grad, const float *g, const float *corr, int64_t E) {
+    const float f = corr ? *g * *corr : *g;
     if (f == 1.f) return;
     constexpr int V = 16 / int(sizeof(T));                 // elements per 16-byte access
     const bool aligned = (reinterpret_cast<uintptr_t>(grad) & 15) == 0;
@@ -526,8 +577,10 @@ __global__ void count_exchange_kernel(double count, void *workspace, ReduceRecor
 }  // namespace
 }  // namespace b200
 
-// In place: grad[i] *= *grad_out (a float in device memory); a no-op kernel when it is 1.
-extern "C" int b200_rescale_gradient(void *grad, const float *grad_out, int64_t E, int dtype, void *stream) {
+// In place: grad[i] *= *grad_out * *correction (floats in device memory; correction may be
+// null = 1); a no-op kernel when the product is 1.
+extern "C" int b200_rescale_gradient(void *grad, const float *grad_out, const float *correction, int64_t E,
+                                     int dtype, void *stream) {
     if (E < 0 || (E > 0 && (!grad || !grad_out))) {
         set_error("b200_rescale_gradient: bad arguments");
         return B200_ERR_ARG;
@@ -538,8 +591,8 @@ extern "C" int b200_rescale_gradient(void *grad, const float *grad_out, int64_t 
     const int64_t cap = int64_t(sm_count()) * 4;
     if (grid > cap) grid = cap;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == B200_F32) rescale_kernel<float><<<unsigned(grid), 256, 0, s>>>(static_cast<float *>(grad), grad_out, E);
-    else if (dtype == B200_F16) rescale_kernel<__half><<<unsigned(grid), 256, 0, s>>>(static_cast<__half *>(grad), grad_out, E);
+    if (dtype == B200_F32) rescale_kernel<float><<<unsigned(grid), 256, 0, s>>>(static_cast<float *>(grad), grad_out, correction, E);
+    else if (dtype == B200_F16) rescale_kernel<__half><<<unsigned(grid), 256, 0, s>>>(static_cast<__half *>(grad), grad_out, correction, E);
     else {
         set_error("b200_rescale_gradient: unknown dtype code %d", dtype);
         return B200_ERR_ARG;

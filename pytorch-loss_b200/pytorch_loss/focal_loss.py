@@ -111,7 +111,7 @@ class _FocalReducedFunc(torch.autograd.Function):
     forward is the reducing kernel alone."""
 
     @staticmethod
-    def _fused_forward(ctx, logits, labels, alpha, gamma, mean, group, dev, dt):
+    def _fused_forward(ctx, logits, labels, alpha, gamma, mean, group, dev, dt, state):
         lib = _cabi.load_library()
         rec = _cabi.new_record(dev)
         exchange = _p2p.get_exchange(group, dev)
@@ -120,33 +120,50 @@ class _FocalReducedFunc(torch.autograd.Function):
         n = logits.numel()
         denom = None
         scale = 1.0
+        correction = None
+        st = _cabi.stream_ptr(dev)
         with torch.cuda.device(dev):
             if mean and exchange is not None:
-                # the global element count has to be known before the gradients are written
-                cnt = _cabi.new_record(dev)
-                _cabi.check(lib.b200_exchange_count(float(n), _cabi.ptr(cnt), _cabi.ptr(ws), ws.numel(),
-                                                    _cabi.stream_ptr(dev)))
-                denom = cnt[:4].view(torch.float64)[1:]
+                # The gradients need the GLOBAL element count.  A module keeps the count its
+                # previous call found on the device and divides by that; the kernel checks it
+                # against the count it sums over the ranks and leaves the ratio for backward
+                # (1 unless a rank's shape changed).  Only the first call of a module, and calls
+                # without a module to hold the state, exchange the count in a kernel of its own.
+                key = (dev.index, id(exchange))
+                predicted = state.get(key) if state is not None else None
+                if predicted is None:
+                    cnt = _cabi.new_record(dev)
+                    _cabi.check(lib.b200_exchange_count(float(n), _cabi.ptr(cnt), _cabi.ptr(ws), ws.numel(), st))
+                    denom = cnt[:4].view(torch.float64)[1:]
+                    if state is not None:
+                        state[key] = predicted = denom.clone()
+                if predicted is not None:
+                    correction = torch.empty(1, dtype=torch.float32, device=dev)
             elif mean:
                 scale = 1.0 / max(n, 1)
-            _cabi.check(lib.b200_focal_forward_backward_reduced(
-                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
-                None if denom is None else _cabi._vp(denom.data_ptr()), float(scale), n, dt, float(gamma),
-                float(alpha), _cabi.stream_ptr(dev)))
-        ctx.fused = [grads]                  # handed out by the first backward
+            if correction is not None:
+                _cabi.check(lib.b200_focal_forward_backward_predicted(
+                    _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws),
+                    ws.numel(), _cabi.ptr(predicted), _cabi.ptr(correction), n, dt, float(gamma), float(alpha), st))
+            else:
+                _cabi.check(lib.b200_focal_forward_backward_reduced(
+                    _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
+                    None if denom is None else _cabi._vp(denom.data_ptr()), float(scale), n, dt, float(gamma),
+                    float(alpha), st))
+        ctx.fused = [grads, correction]      # handed out by the first backward
         ctx.variables = logits, labels, alpha, gamma, (rec[:4].view(torch.float64)[1:] if mean else None)
         return rec[4] if mean else rec[5]
 
     @staticmethod
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
-    def forward(ctx, logits, labels, alpha, gamma, mean, group):
+    def forward(ctx, logits, labels, alpha, gamma, mean, group, state=None):
         dev, logits, labels, dt = _prep(logits, labels)
         lib = _cabi.load_library()
         ctx.fused = None
         nccl_group = _sharding.group_is_active(group) and _p2p.get_exchange(group, dev) is None
         if ctx.needs_input_grad[0] and logits.numel() > 0 and not nccl_group and \
                 os.environ.get("B200_FOCAL_FUSED", "1") != "0":
-            return _FocalReducedFunc._fused_forward(ctx, logits, labels, alpha, gamma, mean, group, dev, dt)
+            return _FocalReducedFunc._fused_forward(ctx, logits, labels, alpha, gamma, mean, group, dev, dt, state)
         rec = _cabi.new_record(dev)
         exchange = _p2p.get_exchange(group, dev)      # sums over the ranks inside the kernel, if possible
         ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
@@ -168,15 +185,16 @@ class _FocalReducedFunc(torch.autograd.Function):
     def backward(ctx, grad_output):
         logits, labels, alpha, gamma, denom = ctx.variables
         if ctx.fused:
-            grads = ctx.fused.pop()
+            grads, correction = ctx.fused
+            ctx.fused = None
             g = grad_output.to(torch.float32).reshape(-1)[:1].contiguous()
             with torch.cuda.device(logits.device):
                 _cabi.check(_cabi.load_library().b200_rescale_gradient(
-                    _cabi.ptr(grads), _cabi.ptr(g), grads.numel(), _cabi.dtype_code(grads),
+                    _cabi.ptr(grads), _cabi.ptr(g), _cabi.ptr(correction), grads.numel(), _cabi.dtype_code(grads),
                     _cabi.stream_ptr(logits.device)))
-            return grads, None, None, None, None, None
+            return grads, None, None, None, None, None, None
         grads = _focal_backward(logits, labels, grad_output, denom, alpha, gamma)
-        return grads, None, None, None, None, None
+        return grads, None, None, None, None, None, None
 
 
 class FocalLossV3(nn.Module):
@@ -198,9 +216,10 @@ class FocalLossV3(nn.Module):
         self.gamma = gamma
         self.reduction = reduction
         self.process_group = process_group
+        self._count_state = {}               # per device: the global element count of the last call
 
     def forward(self, logits, label):
         if self.reduction == 'mean' or self.reduction == 'sum':
             return _FocalReducedFunc.apply(logits, label, self.alpha, self.gamma,
-                                           self.reduction == 'mean', self.process_group)
+                                           self.reduction == 'mean', self.process_group, self._count_state)
         return FocalSigmoidLossFuncV3.apply(logits, label, self.alpha, self.gamma)

@@ -65,6 +65,18 @@ def _worker(rank, world, port, out, p2p):
     for _ in range(5):
         loss = crit(logits[lo:hi].to(dev), lab[lo:hi].to(dev))
     errs.append((abs(float(loss) - float(want_loss)) / abs(float(want_loss)), 0.0))
+    # focal 'mean' divides by a predicted global element count: right on a repeated call, wrong
+    # when a rank's shard changes size (the rescale kernel then corrects the gradient), right again
+    fcrit = cases[2][0]
+    uneven = [(0, 1), (1, 4)] if world == 2 else [_sharding.shard_bounds(4, world, r) for r in range(world)]
+    for bounds in ([(lo, hi)] * 2 + [uneven[rank]] * 2 + [(lo, hi)]):
+        a, b = bounds
+        x = logits[a:b].to(dev).requires_grad_(True)
+        loss = fcrit(x, flabels[a:b].to(dev))
+        loss.backward()
+        want_loss, want_grad = cases[2][2]
+        errs.append((abs(float(loss) - float(want_loss)) / abs(float(want_loss)),
+                     float((x.grad.cpu() - want_grad[a:b]).abs().max())))
     from pytorch_loss import _cabi, _p2p
     _cabi.read_status(dev)
     for ex in _p2p._contexts.values():
