@@ -100,6 +100,30 @@ int b200_rescale_gradient(void *grad, const float *grad_out, const float *correc
                           void *stream);
 int b200_exchange_count(double count, void *out, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The same fusion for the two softmax losses (no counterpart in the reference, whose
+ * LSR_forward/LSR_backward, csrc/lsr_kernel.cu:191-318, and large-margin pair,
+ * csrc/large_margin_kernel.cu:354-481, always read the logits twice per step):
+ *   b200_softmax_fused_step_path: 1 when the layout has a fused step (channel columns of a
+ *       pixel tile fit in shared memory, 16-byte aligned rows), else 0.
+ *   b200_count_valid: out->count = number of labels != ignore_index (summed over attached
+ *       ranks): the 'mean' divisor, needed on the device before gradients are written.
+ *   b200_{lsr,lmargin}_forward_backward_reduced: one pass over the logits; out = reduction
+ *       record of the loss, grad_logits = dloss/dlogits / *denom (denom: optional device double).
+ *       B200_ERR_UNSUPPORTED when b200_softmax_fused_step_path says 0.
+ * Backward of the step is b200_rescale_gradient. */
+int b200_softmax_fused_step_path(const void *logits, const int64_t *labels, const void *grad_logits,
+                                 int64_t N, int64_t C, int64_t M, int dtype);
+int b200_count_valid(const int64_t *labels, int64_t P, int64_t ignore_index, void *out,
+                     void *workspace, size_t workspace_bytes, void *stream);
+int b200_lsr_forward_backward_reduced(const void *logits, const int64_t *labels, void *grad_logits,
+                                      void *out, void *workspace, size_t workspace_bytes,
+                                      const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
+                                      int64_t ignore_index, float smooth, void *stream);
+int b200_lmargin_forward_backward_reduced(const void *logits, const int64_t *labels, void *grad_logits,
+                                          void *out, void *workspace, size_t workspace_bytes,
+                                          const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
+                                          int64_t ignore_index, float lam, void *stream);
+
 /* ------------------------------------------------- cross-GPU sum (optional) ---
  * No counterpart in the reference (it has no multi-GPU path for these losses).
  * With one process per GPU and the batch sharded over the ranks, reduction 'mean'

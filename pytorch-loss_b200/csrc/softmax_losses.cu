@@ -596,11 +596,17 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     m = slice_combine_max_first(m, red, ks, KS, TPT, pix, ok);
                     if (!ok) break;
                 }
-                // target logits (forward only; backward overwrites the tile with e^{x-m})
+                // target logits.  Forward: slice 0 reads them (nobody writes the tile).  Backward
+                // overwrites the tile with e^{x-m}, so the fused step (backward + loss sum) lets the
+                // slice that owns the label channel read its logit ahead of its own sweep.
                 float2 xl = splat2(0.f);
                 if (!BWD && ks == 0) {
                     if (lbi[0] >= 0) xl.x = to_f32(tile[bxo + lbi[0] * TP]);
                     if (lbi[1] >= 0) xl.y = to_f32(tile[bxo + lbi[1] * TP + 1]);
+                }
+                if (BWD && REDUCE) {
+                    if (own0) xl.x = to_f32(tile[bxo + lbi[0] * TP]);
+                    if (own1) xl.y = to_f32(tile[bxo + lbi[1] * TP + 1]);
                 }
                 // ---- phase 2: sum of exponentials, sum of logits
                 float2 sum, sx;
@@ -613,14 +619,14 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                         const pk_t x = ld_pk(q);
                         const pk_t e = pex2(pfma(x, l2e, nml));
                         psum = padd(psum, e);
-                        if (!BWD) psx = padd(psx, x);
+                        if (!BWD || REDUCE) psx = padd(psx, x);
                         if (BWD) st_pk(q, e);
                     }
                     sum = upk2(psum);
                     sx = upk2(psx);
                 }
                 if (KS > 1) {
-                    if (BWD) sum = slice_combine<false>(sum, red + plane, ks, KS, TPT, pix);
+                    if (BWD && !REDUCE) sum = slice_combine<false>(sum, red + plane, ks, KS, TPT, pix);
                     else slice_sum2(sum, sx, red + plane, plane, ks, KS, TPT, pix);
                 }
                 if (!BWD) {
@@ -644,6 +650,19 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.empty[s]);
                 } else {
+                    if (REDUCE) {
+                        // fused step: the loss is a sum of terms, so slice 0 adds the softmax part
+                        // and the label's owner the target part
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            if (ks == 0 && lbi[i] != -1) {
+                                const float si = i ? sum.y : sum.x, mi = i ? m.y : m.x, sxi = i ? sx.y : sx.x;
+                                acc32 += kc.sumy * (mi + __logf(si)) - kc.lb_neg * sxi;
+                                cnt32 += 1;
+                            }
+                            if (i ? own1 : own0) acc32 -= (kc.lb_pos - kc.lb_neg) * (i ? xl.y : xl.x);
+                        }
+                    }
                     // ---- phase 3: g = (sumy * e / s - eps/C) * scale, then the target term
                     float2 a, b;
                     a.x = lbi[0] != -1 ? kc.sumy * __fdividef(psc.x, sum.x) : 0.f;
@@ -760,6 +779,15 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.empty[s]);
                 } else {
+                    if (REDUCE && ks == 0) {          // fused step: every slice holds the same loss
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            if (lbi[i] != -1) {
+                                acc32 += loss[i];
+                                cnt32 += 1;
+                            }
+                        }
+                    }
                     // g_j = scale * ( r*q + lam/2 * (q*(d + 1 - Sqx) - a) ),  q = e^d / s'
                     //     = q * (A + B*d) + Cc     with per-pixel A, B, Cc
                     float2 qa, qb, cc, qs;
@@ -1998,10 +2026,128 @@ int backward(const char *who, const void *logits, const int64_t *labels, const v
     return dispatch<KIND, true>(prm, dtype, false, static_cast<cudaStream_t>(stream));
 }
 
+// The fused training step runs in the TMA tile kernel only (whole channel columns resident in
+// shared memory, so one read of the logits serves the loss and the gradient).
+inline bool fused_step_eligible(size_t es, const void *logits, const void *grads, const void *labels, int64_t N,
+                                int64_t C, int64_t M) {
+    if (N < 1 || M <= 1 || size_t(C) * 32 * es + 8192 > kSmemLimit) return false;
+    return (M * es) % 16 == 0 && aligned16(logits) && aligned16(grads) && aligned16(labels) &&
+           M < (int64_t(1) << 31) && N < (int64_t(1) << 31);
+}
+
+template <int KIND>
+int fused_step(const char *who, const void *logits, const int64_t *labels, void *grad_logits, void *out,
+               void *workspace, size_t workspace_bytes, const void *denom, int64_t N, int64_t C, int64_t M,
+               int dtype, int64_t ignore_index, float hp, void *stream) {
+    int rc = check_shape(who, N, C, M);
+    if (rc != B200_OK) return rc;
+    if (!out || !workspace || workspace_bytes < kReduceWorkspaceBytes) {
+        set_error("%s: out and a workspace of %zu bytes are required", who, kReduceWorkspaceBytes);
+        return B200_ERR_WORKSPACE;
+    }
+    if (!logits || !labels || !grad_logits) {
+        set_error("%s: null pointer", who);
+        return B200_ERR_ARG;
+    }
+    const size_t es = dtype == B200_F16 ? 2 : 4;
+    if (!fused_step_eligible(es, logits, grad_logits, labels, N, C, M)) {
+        set_error("%s: this layout has no fused step (ask b200_softmax_fused_step_path first)", who);
+        return B200_ERR_UNSUPPORTED;
+    }
+    SoftmaxParams prm{};
+    prm.logits = logits;
+    prm.labels = labels;
+    prm.grads = grad_logits;
+    prm.denom = static_cast<const double *>(denom);
+    prm.workspace = workspace;
+    prm.out = static_cast<ReduceRecord *>(out);
+    prm.N = N;
+    prm.C = C;
+    prm.M = M;
+    prm.ignore = ignore_index;
+    prm.k = make_consts(KIND, C, hp);
+    return dispatch<KIND, true>(prm, dtype, true, static_cast<cudaStream_t>(stream));
+}
+
+// Number of labels != ignore, 16-byte loads, four in flight per thread.
+__global__ void __launch_bounds__(256) count_valid_kernel(const int64_t *labels, int64_t P, int64_t ignore,
+                                                          void *workspace, ReduceRecord *out) {
+    __shared__ double sh[64];
+    const bool al = (reinterpret_cast<uintptr_t>(labels) & 15u) == 0;
+    const int64_t nvec = al ? P / 2 : 0;
+    const longlong2 *v = reinterpret_cast<const longlong2 *>(labels);
+    const int64_t stride = int64_t(gridDim.x) * 256;
+    int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
+    int cnt = 0;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        longlong2 a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) a[u] = __ldcs(v + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) cnt += int(a[u].x != ignore) + int(a[u].y != ignore);
+    }
+    for (; i < nvec; i += stride) {
+        const longlong2 a = __ldcs(v + i);
+        cnt += int(a.x != ignore) + int(a.y != ignore);
+    }
+    for (int64_t j = nvec * 2 + int64_t(blockIdx.x) * 256 + threadIdx.x; j < P; j += stride)
+        cnt += int(labels[j] != ignore);
+    grid_reduce_finish(0.0, double(cnt), workspace, out, sh);
+}
+
 }  // namespace
 }  // namespace b200
 
 using namespace b200;
+
+// out->count = number of labels != ignore_index among `P` (summed over the ranks attached to the
+// workspace, if any); out->sum = 0.  The divisor of a 'mean' that the fused step needs on the
+// device BEFORE it writes gradients.
+extern "C" int b200_count_valid(const int64_t *labels, int64_t P, int64_t ignore_index, void *out,
+                                void *workspace, size_t workspace_bytes, void *stream) {
+    if (P < 0 || !out || (P > 0 && !labels)) {
+        set_error("b200_count_valid: bad arguments");
+        return B200_ERR_ARG;
+    }
+    if (!workspace || workspace_bytes < kReduceWorkspaceBytes) {
+        set_error("b200_count_valid: workspace of %zu bytes required", kReduceWorkspaceBytes);
+        return B200_ERR_WORKSPACE;
+    }
+    int64_t grid = (P / 2 + 256 * 4 - 1) / (256 * 4);
+    const int64_t cap = int64_t(sm_count()) * 8;
+    if (grid > cap) grid = cap;
+    if (grid < 1) grid = 1;
+    count_valid_kernel<<<unsigned(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        labels, P, ignore_index, workspace, static_cast<ReduceRecord *>(out));
+    return launch_status("label count kernel launch");
+}
+
+// 1 when (logits, labels, grad_logits, N, C, M, dtype) has a fused training step, else 0.
+extern "C" int b200_softmax_fused_step_path(const void *logits, const int64_t *labels, const void *grad_logits,
+                                            int64_t N, int64_t C, int64_t M, int dtype) {
+    if (dtype != B200_F32 && dtype != B200_F16) return 0;
+    if (C < 1 || C >= (int64_t(1) << 31)) return 0;
+    return fused_step_eligible(dtype == B200_F16 ? 2 : 4, logits, grad_logits, labels, N, C, M) ? 1 : 0;
+}
+
+// Loss sum (record in `out`) and FINAL gradient (divided by *denom when given: a device double,
+// e.g. out->count of b200_count_valid) of the label-smooth cross entropy in one pass over the logits.
+extern "C" int b200_lsr_forward_backward_reduced(const void *logits, const int64_t *labels, void *grad_logits,
+                                                 void *out, void *workspace, size_t workspace_bytes,
+                                                 const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
+                                                 int64_t ignore_index, float smooth, void *stream) {
+    return fused_step<kLSR>("b200_lsr_forward_backward_reduced", logits, labels, grad_logits, out, workspace,
+                            workspace_bytes, denom, N, C, M, dtype, ignore_index, smooth, stream);
+}
+
+// The same for the large-margin softmax loss.
+extern "C" int b200_lmargin_forward_backward_reduced(const void *logits, const int64_t *labels, void *grad_logits,
+                                                     void *out, void *workspace, size_t workspace_bytes,
+                                                     const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
+                                                     int64_t ignore_index, float lam, void *stream) {
+    return fused_step<kLMargin>("b200_lmargin_forward_backward_reduced", logits, labels, grad_logits, out, workspace,
+                           workspace_bytes, denom, N, C, M, dtype, ignore_index, lam, stream);
+}
 
 extern "C" int b200_lsr_forward(const void *logits, const int64_t *labels, void *losses, void *out,
                                 void *workspace, size_t workspace_bytes, int64_t N, int64_t C,

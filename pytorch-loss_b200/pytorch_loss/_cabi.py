@@ -41,6 +41,10 @@ SIGNATURES = {
     "b200_focal_forward_backward_predicted": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _i64, _int, _f32, _f32, _vp]),
     "b200_rescale_gradient": (_int, [_vp, _vp, _vp, _i64, _int, _vp]),
     "b200_exchange_count": (_int, [_f64, _vp, _vp, _sz, _vp]),
+    "b200_softmax_fused_step_path": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int]),
+    "b200_count_valid": (_int, [_vp, _i64, _i64, _vp, _vp, _sz, _vp]),
+    "b200_lsr_forward_backward_reduced": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
+    "b200_lmargin_forward_backward_reduced": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
     "b200_focal_forward_noalloc": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _f32, _f32, _vp]),
     "b200_lsr_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
     "b200_lsr_backward": (_int, [_vp, _vp, _vp, _int, _vp, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),

@@ -1,6 +1,8 @@
 """Host logic shared by the two softmax-family losses (label-smooth CE and large-margin
 softmax): argument checks, the per-pixel forward/backward calls and the fused
 'mean'/'sum' autograd Function.  `kind` selects the C-ABI entry points."""
+import os
+
 import torch
 import torch.amp as amp
 
@@ -94,6 +96,39 @@ def backward(kind, logits, labels, grad_output, denom, ignore_index, hyper, stat
     return grads
 
 
+_ENTRY_FUSED = {
+    "lsr": "b200_lsr_forward_backward_reduced",
+    "lmargin": "b200_lmargin_forward_backward_reduced",
+}
+
+
+def fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange):
+    """The training step in one pass over the logits, or None when this layout has none.
+    Returns (record, gradient) with the gradient already divided by the number of valid pixels
+    for 'mean' (counted on the device by a pass over the labels alone; with an `_p2p.Exchange`
+    both the count and the loss sum are global)."""
+    dev, logits, labels, n, c, m, dt = _prep(logits, labels)
+    lib = _cabi.load_library()
+    grads = torch.empty_like(logits)
+    if n * m == 0 or not lib.b200_softmax_fused_step_path(_cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads),
+                                                          n, c, m, dt):
+        return None
+    rec = _cabi.new_record(dev)
+    ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
+    st = _cabi.stream_ptr(dev)
+    denom = None
+    with torch.cuda.device(dev):
+        if mean:
+            cnt = _cabi.new_record(dev)
+            _cabi.check(lib.b200_count_valid(_cabi.ptr(labels), n * m, int(ignore_index), _cabi.ptr(cnt),
+                                             _cabi.ptr(ws), ws.numel(), st))
+            denom = cnt[:4].view(torch.float64)[1:]
+        _cabi.check(getattr(lib, _ENTRY_FUSED[kind])(
+            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
+            None if denom is None else _cabi._vp(denom.data_ptr()), n, c, m, dt, int(ignore_index), float(hyper), st))
+    return rec, grads, logits, labels
+
+
 class ReducedLossFunc(torch.autograd.Function):
     """'mean' / 'sum' over valid pixels as ONE reducing forward kernel (no per-pixel loss
     tensor, no separate count or sum pass) and ONE backward kernel that recomputes the
@@ -106,6 +141,18 @@ class ReducedLossFunc(torch.autograd.Function):
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
     def forward(ctx, logits, labels, kind, hyper, ignore_index, mean, group):
         exchange = _p2p.get_exchange(group, logits.device) if logits.is_cuda else None
+        ctx.fused = None
+        nccl_group = exchange is None and _sharding.group_is_active(group)
+        if ctx.needs_input_grad[0] and logits.is_cuda and not nccl_group and \
+                os.environ.get("B200_SOFTMAX_FUSED", "1") != "0":
+            # the fused step: loss sum and final gradient from one read of the logits
+            step = fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange)
+            if step is not None:
+                rec, grads, logits, labels = step
+                ctx.fused = grads
+                ctx.variables = (logits, labels, kind, hyper, ignore_index,
+                                 (rec[:4].view(torch.float64)[1:] if mean else None), None)
+                return rec[4] if mean else rec[5]
         rec, _, logits, labels, stats = forward_reduced(kind, logits, labels, ignore_index, hyper,
                                                         exchange=exchange, want_stats=True)
         sum_count = rec[:4].view(torch.float64)
@@ -121,5 +168,14 @@ class ReducedLossFunc(torch.autograd.Function):
     @amp.custom_bwd(device_type='cuda')
     def backward(ctx, grad_output):
         logits, labels, kind, hyper, ignore_index, denom, stats = ctx.variables
+        if ctx.fused is not None:
+            # first trip through the graph: the gradient is there, times the upstream gradient
+            grads, ctx.fused = ctx.fused, None
+            g = grad_output.to(torch.float32).reshape(-1)[:1].contiguous()
+            with torch.cuda.device(logits.device):
+                _cabi.check(_cabi.load_library().b200_rescale_gradient(
+                    _cabi.ptr(grads), _cabi.ptr(g), None, grads.numel(), _cabi.dtype_code(grads),
+                    _cabi.stream_ptr(logits.device)))
+            return grads, None, None, None, None, None, None
         grads = backward(kind, logits, labels, grad_output, denom, ignore_index, hyper, stats)
         return grads, None, None, None, None, None, None

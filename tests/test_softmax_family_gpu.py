@@ -254,3 +254,42 @@ def test_statistics_backward_equals_recomputing_backward(kind):
             P(x), P(y), P(gout), mode, P(dn), P(want), n, c, m, _cabi.F32, 255, hp, st))
         assert torch.allclose(got, want, atol=2e-6, rtol=1e-5), (kind, mode, float((got - want).abs().max()))
     _cabi.read_status(dev)
+
+
+@pytest.mark.parametrize("kind", ["lsr", "lmargin"])
+@pytest.mark.parametrize("shape", [(2, 19, (32, 36)), (3, 7, (16, 20)), (1, 150, (40, 52)), (2, 64, (8, 12))],
+                         ids=lambda s: "x".join(map(str, (s[0], s[1]) + s[2])))
+@pytest.mark.parametrize("reduction", ["mean", "sum"])
+def test_fused_step(kind, shape, reduction, monkeypatch):
+    """The training step that reads the logits once (loss sum + final gradient in the backward tile
+    kernel): upstream gradient other than 1, a second backward through the same graph, a forward
+    without gradient, and the same numbers as the separate forward and backward kernels."""
+    import pytorch_loss  # noqa: F401
+    from pytorch_loss import _cabi
+    n, c, sp = shape
+    g = torch.Generator().manual_seed(77 + c)
+    logits = torch.randn((n, c) + sp, generator=g) * 1.5
+    labels = labels_with_ignores(g, (n,) + sp, c, 255, 0.2)
+    crit, oracle = _crit(kind, reduction, 255)
+    want_loss, want_grad = oracle(logits, labels)
+    lib = _cabi.load_library()
+    xg, yg = logits.cuda(), labels.cuda()
+    assert lib.b200_softmax_fused_step_path(_cabi.ptr(xg), _cabi.ptr(yg), _cabi.ptr(torch.empty_like(xg)),
+                                            n, c, labels[0].numel(), 0) == 1
+
+    x = xg.clone().requires_grad_(True)
+    loss = crit(x, yg)
+    (loss * 0.5).backward(retain_graph=True)
+    assert_loss_close(loss, want_loss)
+    assert_grad_close(x.grad, want_grad * 0.5)
+    x.grad = None
+    loss.backward()
+    assert_grad_close(x.grad, want_grad)
+    with torch.no_grad():
+        assert_loss_close(crit(xg, yg), want_loss)
+
+    fused_loss, fused_grad = run_module(crit, xg, yg)
+    monkeypatch.setenv("B200_SOFTMAX_FUSED", "0")
+    plain_loss, plain_grad = run_module(crit, xg, yg)
+    assert_loss_close(fused_loss, plain_loss.cpu(), rtol=2e-6)
+    assert_grad_close(fused_grad, plain_grad.cpu())
