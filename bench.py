@@ -267,15 +267,32 @@ def direct_calls(wl, sets, device):
         new_labels = [torch.empty_like(y) for y in ys]
         n_min = (n * m) // 16
 
+        cnts = [_cabi.new_record(device) for _ in sets]
+
         def fwd(i):
             _cabi.check(lib.b200_ohem_label(P(xs[i]), P(ys[i]), P(new_labels[i]), P(ows), nbytes, n, c, m, dt, 255,
                                             0.7, n_min, st))
-            _cabi.check(lib.b200_lsr_forward(P(xs[i]), P(new_labels[i]), None, P(recs[i]), P(ws), ws.numel(),
-                                             n, c, m, dt, 255, 0.0, st))
-        bwd = lambda i: _cabi.check(lib.b200_lsr_backward(P(xs[i]), P(new_labels[i]), P(one), 1, denoms[i],
-                                                          P(grads[i]), n, c, m, dt, 255, 0.0, st))
+            _cabi.check(lib.b200_count_valid(P(new_labels[i]), n * m, 255, P(cnts[i]), P(ws), ws.numel(), st))
+            _cabi.check(lib.b200_lsr_forward_backward_reduced(
+                P(xs[i]), P(new_labels[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(),
+                _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255, 0.0, st))
+        bwd = lambda i: _cabi.check(lib.b200_rescale_gradient(P(grads[i]), P(one), None, wl.elems, dt, st))
         return fwd, bwd
     stem, hyper, ign = {"lsr": ("lsr", 0.1, 255), "lsr_rows": ("lsr", 0.1, -100), "lmargin": ("lmargin", 0.3, 255)}[wl.name]
+    if os.environ.get("B200_SOFTMAX_FUSED", "1") != "0":
+        # the module's training step: count of valid labels, then ONE pass over the logits that sums
+        # the loss and writes the final gradient; backward is the rescale kernel (upstream gradient 1)
+        if not lib.b200_softmax_fused_step_path(P(xs[0]), P(ys[0]), P(grads[0]), n, c, m, dt):
+            raise SystemExit("bench: workload %s has no fused step on this build" % wl.name)
+        f_step = getattr(lib, "b200_%s_forward_backward_reduced" % stem)
+        cnts = [_cabi.new_record(device) for _ in sets]
+
+        def fwd(i):
+            _cabi.check(lib.b200_count_valid(P(ys[i]), n * m, ign, P(cnts[i]), P(ws), ws.numel(), st))
+            _cabi.check(f_step(P(xs[i]), P(ys[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(),
+                               _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, ign, hyper, st))
+        bwd = lambda i: _cabi.check(lib.b200_rescale_gradient(P(grads[i]), P(one), None, wl.elems, dt, st))
+        return fwd, bwd
     if lib.b200_softmax_stats_path(P(xs[0]), P(ys[0]), P(grads[0]), n, c, m, dt):
         # many classes: the module hands per-pixel statistics from forward to backward
         f_fwd, f_bwd = getattr(lib, "b200_%s_forward_ex" % stem), getattr(lib, "b200_%s_backward_ex" % stem)

@@ -7,6 +7,7 @@ logits, then labels (or the label cell grid), then the ignore mask.  "N(0, v)" i
 mean 0, variance v.
 """
 import math
+import os
 
 import torch
 
@@ -40,14 +41,18 @@ class Workload:
             return 12 * e                    # fused step: logits and labels read once, gradient written once
         if self.name == "ohem":
             # relabelling: logits and labels read, labels written (4E + 16P; scores and the select
-            # passes over them, <= 16P more, not counted) + cross entropy forward 4E + 8P
-            return 8 * e + 24 * p
+            # passes over them, <= 16P more, not counted) + label count 8P + fused cross entropy
+            # step (logits read, gradient written, labels read) 8E + 8P
+            return 12 * e + 32 * p
         if self.name == "lovasz":
             # the passes over ALL elements: keys (read logits, write keys) 8E, prune count 4E,
             # compaction (read keys, write dJ = 0) 8E.  The sort of the kept elements (~7% of E
             # on this workload's random logits: two 16-byte scatter passes, three histogram reads,
             # the 12-byte Jaccard pass) is data dependent and not counted.
             return 20 * e + 8 * p
+        if self.fused_softmax():
+            # label count (8P), then the fused step: logits read, gradient written, labels read
+            return 2 * s * e + 16 * p
         return s * e + 8 * p
 
     def bytes_backward(self):
@@ -58,7 +63,13 @@ class Workload:
             return 0                         # upstream gradient 1: the rescale kernel has nothing to do
         if self.name == "lovasz":
             return 12 * e + 8 * p
+        if self.name == "ohem" or self.fused_softmax():
+            return 0                         # upstream gradient 1: the rescale kernel has nothing to do
         return 2 * s * e + 8 * p
+
+    def fused_softmax(self):
+        """The softmax workloads run the fused training step unless B200_SOFTMAX_FUSED=0."""
+        return self.name in ("lsr", "lsr_rows", "lmargin") and os.environ.get("B200_SOFTMAX_FUSED", "1") != "0"
 
     def bytes_step(self):
         return self.bytes_forward() + self.bytes_backward()
@@ -82,7 +93,10 @@ class Workload:
         if self.name == "focal":
             return "b200_focal_forward_backward_reduced", "b200_rescale_gradient"
         if self.name == "ohem":
-            return "b200_ohem_label+b200_lsr_forward", "b200_lsr_backward"
+            return "b200_ohem_label+b200_count_valid+b200_lsr_forward_backward_reduced", "b200_rescale_gradient"
+        if self.fused_softmax():
+            stem = "lmargin" if self.name == "lmargin" else "lsr"
+            return "b200_count_valid+b200_%s_forward_backward_reduced" % stem, "b200_rescale_gradient"
         stem = {"lsr": "lsr", "lsr_rows": "lsr", "focal": "focal", "lmargin": "lmargin", "lovasz": "lovasz"}[self.name]
         return "b200_%s_forward" % stem, "b200_%s_backward" % stem
 

@@ -1269,20 +1269,30 @@ __device__ __forceinline__ void block_reduce2(float &a, float &b, float *sh, int
     }
 }
 
-constexpr int kRowsCompute = 512;
+constexpr int kRowsCompute = 448;   // 14 compute warps + loader + storer = 16 warps: three blocks per SM at 40 registers
 constexpr int kRowsBlock = kRowsCompute + 64;
 
+// (register cap = the blocks per SM the launch asks for: backward and the fused step, BWD && REDUCE,
+// run three per SM; uncapped, the fused step took 56 registers and fell to two blocks)
 template <typename T, int KIND, bool BWD, bool REDUCE>
-__global__ void __launch_bounds__(kRowsBlock)
+__global__ void __launch_bounds__(kRowsBlock, BWD ? 3 : 2)
 rows_pipe_kernel(const SoftmaxParams prm) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ PipeBarriers bars;
     __shared__ double sh_red[64];
     __shared__ float sh_stat[32 * 3];
+    // fused step: the loss sums live in shared memory (thread 0 alone touches them) and the label's
+    // owner hands its logit to thread 0 through sh_xl, so the row loop carries no extra registers
+    __shared__ double sh_acc[2];
+    __shared__ float sh_xl;
 
     const int C = static_cast<int>(prm.C), NS = prm.stages;
     unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     const size_t stage_bytes = (size_t(C) * sizeof(T) + 127) & ~size_t(127);
+    if (BWD && REDUCE && threadIdx.x == 0) {
+        sh_acc[0] = 0.0;
+        sh_acc[1] = 0.0;
+    }
     const int tid = threadIdx.x;
     unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
     const uint32_t row_bytes = uint32_t(C) * sizeof(T);
@@ -1356,6 +1366,8 @@ rows_pipe_kernel(const SoftmaxParams prm) {
                 }
             } else if (!BWD && tid == 0 && lbi >= 0) {
                 xl = to_f32(row[lbi]);
+            } else if (BWD && REDUCE && own) {
+                sh_xl = to_f32(row[lbi]);    // fused step: read by the thread that will overwrite it
             }
             // ---- phase 1: maximum (half rows: on the packed halves, exact and four values per
             // instruction-pair instead of a conversion and a compare each)
@@ -1383,6 +1395,8 @@ rows_pipe_kernel(const SoftmaxParams prm) {
             } else {
                 float dummy = 0.f;
                 block_reduce2<true>(red1[0], dummy, sh_stat, kRowsCompute);
+                // after that exchange's barrier, and before the next one lets an owner write again
+                if (BWD && REDUCE && tid == 0 && lbi >= 0) xl = sh_xl;
             }
             const float m = red1[0];
 
@@ -1397,7 +1411,7 @@ rows_pipe_kernel(const SoftmaxParams prm) {
                         const float2 x = pair_of(xv, q);
                         const float2 e = ex2_2(fma2(x, splat2(kLog2e), nml));
                         sum2 = add2(sum2, e);
-                        if (!BWD) sx2 = add2(sx2, x);
+                        if (!BWD || REDUCE) sx2 = add2(sx2, x);
                         if (BWD) set_pair(xv, q, e);
                     }
                     if (BWD) *reinterpret_cast<V *>(row + v * VN) = xv;
@@ -1418,6 +1432,14 @@ rows_pipe_kernel(const SoftmaxParams prm) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.empty[s]);
                 } else {
+                    if (REDUCE) {
+                        // fused step
+                        if (tid == 0 && lbi != -1) {
+                            sh_acc[0] += double(kc.sumy * (m + __logf(ssum)) - kc.lb_neg * ssx -
+                                                (kc.lb_pos - kc.lb_neg) * xl);
+                            sh_acc[1] += 1.0;
+                        }
+                    }
                     const float2 a = splat2(lbi != -1 ? kc.sumy * __fdividef(psc, ssum) : 0.f);
                     const float2 b = splat2(lbi != -1 ? -kc.lb_neg * psc : 0.f);
                     for (int v = tid; v < nvec; v += kRowsCompute) {
@@ -1480,6 +1502,10 @@ rows_pipe_kernel(const SoftmaxParams prm) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bars.empty[s]);
                 } else {
+                    if (REDUCE && tid == 0 && lbi != -1) {      // fused step
+                        sh_acc[0] += double((mm + __logf(s_all)) - xl + kc.half_lam * (sqx - kc.a * sd));
+                        sh_acc[1] += 1.0;
+                    }
                     const float sc = lbi != -1 ? psc : 0.f;
                     const float2 qa = splat2((rr + kc.half_lam * (1.f - sqx)) * sc);
                     const float2 qb = splat2(kc.half_lam * sc);
@@ -1502,6 +1528,10 @@ rows_pipe_kernel(const SoftmaxParams prm) {
                 }
             }
         }
+    }
+    if (BWD && REDUCE && threadIdx.x == 0) {
+        acc_loss = sh_acc[0];
+        acc_cnt = sh_acc[1];
     }
     if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
 }
@@ -2026,11 +2056,16 @@ int backward(const char *who, const void *logits, const int64_t *labels, const v
     return dispatch<KIND, true>(prm, dtype, false, static_cast<cudaStream_t>(stream));
 }
 
-// The fused training step runs in the TMA tile kernel only (whole channel columns resident in
-// shared memory, so one read of the logits serves the loss and the gradient).
+// The fused training step runs in the TMA tile kernel and in the whole-row kernel: both keep all
+// channels of a pixel (a row) resident in shared memory, so one read of the logits serves the
+// loss and the gradient.
 inline bool fused_step_eligible(size_t es, const void *logits, const void *grads, const void *labels, int64_t N,
                                 int64_t C, int64_t M) {
-    if (N < 1 || M <= 1 || size_t(C) * 32 * es + 8192 > kSmemLimit) return false;
+    if (N < 1 || M < 1) return false;
+    if (M == 1)
+        return C >= 256 && size_t(C) * es + 1024 <= kSmemLimit && (size_t(C) * es) % 16 == 0 && aligned16(logits) &&
+               aligned16(grads);
+    if (size_t(C) * 32 * es + 8192 > kSmemLimit) return false;
     return (M * es) % 16 == 0 && aligned16(logits) && aligned16(grads) && aligned16(labels) &&
            M < (int64_t(1) << 31) && N < (int64_t(1) << 31);
 }

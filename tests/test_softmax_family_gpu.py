@@ -257,7 +257,8 @@ def test_statistics_backward_equals_recomputing_backward(kind):
 
 
 @pytest.mark.parametrize("kind", ["lsr", "lmargin"])
-@pytest.mark.parametrize("shape", [(2, 19, (32, 36)), (3, 7, (16, 20)), (1, 150, (40, 52)), (2, 64, (8, 12))],
+@pytest.mark.parametrize("shape", [(2, 19, (32, 36)), (3, 7, (16, 20)), (1, 150, (40, 52)), (2, 64, (8, 12)),
+                                   (5, 4096, ()), (700, 2048, ()), (3, 1000, ())],
                          ids=lambda s: "x".join(map(str, (s[0], s[1]) + s[2])))
 @pytest.mark.parametrize("reduction", ["mean", "sum"])
 def test_fused_step(kind, shape, reduction, monkeypatch):
