@@ -78,16 +78,24 @@ class Workload:
     # behind the entry point) from the ncu captures summarised under profiles/, taken on reduced
     # batches and scaled by the element count (traffic grows in proportion).  Written gradients
     # that are still in the 126 MB L2 when the kernel ends are not counted by those counters.
-    MEASURED_TRAFFIC = {
-        "focal": (9.92, 0.0), "lsr": (4.45, 5.72), "lmargin": (4.15, 7.49),
-        "lovasz": (22.3, 11.5), "lsr_rows": (2.01, 3.15), "ohem": (9.9, 5.72),
+    MEASURED_TRAFFIC = {                     # fused training steps (forward entry = the whole step)
+        "focal": (9.92, 0.0), "lsr": (6.16, 0.0), "lmargin": (7.44, 0.0),
+        "lovasz": (22.3, 11.5), "lsr_rows": (3.23, 0.0), "ohem": (11.67, 0.0),
+    }
+    MEASURED_TRAFFIC_SEPARATE = {            # separate forward and backward kernels (B200_SOFTMAX_FUSED=0)
+        "lsr": (4.45, 5.72), "lmargin": (4.15, 7.49), "lsr_rows": (2.01, 3.15),
     }
 
+    def _traffic(self):
+        if self.name in self.MEASURED_TRAFFIC_SEPARATE and not self.fused_softmax():
+            return self.MEASURED_TRAFFIC_SEPARATE[self.name]
+        return self.MEASURED_TRAFFIC[self.name]
+
     def traffic_forward(self):
-        return self.MEASURED_TRAFFIC[self.name][0] * self.elems
+        return self._traffic()[0] * self.elems
 
     def traffic_backward(self):
-        return self.MEASURED_TRAFFIC[self.name][1] * self.elems
+        return self._traffic()[1] * self.elems
 
     def entries(self):
         if self.name == "focal":
