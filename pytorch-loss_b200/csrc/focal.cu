@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(kRingBlock) focal_ring_kernel(const FocalParam
     }
     if (REDUCE) {
         const double cnt = (blockIdx.x == 0 && tid == 0) ? double(prm.E) : 0.0;
-        grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh);
+        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh)) publish_denominator(prm);
     }
 }
 
@@ -342,8 +342,9 @@ int launch_focal(const FocalParams &prm, cudaStream_t stream) {
                     (!prm.losses || aligned16(prm.losses)) && (!prm.grads || aligned16(prm.grads)) &&
                     (prm.grad_mode != 2 || aligned16(prm.grad_out));
     // the ring wins for the read-only forward (8% at the 16.7 M-element size); with a gradient
-    // stream to write, plain loads + stores are as fast and simpler
-    if (al && MODE == kFwd && !getenv("B200_FOCAL_NO_RING")) {
+    // stream to write, plain loads + stores are as fast and simpler (fused step, measured with
+    // B200_FOCAL_RING_STEP=1: ring 40.1 us at its best geometry, plain 39.1 us)
+    if (al && (MODE == kFwd || (kFusedStep && getenv("B200_FOCAL_RING_STEP"))) && !getenv("B200_FOCAL_NO_RING")) {
         constexpr size_t smem = 128 + size_t(kRingStages) * 2 * kRingChunkBytes;
         const int per_sm = eb && atoi(eb) > 0 ? atoi(eb) : int((220 * 1024) / (smem + 1024));
         const int64_t chunk_elems = kRingChunkBytes / sizeof(T);
