@@ -131,6 +131,8 @@ class _FocalReducedFunc(torch.autograd.Function):
                 # without a module to hold the state, exchange the count in a kernel of its own.
                 key = (dev.index, id(exchange))
                 predicted = state.get(key) if state is not None else None
+                if predicted is None and torch.cuda.is_current_stream_capturing():
+                    state = None             # memory allocated during a capture must not outlive the graph
                 if predicted is None:
                     cnt = _cabi.new_record(dev)
                     _cabi.check(lib.b200_exchange_count(float(n), _cabi.ptr(cnt), _cabi.ptr(ws), ws.numel(), st))
