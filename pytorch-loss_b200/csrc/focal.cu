@@ -539,15 +539,16 @@ namespace b200 {
 namespace {
 // grad *= *g unless *g == 1 (the usual upstream gradient of a scalar loss): then every block
 // leaves at once and the stored gradient is already the answer.
+constexpr int kRescaleThreads = 1024;
 template <typename T>
-__global__ void __launch_bounds__(256) rescale_kernel(T *grad, const float *g, const float *corr, int64_t E) {
+__global__ void __launch_bounds__(kRescaleThreads) rescale_kernel(T *grad, const float *g, const float *corr, int64_t E) {
     const float f = corr ? *g * *corr : *g;
     if (f == 1.f) return;
     constexpr int V = 16 / int(sizeof(T));                 // elements per 16-byte access
     const bool aligned = (reinterpret_cast<uintptr_t>(grad) & 15) == 0;
     const int64_t nvec = aligned ? E / V : 0;
-    const int64_t stride = int64_t(gridDim.x) * 256;
-    int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
+    const int64_t stride = int64_t(gridDim.x) * kRescaleThreads;
+    int64_t i = int64_t(blockIdx.x) * kRescaleThreads + threadIdx.x;
     uint4 *g4 = reinterpret_cast<uint4 *>(grad);
     for (; i + 3 * stride < nvec; i += 4 * stride) {        // four independent accesses in flight
         uint4 v[4];
@@ -568,7 +569,7 @@ __global__ void __launch_bounds__(256) rescale_kernel(T *grad, const float *g, c
         for (int k = 0; k < V; ++k) e[k] = from_f32<T>(to_f32(e[k]) * f);
         g4[i] = v;
     }
-    for (int64_t j = nvec * V + int64_t(blockIdx.x) * 256 + threadIdx.x; j < E; j += stride)
+    for (int64_t j = nvec * V + int64_t(blockIdx.x) * kRescaleThreads + threadIdx.x; j < E; j += stride)
         grad[j] = from_f32<T>(to_f32(grad[j]) * f);
 }
 __global__ void count_exchange_kernel(double count, void *workspace, ReduceRecord *out) {
@@ -587,13 +588,14 @@ extern "C" int b200_rescale_gradient(void *grad, const float *grad_out, const fl
         return B200_ERR_ARG;
     }
     if (E == 0) return B200_OK;
-    // a small grid: the usual call (upstream gradient 1) only has to start and leave
-    int64_t grid = (E + 256 * 16 - 1) / (256 * 16);
-    const int64_t cap = int64_t(sm_count()) * 4;
+    // one block of 1024 threads per SM at most: the usual call (upstream gradient 1) only has to
+    // start and leave, and 148 x 1024 threads x 4 vectors in flight still cover the memory latency
+    int64_t grid = (E + kRescaleThreads * 16 - 1) / (kRescaleThreads * 16);
+    const int64_t cap = int64_t(sm_count());
     if (grid > cap) grid = cap;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == B200_F32) rescale_kernel<float><<<unsigned(grid), 256, 0, s>>>(static_cast<float *>(grad), grad_out, correction, E);
-    else if (dtype == B200_F16) rescale_kernel<__half><<<unsigned(grid), 256, 0, s>>>(static_cast<__half *>(grad), grad_out, correction, E);
+    if (dtype == B200_F32) rescale_kernel<float><<<unsigned(grid), kRescaleThreads, 0, s>>>(static_cast<float *>(grad), grad_out, correction, E);
+    else if (dtype == B200_F16) rescale_kernel<__half><<<unsigned(grid), kRescaleThreads, 0, s>>>(static_cast<__half *>(grad), grad_out, correction, E);
     else {
         set_error("b200_rescale_gradient: unknown dtype code %d", dtype);
         return B200_ERR_ARG;
