@@ -76,6 +76,14 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_first(self, timeout=3.0):
+        """Blocks until the sampler has delivered its first line (or `timeout` seconds): the start
+        of nvidia-smi (NVML initialisation over every GPU of the box, once per rank) must not fall
+        into the timed region, which lasts about a millisecond."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.lines and time.perf_counter() - t0 < timeout:
+            time.sleep(0.01)
+
     def __exit__(self, *exc):
         if self.proc is not None:
             time.sleep(0.15)
@@ -373,6 +381,9 @@ def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e):
     barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(device.index) as clocks:
+        clocks.wait_first()
+        run_steps(args.warmup)
+        barrier()
         start.record()
         run_steps(args.steps)
         end.record()
