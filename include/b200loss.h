@@ -105,8 +105,12 @@ int b200_exchange_count(double count, void *out, void *workspace, size_t workspa
  * csrc/large_margin_kernel.cu:354-481, always read the logits twice per step):
  *   b200_softmax_fused_step_path: 1 when the layout has a fused step (channel columns of a
  *       pixel tile fit in shared memory, 16-byte aligned rows), else 0.
- *   b200_count_valid: out->count = number of labels != ignore_index (summed over attached
- *       ranks): the 'mean' divisor, needed on the device before gradients are written.
+ *   b200_count_valid: out->count = number of labels != ignore_index: the 'mean' divisor, needed
+ *       on the device before gradients are written.  With ranks attached (cross-GPU sum below)
+ *       the kernel only POSTS its count to the peers and leaves out->count = -1; the next
+ *       b200_{lsr,lmargin}_forward_backward_reduced / *_backward call on the same workspace that
+ *       gets `denom` = &out->count collects the ranks' counts while its first tiles load, stores
+ *       the sum there and divides by it -- so no kernel sits waiting for a peer between the two.
  *   b200_{lsr,lmargin}_forward_backward_reduced: one pass over the logits; out = reduction
  *       record of the loss, grad_logits = dloss/dlogits / *denom (denom: optional device double).
  *       B200_ERR_UNSUPPORTED when b200_softmax_fused_step_path says 0.
@@ -136,14 +140,17 @@ int b200_lmargin_forward_backward_reduced(const void *logits, const int64_t *lab
  *
  * The context is `b200_exchange_ctx_bytes()` bytes of device memory laid out as
  *     int32 world; int32 rank; uint32 poll_limit; uint32 reserved;
- *     uint64 *seq;              // one zero-initialised uint64 in this rank's memory
+ *     uint64 *seq;              // eight zero-initialised uint64 in this rank's memory
  *     void  *slots[16];         // slots[p]: rank p's slot array as mapped in THIS
  *                               // process (p == rank: the local array); each array is
  *                               // b200_exchange_slot_bytes(world) bytes, zero-initialised
  * The peers' arrays are ordinary device allocations opened through CUDA IPC (or any
- * other peer mapping); the kernel only STORES to them and polls its own array.  A
- * wait that exceeds poll_limit polls sets status bit 0x100 (b200_read_status) and
- * the record then holds the local sums.  exchange_ctx == NULL detaches.
+ * other peer mapping); the kernel only STORES to them and polls its own array.  Messages
+ * are 8-byte words that carry their own flag (no fence between data and flag) and a tag
+ * (count / loss sum).  A wait that exceeds poll_limit polls sets status bit 0x100, a message
+ * with a foreign tag (the ranks' call sequences differ) sets 0x200 (b200_read_status); in
+ * both cases the record's sum, count and mean are NaN, never a silently local or stale
+ * number.  exchange_ctx == NULL detaches.
  */
 /* Lets kernels of the calling thread's current device store into `peer_device`'s memory
  * (cudaDeviceEnablePeerAccess; already enabled counts as success). */
@@ -205,7 +212,9 @@ int b200_focal_forward_backward(const void *logits, const void *labels, void *lo
  *     `stream` first.  Two calls that overlap on the GPU (different streams or threads)
  *     race on it: serialise them.
  * Neither this function nor anything it calls uses cudaMalloc, cudaFree or an allocating
- * library routine.  Results are identical to b200_focal_forward on the same input. */
+ * library routine.  Per-element losses are bit-identical to b200_focal_forward's; the sum,
+ * count and mean agree with it to the rounding of the reduction (another grid, so another
+ * summation order: ~1e-7 relative, the count exactly). */
 int b200_focal_forward_noalloc(const void *logits, const void *labels, void *losses, void *out,
                                int64_t E, int dtype, float gamma, float alpha, void *stream);
 

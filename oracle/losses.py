@@ -120,9 +120,9 @@ def large_margin_softmax(logits, labels, lam=0.3, ignore_index=255, reduction='m
     return _reduce(loss_px, n_valid, reduction), grad
 
 
-def _lovasz_group(x, labels, ignore_index):
+def _lovasz_group(x, labels, ignore_index, upstream=None):
     """One group (all pixels of `x` [n, C, *] sorted together): per-class loss [C] and
-    its gradient.  Follows LovaszSoftmaxV1.forward (reference lovasz_softmax.py:31-61):
+    its gradient for an upstream gradient of ones, or of `upstream` [C].  Follows LovaszSoftmaxV1.forward (reference lovasz_softmax.py:31-61):
     drop ignored pixels, errs = |one_hot - softmax|, sort descending per class, Jaccard
     index of the sorted prefix, adjacent difference, dot product."""
     x = x.detach().clone().requires_grad_(True)
@@ -145,7 +145,7 @@ def _lovasz_group(x, labels, ignore_index):
         if n_samples > 1:
             jacc[:, 1:] = jacc[:, 1:] - jacc[:, :-1]
     losses = torch.einsum('ab,ab->a', errs_sort, jacc)
-    losses.sum().backward()
+    (losses.sum() if upstream is None else (losses * upstream.to(losses.dtype)).sum()).backward()
     return losses.detach(), x.grad
 
 

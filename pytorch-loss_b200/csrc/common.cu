@@ -140,7 +140,7 @@ int b200_read_status(void *workspace, void *stream) {
 
 size_t b200_exchange_ctx_bytes(void) { return sizeof(b200::ExchangeCtx); }
 size_t b200_exchange_slot_bytes(int world) {
-    return world > 0 ? size_t(2) * size_t(world) * sizeof(b200::ExchangeSlot) : 0;
+    return world > 0 ? size_t(b200::kExchangeSets) * size_t(world) * sizeof(b200::ExchangeSlot) : 0;
 }
 
 int b200_enable_peer_access(int peer_device) {

@@ -30,31 +30,43 @@ constexpr int kMaxPartials = 65536;
 constexpr size_t kPartialsOffset = 64;
 constexpr size_t kReduceWorkspaceBytes = kPartialsOffset + size_t(kMaxPartials) * 16;
 
-// Cross-GPU sum of [sum, count] inside the reducing kernel (one process per GPU, batch
-// sharded over the ranks).  Every rank owns an array of slots that its peers can write
-// (peer-mapped device memory); the block that finishes a rank's reduction stores its pair into
-// slot [seq & 1][rank] of EVERY rank (its own included), then waits -- bounded -- until all
-// `world` slots of its own array carry this call's sequence number, and adds them in rank
-// order, so all ranks get the same bits.  Plain peer stores and local polls: no peer loads,
-// no multicast, no atomics across GPUs.  The sequence number is a device-side counter, so
-// replaying a captured graph keeps working.  Two slot sets suffice: a rank cannot start call
-// k+2 before every peer has finished reading call k (it needs their call k+1 message first).
-struct ExchangeSlot {       // 32 bytes
-    double sum;
-    double count;
-    unsigned long long seq;
-    unsigned long long pad;
+// Cross-GPU sum of [sum, count] inside the reducing kernels (one process per GPU, batch
+// sharded over the ranks).  Every rank owns an array of message slots that its peers can write
+// (peer-mapped device memory).  A message is five 8-byte words, each {32 data bits, 32-bit
+// flag}: the two doubles in four words and a tag word.  The flag is derived from the call's
+// sequence number, so a word validates itself: the sender needs no fence between data and
+// flag and the receiver polls ITS OWN memory until all five words carry the flag.  Plain peer
+// stores and local polls only: no peer loads, no multicast, no atomics across GPUs.
+//   post    lane p of one warp stores this rank's message into slot [seq & 3][rank] of rank p
+//   collect lane p polls slot [seq & 3][p] of this rank's own array -- bounded -- and lane 0
+//           adds the pairs in rank order, so every rank gets the same bits
+// The sequence number is a device-side counter (graph replays keep working).  Four slot sets:
+// a message may still be unread while the next one of the same rank is posted (the count of
+// valid labels is posted by one kernel and collected by the next), and a rank cannot post
+// message k+4 before every peer has collected message k, because it collects k+2 or k+3 first
+// and those need the peers' posts, which follow their own collection of k.
+// The tag names what the message carries (a count, a loss sum).  Ranks whose call sequences
+// differ (one took a path with one exchange, another a path with two) meet a foreign tag or
+// never see the flag: both give NaN sums, status bit 0x200 / 0x100, and never a silently
+// wrong number.
+struct ExchangeSlot {       // 64 bytes
+    unsigned long long w[8];    // w[0..3]: sum lo/hi, count lo/hi; w[4]: tag; each | flag << 32
 };
+constexpr int kExchangeSets = 4;
+constexpr unsigned kTagSum = 0x53554d21u;      // 'SUM!'
+constexpr unsigned kTagCount = 0x434e5421u;    // 'CNT!'
 constexpr int kMaxExchangeRanks = 16;
 struct ExchangeCtx {        // lives in device memory; filled by the host once (layout is ABI)
     int world;
     int rank;
-    unsigned poll_limit;    // polls of one slot before the wait gives up (status bit 0x100)
+    unsigned poll_limit;    // polls of one slot before a wait gives up (status bit 0x100)
     unsigned reserved;
-    unsigned long long *seq;                    // this rank's call counter
-    ExchangeSlot *slots[kMaxExchangeRanks];     // slots[p]: rank p's array [2][world]
+    unsigned long long *seq;                    // [0]: this rank's call counter; [1]: sequence
+                                                // number of a count that is posted, not collected
+    ExchangeSlot *slots[kMaxExchangeRanks];     // slots[p]: rank p's array [kExchangeSets][world]
 };
 constexpr size_t kExchangeCtxOffset = 8;
+constexpr double kPendingCount = -1.0;          // record.count while the global count is in flight
 
 struct ReduceRecord {       // the 32-byte "out" record of the C ABI
     double sum;
@@ -144,13 +156,127 @@ __device__ __forceinline__ void block_sum2(double &a, double &b, double *sh) {
     }
 }
 
+// ---- cross-GPU messages (see ExchangeSlot).  All three functions are called by ONE full warp.
+
+__device__ __forceinline__ unsigned exchange_flag(unsigned long long seq) {
+    return unsigned(seq % 0xffffffffull) + 1u;          // never 0: fresh slots are zero
+}
+__device__ __forceinline__ unsigned long long ll_word(unsigned data, unsigned flag) {
+    return (static_cast<unsigned long long>(flag) << 32) | data;
+}
+// Takes the next sequence number (lane 0 increments the device counter) and stores this rank's
+// message {a, b, tag} into every rank's array.  Returns the sequence number in all lanes.
+__device__ __forceinline__ unsigned long long exchange_post(ExchangeCtx *ex, unsigned tag, double a, double b) {
+    const int lane = threadIdx.x & 31;
+    unsigned long long seq = 0;
+    if (lane == 0) seq = ++ex->seq[0];
+    seq = __shfl_sync(0xffffffffu, seq, 0);
+    const int world = ex->world;
+    if (lane < world) {
+        volatile unsigned long long *dst =
+            ex->slots[lane][(seq & (kExchangeSets - 1)) * world + ex->rank].w;
+        const unsigned flag = exchange_flag(seq);
+        const unsigned long long ua = __double_as_longlong(a), ub = __double_as_longlong(b);
+        dst[0] = ll_word(unsigned(ua), flag);
+        dst[1] = ll_word(unsigned(ua >> 32), flag);
+        dst[2] = ll_word(unsigned(ub), flag);
+        dst[3] = ll_word(unsigned(ub >> 32), flag);
+        dst[4] = ll_word(tag, flag);
+    }
+    return seq;
+}
+// Waits (bounded) for message `seq` of every rank in this rank's own array and adds the pairs in
+// rank order.  Returns 0 in all lanes on success (sums valid in lane 0), else the status bits:
+// 0x100 a rank's message did not arrive within poll_limit polls, 0x200 it carried another tag.
+__device__ __forceinline__ unsigned exchange_collect(ExchangeCtx *ex, unsigned long long seq, unsigned tag,
+                                                     double &a, double &b) {
+    const int lane = threadIdx.x & 31;
+    const int world = ex->world;
+    const unsigned flag = exchange_flag(seq);
+    unsigned bad = 0;
+    double ma = 0.0, mb = 0.0;
+    if (lane < world) {
+        const volatile unsigned long long *src =
+            ex->slots[ex->rank][(seq & (kExchangeSets - 1)) * world + lane].w;
+        unsigned long long w[5];
+        unsigned polls = 0;
+        for (;;) {
+            bool all = true;
+#pragma unroll
+            for (int k = 0; k < 5; ++k) {
+                w[k] = src[k];
+                all = all && unsigned(w[k] >> 32) == flag;
+            }
+            if (all) break;
+            if (++polls > ex->poll_limit) {
+                bad = 0x100u;
+                break;
+            }
+            __nanosleep(32);
+        }
+        if (!bad && unsigned(w[4]) != tag) bad = 0x200u;
+        ma = __longlong_as_double((w[1] << 32) | (w[0] & 0xffffffffull));
+        mb = __longlong_as_double((w[3] << 32) | (w[2] & 0xffffffffull));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+    a = 0.0;
+    b = 0.0;
+    for (int p = 0; p < world; ++p) {       // rank order: the same bits on every rank
+        a += __shfl_sync(0xffffffffu, ma, p);
+        b += __shfl_sync(0xffffffffu, mb, p);
+    }
+    return bad;
+}
+
+__device__ __forceinline__ ExchangeCtx *exchange_of(void *workspace) {
+    return workspace ? *reinterpret_cast<ExchangeCtx **>(reinterpret_cast<char *>(workspace) + kExchangeCtxOffset)
+                     : nullptr;
+}
+
+// The divisor of a 'mean' as the gradient kernels read it: a device double that may still be
+// in flight between the GPUs (kPendingCount, left by grid_reduce_finish<defer>).  Warp 0 of block
+// 0 then collects the ranks' counts and stores the sum; every other thread that needs the value
+// polls the double (bounded).  Warp 0 of block 0 must call this with all 32 lanes; it is among the
+// first blocks to run, so the pollers cannot starve it.  NaN when the wait ran out.
+__device__ __forceinline__ double resolve_count(const double *denom, void *workspace) {
+    const volatile double *vd = denom;
+    double d = *vd;
+    if (d >= 0.0 || d != d) return d;                    // the usual case: already there (or NaN)
+    ExchangeCtx *ex = exchange_of(workspace);
+    if (ex && blockIdx.x == 0 && threadIdx.x < 32) {
+        double a, b;
+        const unsigned bad = exchange_collect(ex, ex->seq[1], kTagCount, a, b);
+        if (threadIdx.x == 0) {
+            if (bad) {
+                atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, bad);
+                b = __longlong_as_double(0x7ff8000000000000ll);
+            }
+            *const_cast<volatile double *>(vd) = b;
+            __threadfence();
+        }
+        return __shfl_sync(0xffffffffu, b, 0);
+    }
+    const unsigned limit = ex ? ex->poll_limit : (1u << 20);
+    for (unsigned polls = 0; polls <= limit; ++polls) {
+        d = *vd;
+        if (d >= 0.0 || d != d) return d;
+        __nanosleep(64);
+    }
+    return __longlong_as_double(0x7ff8000000000000ll);
+}
+
 // Final step of a reducing forward kernel.  Every block calls it once with its
 // partial (sum, count).  The block that takes the last ticket adds all partials
 // in a fixed order, writes the record and re-arms the ticket: deterministic,
 // no spinning, no second launch.  blockDim.x must be a multiple of 32, <= 1024.
+// With an exchange attached to the workspace the pair is first added over the ranks (message
+// tag `tag`).  `defer`: only post this rank's pair and leave record.count = kPendingCount; the
+// kernel that needs the global count collects it (resolve_count).
 // Returns true in exactly one thread of the grid: the one that has just written the record.
 __device__ __forceinline__ bool grid_reduce_finish(double sum, double cnt, void *workspace,
-                                                   ReduceRecord *out, double *sh) {
+                                                   ReduceRecord *out, double *sh,
+                                                   unsigned tag = kTagSum, bool defer = false) {
     block_sum2(sum, cnt, sh);
     unsigned *ticket = reinterpret_cast<unsigned *>(workspace);
     double2 *partials =
@@ -172,51 +298,20 @@ __device__ __forceinline__ bool grid_reduce_finish(double sum, double cnt, void 
         b += p.y;
     }
     block_sum2(a, b, sh);
-    ExchangeCtx *ex = *reinterpret_cast<ExchangeCtx **>(reinterpret_cast<char *>(workspace) + kExchangeCtxOffset);
+    if (threadIdx.x >= 32) return false;
+    ExchangeCtx *ex = exchange_of(workspace);
     if (ex) {
-        __shared__ double s_pair[2];
-        __shared__ unsigned long long s_seq;
-        __shared__ int s_fail;
-        if (threadIdx.x == 0) {
-            s_pair[0] = a;
-            s_pair[1] = b;
-            s_seq = ++(*ex->seq);
-            s_fail = 0;
-        }
-        __syncthreads();
-        const int world = ex->world;
-        const unsigned long long q = s_seq;
-        if (int(threadIdx.x) < world) {
-            // my pair to rank threadIdx.x: data, fence, then the sequence number
-            volatile ExchangeSlot *dst = ex->slots[threadIdx.x] + (q & 1ull) * world + ex->rank;
-            dst->sum = s_pair[0];
-            dst->count = s_pair[1];
-            __threadfence_system();
-            dst->seq = q;
-            // rank threadIdx.x's pair in my own array
-            volatile ExchangeSlot *src = ex->slots[ex->rank] + (q & 1ull) * world + threadIdx.x;
-            unsigned polls = 0;
-            while (src->seq != q) {
-                if (++polls > ex->poll_limit) {
-                    s_fail = 1;
-                    break;
-                }
-                __nanosleep(64);
-            }
-            __threadfence_system();
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            if (s_fail) {
-                atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, 0x100u);
-            } else {
-                const volatile ExchangeSlot *mine = ex->slots[ex->rank] + (q & 1ull) * world;
-                a = 0.0;
-                b = 0.0;
-                for (int p = 0; p < world; ++p) {
-                    a += mine[p].sum;
-                    b += mine[p].count;
-                }
+        a = __shfl_sync(0xffffffffu, a, 0);
+        b = __shfl_sync(0xffffffffu, b, 0);
+        const unsigned long long seq = exchange_post(ex, tag, a, b);
+        if (defer) {
+            if (threadIdx.x == 0) ex->seq[1] = seq;
+            b = kPendingCount;
+        } else {
+            const unsigned bad = exchange_collect(ex, seq, tag, a, b);
+            if (bad) {
+                if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, bad);
+                a = b = __longlong_as_double(0x7ff8000000000000ll);
             }
         }
     }

@@ -574,7 +574,7 @@ __global__ void __launch_bounds__(kRescaleThreads) rescale_kernel(T *grad, const
 }
 __global__ void count_exchange_kernel(double count, void *workspace, ReduceRecord *out) {
     __shared__ double sh[64];
-    grid_reduce_finish(0.0, threadIdx.x == 0 ? count : 0.0, workspace, out, sh);
+    grid_reduce_finish(0.0, threadIdx.x == 0 ? count : 0.0, workspace, out, sh, kTagCount);
 }
 }  // namespace
 }  // namespace b200

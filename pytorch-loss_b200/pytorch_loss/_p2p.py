@@ -25,7 +25,7 @@ from . import _cabi
 from . import _sharding
 
 MAX_RANKS = 16
-DEFAULT_POLL_LIMIT = 1 << 23          # ~64 ns sleeps: gives up after roughly a second
+DEFAULT_POLL_LIMIT = 1 << 20          # polls of ~1 us each: gives up after roughly a second
 
 _contexts = {}
 _lock = threading.Lock()
@@ -39,7 +39,7 @@ class Exchange:
         self.device, self.world, self.rank = device, world, rank
         self.local_slots = local_slots              # keeps the shared allocation alive
         self.peer_slots = peer_slots                # rank -> device address of that rank's array here
-        self.seq = torch.zeros(1, dtype=torch.int64, device=device)
+        self.seq = torch.zeros(8, dtype=torch.int64, device=device)   # [0] call counter, [1] pending count
         ptrs = [0] * MAX_RANKS
         for p in range(world):
             ptrs[p] = local_slots.data_ptr() if p == rank else int(peer_slots[p])

@@ -102,11 +102,28 @@ _ENTRY_FUSED = {
 }
 
 
-def fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange):
+def count_valid(labels, ignore_index, exchange=None):
+    """Device double: the number of labels != ignore_index.  With an `_p2p.Exchange` the kernel
+    posts this rank's count to the peers and the value stays "pending" until the gradient kernel
+    that divides by it collects the global count (no kernel waits in between)."""
+    dev = labels.device
+    lib = _cabi.load_library()
+    if labels.dtype != torch.int64:
+        raise RuntimeError("labels must be int64, got %s" % labels.dtype)
+    labels = labels.contiguous()
+    ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
+    cnt = _cabi.new_record(dev)
+    with torch.cuda.device(dev):
+        _cabi.check(lib.b200_count_valid(_cabi.ptr(labels), labels.numel(), int(ignore_index), _cabi.ptr(cnt),
+                                         _cabi.ptr(ws), ws.numel(), _cabi.stream_ptr(dev)))
+    return cnt[:4].view(torch.float64)[1:]
+
+
+def fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange, denom=None):
     """The training step in one pass over the logits, or None when this layout has none.
-    Returns (record, gradient) with the gradient already divided by the number of valid pixels
-    for 'mean' (counted on the device by a pass over the labels alone; with an `_p2p.Exchange`
-    both the count and the loss sum are global)."""
+    Returns (record, gradient, logits, labels) with the gradient already divided by the number of
+    valid pixels for 'mean' (`denom`: what `count_valid` returned, or None to count here; with an
+    `_p2p.Exchange` both the count and the loss sum are global)."""
     dev, logits, labels, n, c, m, dt = _prep(logits, labels)
     lib = _cabi.load_library()
     grads = torch.empty_like(logits)
@@ -116,16 +133,12 @@ def fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange):
     rec = _cabi.new_record(dev)
     ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
     st = _cabi.stream_ptr(dev)
-    denom = None
+    if mean and denom is None:
+        denom = count_valid(labels, ignore_index, exchange)
     with torch.cuda.device(dev):
-        if mean:
-            cnt = _cabi.new_record(dev)
-            _cabi.check(lib.b200_count_valid(_cabi.ptr(labels), n * m, int(ignore_index), _cabi.ptr(cnt),
-                                             _cabi.ptr(ws), ws.numel(), st))
-            denom = cnt[:4].view(torch.float64)[1:]
         _cabi.check(getattr(lib, _ENTRY_FUSED[kind])(
             _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
-            None if denom is None else _cabi._vp(denom.data_ptr()), n, c, m, dt, int(ignore_index), float(hyper), st))
+            None if not mean else _cabi._vp(denom.data_ptr()), n, c, m, dt, int(ignore_index), float(hyper), st))
     return rec, grads, logits, labels
 
 
@@ -143,10 +156,17 @@ class ReducedLossFunc(torch.autograd.Function):
         exchange = _p2p.get_exchange(group, logits.device) if logits.is_cuda else None
         ctx.fused = None
         nccl_group = exchange is None and _sharding.group_is_active(group)
+        denom = None
+        if exchange is not None and mean:
+            # Ranks must make the same sequence of exchanges whichever kernels each of them runs
+            # below (a rank may hold an empty or unaligned shard, or need no gradient): with
+            # 'mean' every rank posts its label count first, then its loss sum.
+            _cabi.require_cuda(logits, labels)
+            denom = count_valid(labels, ignore_index, exchange)
         if ctx.needs_input_grad[0] and logits.is_cuda and not nccl_group and \
                 os.environ.get("B200_SOFTMAX_FUSED", "1") != "0":
             # the fused step: loss sum and final gradient from one read of the logits
-            step = fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange)
+            step = fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange, denom)
             if step is not None:
                 rec, grads, logits, labels = step
                 ctx.fused = grads

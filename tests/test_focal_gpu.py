@@ -141,7 +141,8 @@ def test_focal_deterministic_and_workspace_rearmed():
 
 def test_exchange_single_rank_and_bounded_wait():
     """The in-kernel cross-GPU sum on one GPU: a world of one rank gives the local sums, and a
-    context whose peer never writes makes the bounded wait give up (status word, no hang)."""
+    context whose peer never writes makes the bounded wait give up: status word set, record NaN
+    (never a silently local number), no hang."""
     import pytorch_loss  # noqa: F401  (loads the library)
     from pytorch_loss import _cabi, _p2p
     from oracle import losses as O
@@ -153,10 +154,10 @@ def test_exchange_single_rank_and_bounded_wait():
     want, _ = O.focal_loss(logits, labels, 0.25, 2.0, 'sum')
     x, y = logits.to(dev), labels.to(dev)
 
-    def run(exchange):
+    def run(exchange, calls=6):
         rec = _cabi.new_record(dev)
         ws = exchange.workspace()
-        for _ in range(3):              # both slot sets
+        for _ in range(calls):          # every slot set, and the first one again
             _cabi.check(lib.b200_focal_forward(_cabi.ptr(x), _cabi.ptr(y), None, _cabi.ptr(rec), _cabi.ptr(ws),
                                                ws.numel(), x.numel(), _cabi.F32, 2.0, 0.25, _cabi.stream_ptr(dev)))
         return rec, ws
@@ -167,9 +168,116 @@ def test_exchange_single_rank_and_bounded_wait():
     assert abs(float(sums[0]) - float(want)) <= 1e-5 * abs(float(want))
     assert float(sums[1]) == x.numel()
 
-    rec, ws = run(_p2p.local_exchange_for_tests(dev, 2, 0, 200))     # rank 1 never shows up
+    rec, ws = run(_p2p.local_exchange_for_tests(dev, 2, 0, 200), calls=2)     # rank 1 never shows up
     rc = lib.b200_read_status(_cabi.ptr(ws), _cabi.stream_ptr(dev))
     assert rc == 4, "expected B200_ERR_STATUS, got %d" % rc          # the wait ran out and said so
-    sums = rec[:4].view(torch.float64).cpu()
-    assert abs(float(sums[0]) - float(want)) <= 1e-5 * abs(float(want))   # the record holds the local sums
+    assert b"0x100" in lib.b200_last_error()
+    assert bool(torch.isnan(rec[:4].view(torch.float64)).all()) and bool(torch.isnan(rec[4]))
     assert lib.b200_read_status(_cabi.ptr(ws), _cabi.stream_ptr(dev)) == 0    # cleared by the read
+
+
+def test_exchange_foreign_tag_is_reported():
+    """Ranks whose call sequences differ: this rank waits for a loss sum where its peer's slot
+    holds a label count with the same sequence number.  The message is refused (status 0x200,
+    NaN record) instead of being added as if it were a sum."""
+    import pytorch_loss  # noqa: F401
+    from pytorch_loss import _cabi, _p2p
+    dev = torch.device("cuda", 0)
+    lib = _cabi.load_library()
+    ex = _p2p.local_exchange_for_tests(dev, 2, 0, 200)
+    ws = ex.workspace()
+    st = _cabi.stream_ptr(dev)
+    # play rank 1: a context of its own whose "peer 0" array is rank 0's local array, so its
+    # count message lands where rank 0 will look for rank 1's first message
+    other = _p2p.Exchange(dev, 2, 1, ex.stand_ins[0], {0: ex.local_slots.data_ptr()}, 200)
+    cnt = _cabi.new_record(dev)
+    labels = torch.zeros(64, dtype=torch.int64, device=dev)
+    wo = other.workspace()
+    _cabi.check(lib.b200_count_valid(_cabi.ptr(labels), 64, 255, _cabi.ptr(cnt), _cabi.ptr(wo), wo.numel(), st))
+    x = torch.randn(256, device=dev)
+    y = torch.zeros(256, device=dev)
+    rec = _cabi.new_record(dev)
+    _cabi.check(lib.b200_focal_forward(_cabi.ptr(x), _cabi.ptr(y), None, _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
+                                       256, _cabi.F32, 2.0, 0.25, st))
+    assert lib.b200_read_status(_cabi.ptr(ws), st) == 4
+    assert b"0x200" in lib.b200_last_error()
+    assert bool(torch.isnan(rec[4]))
+
+
+def test_deferred_count_is_collected_by_the_gradient_kernel():
+    """Two emulated ranks on one GPU (two exchange contexts over each other's slot arrays, kernels
+    launched one after the other, so nothing waits on a kernel that has not run): both post their
+    label counts (no wait), then rank 0's fused label-smooth step collects the global count while
+    it runs and divides its gradient by it."""
+    import pytorch_loss  # noqa: F401
+    from pytorch_loss import _cabi, _p2p
+    from oracle import losses as O
+    dev = torch.device("cuda", 0)
+    lib = _cabi.load_library()
+    st = _cabi.stream_ptr(dev)
+    nbytes = int(lib.b200_exchange_slot_bytes(2))
+    arrays = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    ranks = [_p2p.Exchange(dev, 2, r, arrays[r], {1 - r: arrays[1 - r].data_ptr()}, 2000) for r in range(2)]
+    g = torch.Generator().manual_seed(91)
+    logits = torch.randn(4, 19, 32, 32, generator=g)
+    labels = torch.randint(0, 19, (4, 32, 32), generator=g)
+    labels[0, :11] = 255                                       # uneven valid counts per rank
+    want_loss, want_grad = O.label_smooth_ce(logits, labels, 0.1, 255, 'mean')
+    xs = [logits[2 * r:2 * r + 2].to(dev) for r in range(2)]
+    ys = [labels[2 * r:2 * r + 2].to(dev) for r in range(2)]
+    cnts = [_cabi.new_record(dev) for _ in range(2)]
+    for r in range(2):
+        ws = ranks[r].workspace()
+        _cabi.check(lib.b200_count_valid(_cabi.ptr(ys[r]), ys[r].numel(), 255, _cabi.ptr(cnts[r]), _cabi.ptr(ws),
+                                         ws.numel(), st))
+    torch.cuda.synchronize()
+    assert float(cnts[0][:4].view(torch.float64)[1]) == -1.0        # posted, not yet collected
+    # rank 1's loss sum is not there when rank 0's step ends, so rank 0's sum exchange times out;
+    # its gradient only needs the counts, which both ranks have posted
+    grad = torch.empty_like(xs[0])
+    rec = _cabi.new_record(dev)
+    ws = ranks[0].workspace()
+    _cabi.check(lib.b200_lsr_forward_backward_reduced(
+        _cabi.ptr(xs[0]), _cabi.ptr(ys[0]), _cabi.ptr(grad), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
+        _cabi._vp(cnts[0].data_ptr() + 8), 2, 19, 32 * 32, _cabi.F32, 255, 0.1, st))
+    torch.cuda.synchronize()
+    assert float(cnts[0][:4].view(torch.float64)[1]) == float((labels != 255).sum())   # the GLOBAL count
+    assert_grad_close(grad, want_grad[:2])
+    assert lib.b200_read_status(_cabi.ptr(ws), st) == 4 and b"0x100" in lib.b200_last_error()
+
+
+def test_focal_predicted_count_correction():
+    """The sharded fused step divides by the global element count of the PREVIOUS call and leaves
+    predicted / actual for the rescale kernel.  One rank (a world of one) whose batch changes size
+    between calls: the loss is right at once, `correction` != 1, the rescaled gradient matches the
+    oracle, and the state holds the new count."""
+    import pytorch_loss as P
+    from pytorch_loss import _cabi, _p2p
+    from oracle import losses as O
+    dev = torch.device("cuda", 0)
+    lib = _cabi.load_library()
+    st = _cabi.stream_ptr(dev)
+    ex = _p2p.local_exchange_for_tests(dev, 1, 0, 1000)
+    ws = ex.workspace()
+    g = torch.Generator().manual_seed(92)
+    state = torch.tensor([3.0 * 5 * 77], dtype=torch.float64, device=dev)     # count of an earlier, larger batch
+    for shape in ((2, 5, 77), (3, 5, 77), (3, 5, 77)):
+        logits = torch.randn(shape, generator=g) * 2
+        labels = (torch.rand(shape, generator=g) < 0.3).float()
+        want_loss, want_grad = O.focal_loss(logits, labels, 0.25, 2.0, 'mean')
+        x, y = logits.to(dev), labels.to(dev)
+        predicted = float(state)
+        grad = torch.empty_like(x)
+        rec = _cabi.new_record(dev)
+        corr = torch.zeros(1, dtype=torch.float32, device=dev)
+        _cabi.check(lib.b200_focal_forward_backward_predicted(
+            _cabi.ptr(x), _cabi.ptr(y), _cabi.ptr(grad), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
+            _cabi.ptr(state), _cabi.ptr(corr), x.numel(), _cabi.F32, 2.0, 0.25, st))
+        one = torch.ones(1, dtype=torch.float32, device=dev)
+        _cabi.check(lib.b200_rescale_gradient(_cabi.ptr(grad), _cabi.ptr(one), _cabi.ptr(corr), x.numel(),
+                                              _cabi.F32, st))
+        assert_loss_close(rec[4], want_loss)
+        assert abs(float(corr) - predicted / x.numel()) <= 1e-6 * predicted / x.numel()
+        assert float(state) == x.numel()
+        assert_grad_close(grad, want_grad, atol=1e-7)
+    _cabi.check(lib.b200_read_status(_cabi.ptr(ws), st))

@@ -9,8 +9,8 @@ inputs and outputs.
 What is checked: on two calls in a row (the second on different data, so stale scratch from
 the first would show), its reduction record equals the one the ordinary entry point
 (b200_focal_forward with a caller-provided workspace) produces, within the tolerance the
-other focal tests use (1e-5 relative on the loss); the count is exact; oversize inputs are
-refused with a message.  This file sorts last on purpose: a run that stops at the first
+other focal tests use (1e-5 relative on the loss), and both equal the CPU oracle's sum within
+that same tolerance; the count is exact; oversize inputs are refused with a message.  This file sorts last on purpose: a run that stops at the first
 failure has then already executed every other test.
 """
 import ctypes
@@ -44,12 +44,16 @@ def _records(lib, logits, labels, gamma, alpha):
 
 def test_no_alloc_entry_matches_workspace_entry_on_two_calls():
     from pytorch_loss import _cabi
+    from oracle import losses as O
     lib = _cabi.load_library()
     g = torch.Generator().manual_seed(2024)
     for call, shape in enumerate([(4, 3, 257, 129), (2, 1, 1024, 1024)]):
-        logits = (torch.randn(shape, generator=g) * 3 ** 0.5).cuda()
-        labels = (torch.rand(shape, generator=g) < 0.1).float().cuda()
+        logits = torch.randn(shape, generator=g) * 3 ** 0.5
+        labels = (torch.rand(shape, generator=g) < 0.1).float()
+        want_sum = float(O.focal_loss(logits, labels, 0.25, 2.0, 'sum', dtype=torch.float64)[0])
+        logits, labels = logits.cuda(), labels.cuda()
         new, ref = _records(lib, logits, labels, 2.0, 0.25)
+        assert abs(float(new[:4].view(torch.float64)[0]) - want_sum) <= 1e-5 * abs(want_sum), "call %d: oracle" % call
         new_sc, ref_sc = new[:4].view(torch.float64), ref[:4].view(torch.float64)
         assert float(new_sc[1]) == float(ref_sc[1]) == logits.numel(), "call %d: count" % call
         assert abs(float(new_sc[0]) - float(ref_sc[0])) <= 1e-5 * abs(float(ref_sc[0])), "call %d: sum" % call
