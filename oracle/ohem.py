@@ -1,10 +1,12 @@
 """CPU oracle of the OHEM relabelling step — TEST INFRASTRUCTURE, NOT A PRODUCT PATH.
 
-Parity status: UNPINNED.  The reference implements `score_ohem_label` in CUDA only
+Parity status: PINNED.  The reference implements `score_ohem_label` in CUDA only
 (csrc/ohem_label_kernel.cu; its wrapper raises "this ohem method only supports gpu mode",
-:270-272), ships no CPU version, no golden vectors and no test for it, and cannot run in a
-container without a GPU.  This file restates that CUDA algorithm step by step; the loss classes
-built on it use the pinned functions of oracle/losses.py.
+:270-272) and ships no CPU version, no golden vectors and no test for it.  This file restates
+that CUDA algorithm step by step; tests/golden/ohem.npz holds the labels the reference's own
+extension (built unmodified for sm_100a) returned on a B200 for seeded inputs
+(tests/golden/make_ohem_golden.py), and tests/test_oracle_golden.py checks this file against
+them.  The loss classes built on it use the pinned functions of oracle/losses.py.
 
 Only tests/, the smoke check and bench.py's CPU legs may import this module.
 """

@@ -239,10 +239,8 @@ __device__ __forceinline__ ExchangeCtx *exchange_of(void *workspace) {
 // 0 then collects the ranks' counts and stores the sum; every other thread that needs the value
 // polls the double (bounded).  Warp 0 of block 0 must call this with all 32 lanes; it is among the
 // first blocks to run, so the pollers cannot starve it.  NaN when the wait ran out.
-__device__ __forceinline__ double resolve_count(const double *denom, void *workspace) {
+static __device__ __noinline__ double resolve_count_pending(const double *denom, void *workspace) {
     const volatile double *vd = denom;
-    double d = *vd;
-    if (d >= 0.0 || d != d) return d;                    // the usual case: already there (or NaN)
     ExchangeCtx *ex = exchange_of(workspace);
     if (ex && blockIdx.x == 0 && threadIdx.x < 32) {
         double a, b;
@@ -259,11 +257,16 @@ __device__ __forceinline__ double resolve_count(const double *denom, void *works
     }
     const unsigned limit = ex ? ex->poll_limit : (1u << 20);
     for (unsigned polls = 0; polls <= limit; ++polls) {
-        d = *vd;
+        const double d = *vd;
         if (d >= 0.0 || d != d) return d;
         __nanosleep(64);
     }
     return __longlong_as_double(0x7ff8000000000000ll);
+}
+__device__ __forceinline__ double resolve_count(const double *denom, void *workspace) {
+    const double d = *static_cast<const volatile double *>(denom);
+    if (d >= 0.0 || d != d) return d;                    // the usual case: already there (or NaN)
+    return resolve_count_pending(denom, workspace);      // kept out of line: the callers' loops need the registers
 }
 
 // Final step of a reducing forward kernel.  Every block calls it once with its

@@ -107,3 +107,19 @@ def test_ohem_losses_match_oracle(cls):
     crit = getattr(P, cls)(score_thresh=0.2)
     loss2, _ = run_module(crit, logits.cuda(), labels.cuda())
     assert_loss_close(loss2, want_loss, rtol=2e-5)
+
+
+def test_golden_from_reference_cuda(golden_dir):
+    """The library against the labels the reference's own CUDA extension returned on the same
+    inputs (tests/golden/ohem.npz): exact."""
+    import os
+    import numpy as np
+    import ohem_cpp
+    z = np.load(os.path.join(golden_dir, "ohem.npz"))
+    for i in range(int(z["n_cases"])):
+        logits = torch.from_numpy(z[f"c{i}_logits"]).float()
+        labels = torch.from_numpy(z[f"c{i}_labels"])
+        ign, thresh, n_min = z[f"c{i}_args"]
+        want = torch.from_numpy(z[f"c{i}_new_labels"])
+        got = ohem_cpp.score_ohem_label(logits.cuda(), labels.cuda(), int(ign), float(thresh), int(n_min))
+        assert torch.equal(got.cpu(), want), "case %d: %d labels differ" % (i, int((got.cpu() != want).sum()))

@@ -107,3 +107,18 @@ def test_taylor_oracle(golden_dir):
         loss, grad = OT.taylor_cross_entropy(logits, labels, order, ign, str(z[f"ce{i}_reduction"]))
         assert torch.allclose(loss, torch.from_numpy(z[f"ce{i}_loss"]), atol=1e-6, rtol=1e-5), i
         assert torch.allclose(grad, torch.from_numpy(z[f"ce{i}_grad"]), atol=1e-6, rtol=1e-5), i
+
+
+def test_ohem_oracle_matches_reference_cuda_output(golden_dir):
+    """oracle/ohem.py against the labels the reference's own CUDA extension returned
+    (tests/golden/ohem.npz, written by make_ohem_golden.py on a B200): exact, case by case."""
+    from oracle import ohem as OH
+    z = np.load(os.path.join(golden_dir, "ohem.npz"))
+    assert int(z["n_cases"]) >= 8
+    for i in range(int(z["n_cases"])):
+        logits = torch.from_numpy(z[f"c{i}_logits"]).float()
+        labels = torch.from_numpy(z[f"c{i}_labels"])
+        ign, thresh, n_min = z[f"c{i}_args"]
+        want = torch.from_numpy(z[f"c{i}_new_labels"])
+        got, _ = OH.score_ohem_label(logits, labels, int(ign), float(thresh), int(n_min))
+        assert torch.equal(got, want), "case %d: %d labels differ" % (i, int((got != want).sum()))
