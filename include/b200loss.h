@@ -105,12 +105,8 @@ int b200_exchange_count(double count, void *out, void *workspace, size_t workspa
  * csrc/large_margin_kernel.cu:354-481, always read the logits twice per step):
  *   b200_softmax_fused_step_path: 1 when the layout has a fused step (channel columns of a
  *       pixel tile fit in shared memory, 16-byte aligned rows), else 0.
- *   b200_count_valid: out->count = number of labels != ignore_index: the 'mean' divisor, needed
- *       on the device before gradients are written.  With ranks attached (cross-GPU sum below)
- *       the kernel only POSTS its count to the peers and leaves out->count = -1; the next
- *       b200_{lsr,lmargin}_forward_backward_reduced / *_backward call on the same workspace that
- *       gets `denom` = &out->count collects the ranks' counts while its first tiles load, stores
- *       the sum there and divides by it -- so no kernel sits waiting for a peer between the two.
+ *   b200_count_valid: out->count = number of labels != ignore_index (summed over attached
+ *       ranks): the 'mean' divisor, needed on the device before gradients are written.
  *   b200_{lsr,lmargin}_forward_backward_reduced: one pass over the logits; out = reduction
  *       record of the loss, grad_logits = dloss/dlogits / *denom (denom: optional device double).
  *       B200_ERR_UNSUPPORTED when b200_softmax_fused_step_path says 0.

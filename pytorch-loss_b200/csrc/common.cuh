@@ -40,11 +40,10 @@ constexpr size_t kReduceWorkspaceBytes = kPartialsOffset + size_t(kMaxPartials) 
 //   post    lane p of one warp stores this rank's message into slot [seq & 3][rank] of rank p
 //   collect lane p polls slot [seq & 3][p] of this rank's own array -- bounded -- and lane 0
 //           adds the pairs in rank order, so every rank gets the same bits
-// The sequence number is a device-side counter (graph replays keep working).  Four slot sets:
-// a message may still be unread while the next one of the same rank is posted (the count of
-// valid labels is posted by one kernel and collected by the next), and a rank cannot post
-// message k+4 before every peer has collected message k, because it collects k+2 or k+3 first
-// and those need the peers' posts, which follow their own collection of k.
+// The sequence number is a device-side counter (graph replays keep working).  Four slot sets
+// (two would do): a rank cannot post message k+2 before every peer has collected message k,
+// because it collects k+1 first and that needs the peers' posts, which follow their own
+// collection of k.
 // The tag names what the message carries (a count, a loss sum).  Ranks whose call sequences
 // differ (one took a path with one exchange, another a path with two) meet a foreign tag or
 // never see the flag: both give NaN sums, status bit 0x200 / 0x100, and never a silently
@@ -61,12 +60,10 @@ struct ExchangeCtx {        // lives in device memory; filled by the host once (
     int rank;
     unsigned poll_limit;    // polls of one slot before a wait gives up (status bit 0x100)
     unsigned reserved;
-    unsigned long long *seq;                    // [0]: this rank's call counter; [1]: sequence
-                                                // number of a count that is posted, not collected
+    unsigned long long *seq;                    // this rank's call counter (eight words reserved)
     ExchangeSlot *slots[kMaxExchangeRanks];     // slots[p]: rank p's array [kExchangeSets][world]
 };
 constexpr size_t kExchangeCtxOffset = 8;
-constexpr double kPendingCount = -1.0;          // record.count while the global count is in flight
 
 struct ReduceRecord {       // the 32-byte "out" record of the C ABI
     double sum;
@@ -234,52 +231,16 @@ __device__ __forceinline__ ExchangeCtx *exchange_of(void *workspace) {
                      : nullptr;
 }
 
-// The divisor of a 'mean' as the gradient kernels read it: a device double that may still be
-// in flight between the GPUs (kPendingCount, left by grid_reduce_finish<defer>).  Warp 0 of block
-// 0 then collects the ranks' counts and stores the sum; every other thread that needs the value
-// polls the double (bounded).  Warp 0 of block 0 must call this with all 32 lanes; it is among the
-// first blocks to run, so the pollers cannot starve it.  NaN when the wait ran out.
-static __device__ __noinline__ double resolve_count_pending(const double *denom, void *workspace) {
-    const volatile double *vd = denom;
-    ExchangeCtx *ex = exchange_of(workspace);
-    if (ex && blockIdx.x == 0 && threadIdx.x < 32) {
-        double a, b;
-        const unsigned bad = exchange_collect(ex, ex->seq[1], kTagCount, a, b);
-        if (threadIdx.x == 0) {
-            if (bad) {
-                atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, bad);
-                b = __longlong_as_double(0x7ff8000000000000ll);
-            }
-            *const_cast<volatile double *>(vd) = b;
-            __threadfence();
-        }
-        return __shfl_sync(0xffffffffu, b, 0);
-    }
-    const unsigned limit = ex ? ex->poll_limit : (1u << 20);
-    for (unsigned polls = 0; polls <= limit; ++polls) {
-        const double d = *vd;
-        if (d >= 0.0 || d != d) return d;
-        __nanosleep(64);
-    }
-    return __longlong_as_double(0x7ff8000000000000ll);
-}
-__device__ __forceinline__ double resolve_count(const double *denom, void *workspace) {
-    const double d = *static_cast<const volatile double *>(denom);
-    if (d >= 0.0 || d != d) return d;                    // the usual case: already there (or NaN)
-    return resolve_count_pending(denom, workspace);      // kept out of line: the callers' loops need the registers
-}
-
 // Final step of a reducing forward kernel.  Every block calls it once with its
 // partial (sum, count).  The block that takes the last ticket adds all partials
 // in a fixed order, writes the record and re-arms the ticket: deterministic,
 // no spinning, no second launch.  blockDim.x must be a multiple of 32, <= 1024.
 // With an exchange attached to the workspace the pair is first added over the ranks (message
-// tag `tag`).  `defer`: only post this rank's pair and leave record.count = kPendingCount; the
-// kernel that needs the global count collects it (resolve_count).
+// tag `tag`).
 // Returns true in exactly one thread of the grid: the one that has just written the record.
 __device__ __forceinline__ bool grid_reduce_finish(double sum, double cnt, void *workspace,
                                                    ReduceRecord *out, double *sh,
-                                                   unsigned tag = kTagSum, bool defer = false) {
+                                                   unsigned tag = kTagSum) {
     block_sum2(sum, cnt, sh);
     unsigned *ticket = reinterpret_cast<unsigned *>(workspace);
     double2 *partials =
@@ -307,15 +268,10 @@ __device__ __forceinline__ bool grid_reduce_finish(double sum, double cnt, void 
         a = __shfl_sync(0xffffffffu, a, 0);
         b = __shfl_sync(0xffffffffu, b, 0);
         const unsigned long long seq = exchange_post(ex, tag, a, b);
-        if (defer) {
-            if (threadIdx.x == 0) ex->seq[1] = seq;
-            b = kPendingCount;
-        } else {
-            const unsigned bad = exchange_collect(ex, seq, tag, a, b);
-            if (bad) {
-                if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, bad);
-                a = b = __longlong_as_double(0x7ff8000000000000ll);
-            }
+        const unsigned bad = exchange_collect(ex, seq, tag, a, b);
+        if (bad) {
+            if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, bad);
+            a = b = __longlong_as_double(0x7ff8000000000000ll);
         }
     }
     if (threadIdx.x == 0) {

@@ -21,8 +21,9 @@
 //            for the rest.  A segment that would keep more than 3/4 is sorted from the full
 //            array instead (`direct`).  What is kept depends on the data: ~7% for random
 //            logits over 19 classes, everything when some foreground pixel has error 0.
-//   sort     segmented LSD radix sort of the kept (key, pixel index) pairs on key bits 1..30,
-//            kBits per pass.  Each pass: per-tile digit histogram -> per-segment scan ->
+//   sort     segmented LSD radix sort of the kept (key, pixel index) pairs, kBits per pass: all 30
+//            key bits in three stable passes, or -- segments with many foreground elements,
+//            see "Key bits" below -- the top 20 bits in two.  Each pass: per-tile digit histogram -> per-segment scan ->
 //            stable scatter.  The scatter ranks with kBits ballots per round + per-warp
 //            counters, reorders the tile in shared memory and writes each digit's run
 //            contiguously.  The kept counts exist on the device only: the kernels run over a
@@ -33,6 +34,19 @@
 //            with I = remaining fg, U = union before the step; accumulates err*dJ and scatters
 //            dJ to pixel order (the `jacc` output).
 //   backward one tile kernel: softmax recomputed, g = p*(gp - sum p*gp), zero at ignored pixels.
+//
+// Key bits.  Swapping two neighbours of the sorted order moves the loss by (their error
+// difference) x (their dJ difference) and their dJ by the step between adjacent ranks, which is
+// at most 1/U^2 with U >= n_pos (the segment's foreground count).  A segment with n_pos >=
+// kFastMinFg that sorts at least kFastMinKept elements is therefore sorted on the top 20 of its 30
+// error bits only ("fast": two passes instead of three): elements whose errors agree to 2^-13
+// relative may come out in either order, which moves a pixel's dJ by at most 1/4096^2 = 6e-8
+// (measured on 1 Mpixel segments with 55 000 foreground pixels: 1.7e-9 absolute, 8e-5 of the
+// largest dJ of the class, loss 4e-13 relative) -- far inside the 1e-5 gradient tolerance.  The
+// reference's own order among such near-ties is no better defined: its errors carry the
+// rounding of its own softmax (1e-7 relative) and thrust's sort is not stable.  Fast segments
+// are also ranked with one shared-memory atomic per element (see rank_round); every other
+// segment takes three stable passes over all 30 bits, exact array order among equal keys.
 #include "common.cuh"
 #include "pipeline.cuh"
 
@@ -45,7 +59,9 @@ namespace {
 
 constexpr int kBits = 10;
 constexpr int kBins = 1 << kBits;
-constexpr int kPasses = 3;                 // key bits 1..30
+constexpr int kPasses = 3;                 // key bits 1..30; "fast" segments skip the first pass (see Key bits)
+constexpr uint32_t kFastMinFg = 4096;      // foreground elements a segment needs to sort on 20 bits
+constexpr uint32_t kFastMinKept = 32u * kBins;   // ... and elements it sorts
 constexpr int kSortThreads = 256;
 constexpr int kSortItems = 32;
 constexpr int kSortTile = kSortThreads * kSortItems;   // 8192 pairs per tile
@@ -84,8 +100,9 @@ struct Workspace {
     uint32_t *maxfg;      // [S]  largest foreground key seen (0: none)
     uint32_t *minkey;     // [S]  smallest key among the sampled tiles (0xFFFFFFFF: none)
     uint32_t *kept;       // [S][T] kept elements per tile -> exclusive offsets
+    uint32_t *fgkept;     // [S][T] foreground elements per tile
     uint32_t *Lp;         // [S]  elements of the segment that go through the sort
-    uint32_t *direct;     // [S]  1: the segment is sorted from the full key array (not compacted)
+    uint32_t *direct;     // [S]  segment flags: kSegFlagDirect (sorted from the full key array, not compacted), kSegFlagFast
     uint2 *tilemap;       // [S*T] (segment, tile) of every sort tile in use, segment-major
     uint32_t *n_tiles;    // 1 word: sort tiles in use
     size_t bytes;
@@ -107,6 +124,7 @@ Workspace carve(void *base, const LovaszGeom &g) {
     w.maxfg = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
     w.minkey = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
     w.kept = reinterpret_cast<uint32_t *>(take(size_t(g.S) * g.T * 4));
+    w.fgkept = reinterpret_cast<uint32_t *>(take(size_t(g.S) * g.T * 4));
     w.Lp = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
     w.direct = reinterpret_cast<uint32_t *>(take(size_t(g.S) * 4));
     w.tilemap = reinterpret_cast<uint2 *>(take(size_t(g.S) * g.T * 8));
@@ -605,21 +623,33 @@ __device__ __forceinline__ uint32_t digit_of(uint32_t key, int shift) {
 __device__ __forceinline__ bool key_is_fg(uint32_t key) { return (key & 1u) && key != kKeyIgnored; }
 
 // One entry of the list of sort tiles in use: everything a block needs to start on the tile,
-// in one 8-byte load.   x = segment,   y = tile | (elements - 1) << 18 | direct << 31
+// in one 8-byte load.   x = segment | direct << 30 | fast << 31,
+//                       y = tile | (elements - 1) << 18 | swapped << 31
+// The launches pass the two buffer pairs in the roles they have for a compacted segment that
+// takes all three passes (B -> A -> B, ranked from B).  A segment that was not compacted
+// (`direct`) starts in A, and a `fast` segment skips the first pass: either shifts the segment's
+// data to the other pair in every pass it takes, both together cancel: swapped = direct ^ fast.
 struct TileRef {
     int64_t seg, tile;
     int n;
-    bool direct;       // the segment was not compacted: its buffers are used in swapped roles
+    bool direct;       // the segment was not compacted: its first pass makes up the values (positions)
+    bool fast;         // two passes on the top 20 key bits, atomic ranking
+    bool swapped;      // the segment uses the two buffer pairs in swapped roles
 };
-__device__ __forceinline__ uint2 encode_tile(uint32_t seg, uint32_t tile, uint32_t n, bool direct) {
-    return make_uint2(seg, tile | ((n - 1u) << 18) | (direct ? 0x80000000u : 0u));
+constexpr uint32_t kSegFlagDirect = 1u, kSegFlagFast = 2u;
+__device__ __forceinline__ uint2 encode_tile(uint32_t seg, uint32_t tile, uint32_t n, uint32_t flags) {
+    const bool direct = flags & kSegFlagDirect, fast = flags & kSegFlagFast;
+    return make_uint2(seg | (direct ? 0x40000000u : 0u) | (fast ? 0x80000000u : 0u),
+                      tile | ((n - 1u) << 18) | (direct != fast ? 0x80000000u : 0u));
 }
 __device__ __forceinline__ TileRef decode_tile(uint2 e) {
     TileRef t;
-    t.seg = e.x;
+    t.seg = e.x & 0x3FFFFFFFu;
+    t.direct = (e.x >> 30) & 1u;
+    t.fast = (e.x >> 31) != 0u;
     t.tile = e.y & 0x3FFFFu;
     t.n = int((e.y >> 18) & 0x1FFFu) + 1;
-    t.direct = (e.y >> 31) != 0u;
+    t.swapped = (e.y >> 31) != 0u;
     return t;
 }
 // The block's next tile: thread 0 draws a ticket while the tile's key loads are in flight, and
@@ -655,16 +685,17 @@ __global__ void __launch_bounds__(kSortThreads)
 sort_hist_kernel(const uint32_t *__restrict__ keys, uint32_t *__restrict__ hist,
                  uint32_t *__restrict__ fghist, const uint2 *__restrict__ tilemap,
                  const uint32_t *__restrict__ n_tiles, const uint32_t *__restrict__ keys_alt, int64_t L, int64_t T,
-                 int shift) {
+                 int shift, int first_pass) {
     __shared__ uint32_t sh[kBins];
     __shared__ uint32_t shfg[LAST ? kBins : 1];
     const uint32_t total = __ldg(n_tiles);
   for (uint32_t w = blockIdx.x; w < total; w += gridDim.x) {
     const TileRef tr = decode_tile(__ldg(tilemap + w));
+    if (first_pass && tr.fast) continue;               // fast segments have no first pass
     const int64_t seg = tr.seg, tile = tr.tile;
     const int64_t t0 = tile * kSortTile;
     const int n = tr.n;
-    const uint32_t *src = (tr.direct ? keys_alt : keys) + seg * L + t0;
+    const uint32_t *src = (tr.swapped ? keys_alt : keys) + seg * L + t0;
     for (int b = threadIdx.x; b < kBins; b += kSortThreads) {
         sh[b] = 0;
         if (LAST) shfg[b] = 0;
@@ -730,10 +761,12 @@ __device__ __forceinline__ uint32_t block_excl_scan_1024(uint32_t v, uint32_t *w
 template <bool LAST>
 __global__ void __launch_bounds__(kBins)
 sort_scan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fghist,
-                 uint32_t *__restrict__ n_pos, const uint32_t *__restrict__ Lp, int64_t T) {
+                 uint32_t *__restrict__ n_pos, const uint32_t *__restrict__ Lp,
+                 const uint32_t *__restrict__ seg_flags, int64_t T, int first_pass) {
     __shared__ uint32_t warp_tot[32];
     __shared__ uint32_t grand;
     const int64_t seg = blockIdx.x;
+    if (first_pass && (__ldg(seg_flags + seg) & kSegFlagFast)) return;
     const int b = threadIdx.x;
     const int64_t Tk = (int64_t(__ldg(Lp + seg)) + kSortTile - 1) / kSortTile;   // tiles in use
 #pragma unroll
@@ -758,55 +791,78 @@ sort_scan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fghist,
 // sort tile, a scan per segment, and a stable compaction that also writes the dropped
 // elements' dJ (zero).  The sort then runs on the kept elements only (Lp per segment).
 
-// kept[seg][tile] = number of elements of the tile with (key >> 1) < limit.
+// kept[seg][tile] = number of elements of the tile with (key >> 1) < limit;
+// fgkept[seg][tile] = number of foreground elements of the tile.
 __global__ void __launch_bounds__(kSortThreads)
 prune_count_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restrict__ maxfg,
-                   const uint32_t *__restrict__ minkey, uint32_t *__restrict__ kept, int64_t L, int64_t T,
-                   int prune) {
-    __shared__ uint32_t wsum[kSortWarps];
+                   const uint32_t *__restrict__ minkey, uint32_t *__restrict__ kept, uint32_t *__restrict__ fgkept,
+                   int64_t L, int64_t T, int prune) {
+    __shared__ uint32_t wsum[kSortWarps], wfg[kSortWarps];
     const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
     const uint32_t limit = prune_limit(maxfg, minkey, seg, prune);
     const int64_t t0 = tile * kSortTile;
     const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
     const uint32_t *src = keys + seg * L + t0;
-    uint32_t c = 0;
+    uint32_t c = 0, f = 0;
 #pragma unroll
     for (int r = 0; r < kSortItems; ++r) {
         const int idx = r * kSortThreads + threadIdx.x;
-        if (idx < n) c += (__ldg(src + idx) >> 1) < limit ? 1u : 0u;
+        if (idx < n) {
+            const uint32_t k = __ldg(src + idx);
+            c += (k >> 1) < limit ? 1u : 0u;
+            f += key_is_fg(k) ? 1u : 0u;
+        }
     }
     c = __reduce_add_sync(0xffffffffu, c);
-    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = c;
+    f = __reduce_add_sync(0xffffffffu, f);
+    if ((threadIdx.x & 31) == 0) {
+        wsum[threadIdx.x >> 5] = c;
+        wfg[threadIdx.x >> 5] = f;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
-        uint32_t tot = 0;
-        for (int w = 0; w < kSortWarps; ++w) tot += wsum[w];
+        uint32_t tot = 0, fg = 0;
+        for (int w = 0; w < kSortWarps; ++w) {
+            tot += wsum[w];
+            fg += wfg[w];
+        }
         kept[seg * T + tile] = tot;
+        fgkept[seg * T + tile] = fg;
     }
 }
 
 // kept[seg][*] -> exclusive offsets, Lp[seg] = total.  One block of kBins threads per segment.
 // A segment that keeps more than 3/4 of its elements is not worth compacting: it is flagged
-// `direct`, Lp = L, and the first sort pass reads it from the full array (the ignored pixels'
-// keys sort last and the Jaccard kernel passes over them).
+// `direct`, Lp = L, and its first sort pass reads it from the full array (the ignored pixels'
+// keys sort last and the Jaccard kernel passes over them).  A segment with enough foreground
+// and enough sorted elements is flagged `fast` (see "Key bits").
 __global__ void __launch_bounds__(kBins)
-prune_scan_kernel(uint32_t *__restrict__ kept, uint32_t *__restrict__ Lp, uint32_t *__restrict__ direct,
-                  int64_t L, int64_t T) {
+prune_scan_kernel(uint32_t *__restrict__ kept, const uint32_t *__restrict__ fgkept, uint32_t *__restrict__ Lp,
+                  uint32_t *__restrict__ seg_flags, int64_t L, int64_t T, int allow_fast) {
     __shared__ uint32_t warp_tot[32];
     __shared__ uint32_t grand;
+    __shared__ uint32_t fgw[32];
     const int64_t seg = blockIdx.x;
-    uint32_t carry = 0;
+    uint32_t carry = 0, fg = 0;
     for (int64_t base = 0; base < T; base += kBins) {
         const int64_t t = base + threadIdx.x;
         const uint32_t v = t < T ? kept[seg * T + t] : 0u;
+        fg += t < T ? fgkept[seg * T + t] : 0u;
         const uint32_t ex = block_excl_scan_1024(v, warp_tot, &grand);
         if (t < T) kept[seg * T + t] = carry + ex;
         carry += grand;
     }
+    fg = __reduce_add_sync(0xffffffffu, fg);
+    if ((threadIdx.x & 31) == 0) fgw[threadIdx.x >> 5] = fg;
+    __syncthreads();
     if (threadIdx.x == 0) {
+        uint32_t n_fg = 0;
+        for (int w = 0; w < kBins / 32; ++w) n_fg += fgw[w];
         const bool d = int64_t(carry) * 4 > L * 3;
-        Lp[seg] = d ? uint32_t(L) : carry;
-        direct[seg] = d ? 1u : 0u;
+        const uint32_t sorted = d ? uint32_t(L) : carry;
+        const bool fast = allow_fast && n_fg >= kFastMinFg && sorted >= kFastMinKept;
+        Lp[seg] = sorted;
+        seg_flags[seg] = (d ? kSegFlagDirect : 0u) | (fast ? kSegFlagFast : 0u);
     }
 }
 
@@ -819,7 +875,7 @@ prune_compact_kernel(const uint32_t *__restrict__ keys, const uint32_t *__restri
                      uint32_t *__restrict__ vals_out, float *__restrict__ jacc, int64_t L, int64_t T, int prune) {
     __shared__ uint32_t wtot[kSortWarps];
     const int64_t seg = blockIdx.x / T, tile = blockIdx.x % T;
-    if (__ldg(direct + seg)) return;
+    if (__ldg(direct + seg) & kSegFlagDirect) return;
     const uint32_t limit = prune_limit(maxfg, minkey, seg, prune);
     const int64_t t0 = tile * kSortTile;
     const int n = int(L - t0 < kSortTile ? L - t0 : kSortTile);
@@ -879,10 +935,10 @@ tile_map_kernel(const uint32_t *__restrict__ Lp, const uint32_t *__restrict__ di
     for (int w = 0; w < 8; ++w) first += wsum[w];
     const uint32_t Lk = __ldg(Lp + seg);
     const uint32_t mine = (Lk + kSortTile - 1) / kSortTile;
-    const bool d = __ldg(direct + seg) != 0u;
+    const uint32_t flags = __ldg(direct + seg);
     for (uint32_t t = threadIdx.x; t < mine; t += 256) {
         const uint32_t left = Lk - t * kSortTile;
-        tilemap[first + t] = encode_tile(uint32_t(seg), t, left < kSortTile ? left : uint32_t(kSortTile), d);
+        tilemap[first + t] = encode_tile(uint32_t(seg), t, left < kSortTile ? left : uint32_t(kSortTile), flags);
     }
     if (seg == S - 1 && threadIdx.x == 0) *n_tiles = first + mine;
 }
@@ -905,14 +961,24 @@ constexpr size_t kScatCntBytes = size_t(kScatWarps) * kBins * 2;
 constexpr size_t kScatterSmem = kTileWordsBytes /*bufv*/ + kTileWordsBytes /*bufk*/ + kScatCntBytes + 2 * kBins * 4;
 constexpr size_t kJaccardSmem = kMatchBytes + 2 * kCntBytes + 2 * kBins * 4 + kTileWordsBytes;
 
-// One ranking round of a warp: which lanes hold my digit, my stable rank among them, and the
-// warp counter update.  The lane mask comes from kBits ballots (one per digit bit, all
-// independent of each other), so a round is a fixed ~50 issue slots with a single
-// shared-memory round trip (the leader's counter update) -- atomics or match.any on the digit
-// cost as much per round as there are equal / distinct digits and left the kernel waiting.
-// Returns the rank of this lane's element inside (warp, digit) counting all earlier rounds.
-__device__ __forceinline__ uint32_t rank_round(uint32_t d, uint16_t *wcnt, int lane,
-                                               uint32_t lt, uint32_t &peers_out) {
+// One ranking round of a warp, two ways.
+//
+// rank_round_exact: which lanes hold my digit (lane masks from kBits ballots, all independent of
+// each other), my rank among them in lane order, and the warp counter update by the lowest such
+// lane: ranks follow array order exactly.  ~45 issue slots per round.
+//
+// rank_round_fast ("fast" segments only): one shared-memory atomic on the warp's own packed
+// counter (two 16-bit counters per word; a warp sees at most 1024 elements per tile, so a half
+// never carries into its neighbour).  Rounds follow each other in program order and every warp
+// owns its counters, so ranks respect (warp, round) order = array order; WITHIN a round, lanes
+// that hold the same digit are ranked in the order the hardware serialises the atomic.  That
+// order only separates elements that are 32 or fewer positions apart in the input.  In a fast
+// segment's first pass their final order is decided by the second digit unless both digits agree
+// (a tie of the 20-bit sort key); in its last pass the input is already sorted by the first
+// digit and holds at least 32 elements per value of it, so neighbours with the same last digit
+// differ by at most one step of the first.  Either way the two errors agree to 2^-13 relative:
+// the resolution a fast segment is sorted to (see "Key bits").  ~6 issue slots per round.
+__device__ __forceinline__ uint32_t rank_round_exact(uint32_t d, uint16_t *wcnt, int lane, uint32_t lt) {
     uint32_t peers = 0xffffffffu;
 #pragma unroll
     for (int b = 0; b < kBits; ++b) {
@@ -928,8 +994,13 @@ __device__ __forceinline__ uint32_t rank_round(uint32_t d, uint16_t *wcnt, int l
     }
     __syncwarp();
     old = __shfl_sync(0xffffffffu, old, leader);
-    peers_out = peers;
     return old + __popc(peers & lt);
+}
+__device__ __forceinline__ uint32_t rank_round_fast(uint32_t d, uint16_t *wcnt) {
+    uint32_t *w32 = reinterpret_cast<uint32_t *>(wcnt);
+    const uint32_t sh = (d & 1u) << 4;
+    const uint32_t old = atomicAdd(&w32[d >> 1], 1u << sh);
+    return (old >> sh) & 0xffffu;
 }
 
 // Stable scatter of one tile (passes that are not the last).  kin / vin point at the tile,
@@ -939,7 +1010,7 @@ __device__ __forceinline__ uint32_t rank_round(uint32_t d, uint16_t *wcnt, int l
 // The n elements are dealt to the warps in contiguous chunks of R rounds of 32
 // (R = ceil(n / 512), at most kScatItems), so (warp, round, lane) order equals array order
 // and a partly filled tile skips the rounds it does not need.
-template <bool FULL>      // FULL: a tile of exactly kSortTile elements -- straight-line code, no round tests
+template <bool FULL, bool FAST>   // FULL: a tile of exactly kSortTile elements -- straight-line code, no round tests
 __device__ __forceinline__ void scatter_tile(const uint32_t *__restrict__ kin, const uint32_t *__restrict__ vin,
                                              uint32_t *__restrict__ kout, uint32_t *__restrict__ vout,
                                              const uint32_t *__restrict__ off, int n, int shift, uint32_t pos0,
@@ -973,10 +1044,18 @@ __device__ __forceinline__ void scatter_tile(const uint32_t *__restrict__ kin, c
 #pragma unroll
     for (int r = 0; r < kScatItems; r += 2) {
         if (r < R) {
-            uint32_t peers;
-            const uint32_t r0 = rank_round(digit_of(key[r], shift), wcnt, lane, lt, peers);
-            uint32_t r1 = 0;
-            if (r + 1 < R) r1 = rank_round(digit_of(key[r + 1], shift), wcnt, lane, lt, peers);
+            uint32_t r0 = 0, r1 = 0;
+            if (FAST) {
+                // (padding lanes of a partly filled round take no rank: the hardware might serialise
+                // them ahead of real elements of the same digit)
+                if (FULL || wbase + r * 32 + lane < cnt) r0 = rank_round_fast(digit_of(key[r], shift), wcnt);
+                if (r + 1 < R && (FULL || wbase + (r + 1) * 32 + lane < cnt))
+                    r1 = rank_round_fast(digit_of(key[r + 1], shift), wcnt);
+            } else {
+                // (padding lanes hold all-ones keys in the highest positions: ranked last)
+                r0 = rank_round_exact(digit_of(key[r], shift), wcnt, lane, lt);
+                if (r + 1 < R) r1 = rank_round_exact(digit_of(key[r + 1], shift), wcnt, lane, lt);
+            }
             rank2[r / 2] = r0 | (r1 << 16);
         }
     }
@@ -1032,7 +1111,7 @@ __device__ __forceinline__ void scatter_tile(const uint32_t *__restrict__ kin, c
     // local sorted position (kept in place of the rank); keys into the reorder buffer
 #pragma unroll
     for (int r = 0; r < kScatItems; ++r) {
-        if (r < R) {
+        if (r < R && (FULL || wbase + r * 32 + lane < cnt)) {      // padding lanes hold no element
             const uint32_t d = digit_of(key[r], shift);
             const uint32_t rk = (r & 1) ? (rank2[r / 2] >> 16) : (rank2[r / 2] & 0xffffu);
             const uint32_t lp = binstart[d] + wcnt[d] + rk;
@@ -1051,7 +1130,7 @@ __device__ __forceinline__ void scatter_tile(const uint32_t *__restrict__ kin, c
         }
 #pragma unroll
         for (int r = 0; r < kScatItems; ++r) {
-            if (r < R) {
+            if (r < R && (FULL || wbase + r * 32 + lane < cnt)) {
                 const uint32_t lp = (r & 1) ? (rank2[r / 2] >> 16) : (rank2[r / 2] & 0xffffu);
                 bufv[lp] = v[r];
             }
@@ -1078,7 +1157,7 @@ __global__ void __launch_bounds__(kScatThreads, 2)
 sort_scatter_kernel(const uint32_t *keys_in, const uint32_t *vals_in, uint32_t *keys_out, uint32_t *vals_out,
                     const uint32_t *__restrict__ offsets, const uint2 *__restrict__ tilemap,
                     const uint32_t *__restrict__ n_tiles, unsigned *__restrict__ ticket, int64_t L, int64_t T,
-                    int shift, int first) {
+                    int shift, int first_pass) {
     __shared__ uint32_t cursor, cursor_next;
     if (threadIdx.x == 0) cursor = blockIdx.x;
     __syncthreads();
@@ -1086,22 +1165,35 @@ sort_scatter_kernel(const uint32_t *keys_in, const uint32_t *vals_in, uint32_t *
         const uint32_t w = *const_cast<volatile uint32_t *>(&cursor);
         if (w >= __ldg(n_tiles)) break;
         const TileRef tr = decode_tile(__ldg(tilemap + w));
+        if (first_pass && tr.fast) {                   // fast segments have no first pass
+            __syncthreads();
+            if (threadIdx.x == 0) cursor = gridDim.x + atomicAdd(ticket, 1u);
+            __syncthreads();
+            continue;
+        }
         const int64_t seg = tr.seg, tile = tr.tile;
         const int64_t sbase = seg * L, t0 = tile * kSortTile;
         const int n = tr.n;
-        const bool d = tr.direct;
-        const uint32_t *ki = d ? keys_out : keys_in;
-        const uint32_t *vi = d ? vals_out : vals_in;
-        uint32_t *ko = d ? const_cast<uint32_t *>(keys_in) : keys_out;
-        uint32_t *vo = d ? const_cast<uint32_t *>(vals_in) : vals_out;
-        if (n == kSortTile)
-            scatter_tile<true>(ki + sbase + t0, (d && first) ? nullptr : vi + sbase + t0, ko + sbase, vo + sbase,
-                               offsets + (seg * T + tile) * kBins, n, shift, uint32_t(t0), &cursor_next, ticket,
-                               tilemap, n_tiles);
-        else
-            scatter_tile<false>(ki + sbase + t0, (d && first) ? nullptr : vi + sbase + t0, ko + sbase, vo + sbase,
-                                offsets + (seg * T + tile) * kBins, n, shift, uint32_t(t0), &cursor_next, ticket,
-                                tilemap, n_tiles);
+        const bool sw = tr.swapped;
+        const uint32_t *ki = sw ? keys_out : keys_in;
+        const uint32_t *vi = sw ? vals_out : vals_in;
+        uint32_t *ko = sw ? const_cast<uint32_t *>(keys_in) : keys_out;
+        uint32_t *vo = sw ? const_cast<uint32_t *>(vals_in) : vals_out;
+        // the first pass a segment takes: a segment that was not compacted has no values yet
+        const bool seg_first = first_pass || tr.fast;
+        const uint32_t *vin = (tr.direct && seg_first) ? nullptr : vi + sbase + t0;
+        const uint32_t *off = offsets + (seg * T + tile) * kBins;
+        if (tr.fast) {
+            if (n == kSortTile)
+                scatter_tile<true, true>(ki + sbase + t0, vin, ko + sbase, vo + sbase, off, n, shift, uint32_t(t0),
+                                         &cursor_next, ticket, tilemap, n_tiles);
+            else
+                scatter_tile<false, true>(ki + sbase + t0, vin, ko + sbase, vo + sbase, off, n, shift, uint32_t(t0),
+                                          &cursor_next, ticket, tilemap, n_tiles);
+        } else {
+            scatter_tile<false, false>(ki + sbase + t0, vin, ko + sbase, vo + sbase, off, n, shift, uint32_t(t0),
+                                       &cursor_next, ticket, tilemap, n_tiles);
+        }
         __syncthreads();
         if (threadIdx.x == 0) cursor = cursor_next;
         __syncthreads();
@@ -1122,8 +1214,7 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__re
                     unsigned *__restrict__ ticket, int64_t L, int64_t T, int shift) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t *match = reinterpret_cast<uint32_t *>(smem_raw);
-    uint16_t *wcnt_all = reinterpret_cast<uint16_t *>(smem_raw + kMatchBytes);
-    uint16_t *wfg_all = reinterpret_cast<uint16_t *>(smem_raw + kMatchBytes + kCntBytes);
+    uint32_t *wpk_all = reinterpret_cast<uint32_t *>(smem_raw + kMatchBytes);     // [warps][kBins]
     uint32_t *off = reinterpret_cast<uint32_t *>(smem_raw + kMatchBytes + 2 * kCntBytes);
     uint32_t *fgoff = off + kBins;
     uint32_t *keybuf = fgoff + kBins;                  // [kSortTile] keys of the tile
@@ -1143,10 +1234,10 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__re
     const int64_t t0 = tile * kSortTile;
     const int n = tr.n;
 
-    const bool swapped = tr.direct;                      // (a direct segment: buffers in swapped roles)
+    const bool swapped = tr.swapped;
     const uint32_t *keys = (swapped ? keys_alt : keys_main) + sbase + t0;
     const uint32_t *vals = (swapped ? vals_alt : vals_main) + sbase + t0;
-    for (int i = tid; i < int(2 * kCntBytes / 4); i += kSortThreads) reinterpret_cast<uint32_t *>(wcnt_all)[i] = 0;
+    for (int i = tid; i < int(2 * kCntBytes / 4); i += kSortThreads) wpk_all[i] = 0;
     {
         const int64_t o = (seg * T + tile) * kBins;
         for (int b = tid; b < kBins; b += kSortThreads) {
@@ -1175,38 +1266,57 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__re
     draw_next_tile(&cursor_next, ticket);
     __syncthreads();
     uint32_t rkfg[kSortItems];          // rank | fg rank << 16
-    uint16_t *wcnt = wcnt_all + warp * kBins;
-    uint16_t *wfg = wfg_all + warp * kBins;
-    const uint32_t lt = lanemask_lt();
+    // per (warp, digit) one packed counter: elements seen | foreground elements seen << 16.  ONE
+    // atomic returns both, so an element's rank and the number of foreground elements before it
+    // come from the same serialisation of the warp's lanes (see rank_round).
+    uint32_t *wpk = wpk_all + warp * kBins;
+    // fast segments: one atomic per element (see rank_round_fast); all others: exact array order
+    // from kBits ballots per round, the leader lane updates the counter (rank_round_exact)
+    const bool exact_order = !tr.fast;
+    if (!exact_order) {
 #pragma unroll
-    for (int r = 0; r < kSortItems; ++r) {
-        const uint32_t kr = keybuf[wbase + r * 32 + lane];
-        const uint32_t d = digit_of(kr, shift);
-        const bool fg = key_is_fg(kr);
-        const uint32_t fgball = __ballot_sync(0xffffffffu, fg);
-        uint32_t peers;
-        const uint32_t fgold_src = wfg[d];            // read before any leader updates it in this ranking round
-        const uint32_t rk = rank_round(d, wcnt, lane, lt, peers);
-        const int leader = __ffs(peers) - 1;
-        const uint32_t fgold = fgold_src;            // every peer read the same word
-        if (lane == leader) wfg[d] = uint16_t(fgold + __popc(peers & fgball));
-        __syncwarp();
-        rkfg[r] = rk | ((fgold + __popc(peers & fgball & lt)) << 16);
+        for (int r = 0; r < kSortItems; ++r) {
+            const uint32_t kr = keybuf[wbase + r * 32 + lane];
+            const uint32_t d = digit_of(kr, shift);
+            rkfg[r] = 0;
+            if (wbase + r * 32 + lane < n) rkfg[r] = atomicAdd(&wpk[d], key_is_fg(kr) ? 0x10001u : 1u);
+        }
+    } else {
+        const uint32_t lt = lanemask_lt();
+#pragma unroll
+        for (int r = 0; r < kSortItems; ++r) {
+            const uint32_t kr = keybuf[wbase + r * 32 + lane];
+            const uint32_t d = digit_of(kr, shift);     // (padding lanes: last digit, highest positions)
+            const uint32_t fgball = __ballot_sync(0xffffffffu, key_is_fg(kr));
+            uint32_t peers = 0xffffffffu;
+#pragma unroll
+            for (int b = 0; b < kBits; ++b) {
+                const bool bit = (d >> b) & 1u;
+                const uint32_t bal = __ballot_sync(0xffffffffu, bit);
+                peers &= bit ? bal : ~bal;
+            }
+            const int leader = __ffs(peers) - 1;
+            uint32_t old = 0;
+            if (lane == leader) {
+                old = wpk[d];
+                wpk[d] = old + __popc(peers) + (__popc(peers & fgball) << 16);
+            }
+            __syncwarp();
+            old = __shfl_sync(0xffffffffu, old, leader);
+            rkfg[r] = old + __popc(peers & lt) + (__popc(peers & fgball & lt) << 16);
+        }
     }
     __syncthreads();
     constexpr int BPT = kBins / kSortThreads;
 #pragma unroll
     for (int q = 0; q < BPT; ++q) {
         const int b = BPT * tid + q;
-        uint32_t run = 0, runfg = 0;
+        uint32_t run = 0;                // both halves at once: a tile holds at most 8192 < 65536 elements
 #pragma unroll
         for (int w = 0; w < kSortWarps; ++w) {
-            const uint32_t c = wcnt_all[w * kBins + b];
-            wcnt_all[w * kBins + b] = uint16_t(run);
+            const uint32_t c = wpk_all[w * kBins + b];
+            wpk_all[w * kBins + b] = run;
             run += c;
-            const uint32_t f = wfg_all[w * kBins + b];
-            wfg_all[w * kBins + b] = uint16_t(runfg);
-            runfg += f;
         }
     }
     prefetch_next_tile(&cursor_next, tilemap, __ldg(n_tiles));
@@ -1222,8 +1332,9 @@ rank_jaccard_kernel(const uint32_t *__restrict__ keys_main, const uint32_t *__re
             const uint32_t d = digit_of(k, shift);
             const bool ign = k == kKeyIgnored;
             const bool fg = key_is_fg(k);
-            const uint32_t i_glob = off[d] + wcnt[d] + (rkfg[r] & 0xffffu);
-            const uint32_t cs_before = fgoff[d] + wfg[d] + (rkfg[r] >> 16);
+            const uint32_t before = wpk[d] + rkfg[r];            // packed: this tile's earlier elements of digit d
+            const uint32_t i_glob = off[d] + (before & 0xffffu);
+            const uint32_t cs_before = fgoff[d] + (before >> 16);
             const uint32_t union_before = n_pos + (i_glob - cs_before);
             const float I = float(n_pos - cs_before);
             const float U = float(union_before);
@@ -1428,9 +1539,11 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
     // drop the elements past the pruning bound
     const unsigned nblk_all = unsigned(g.S * g.T);
     const int prune = env_int("B200_LOVASZ_NO_PRUNE", 0) ? 0 : 1;
-    prune_count_kernel<<<nblk_all, kSortThreads, 0, s>>>(w.keysA, w.maxfg, w.minkey, w.kept, g.L, g.T, prune);
+    const int allow_fast = env_int("B200_LOVASZ_EXACT", 0) ? 0 : 1;     // 0: every segment sorts on all 30 bits
+    prune_count_kernel<<<nblk_all, kSortThreads, 0, s>>>(w.keysA, w.maxfg, w.minkey, w.kept, w.fgkept, g.L, g.T,
+                                                         prune);
     if ((rc = launch_status("lovasz prune count launch")) != B200_OK) return rc;
-    prune_scan_kernel<<<unsigned(g.S), kBins, 0, s>>>(w.kept, w.Lp, w.direct, g.L, g.T);
+    prune_scan_kernel<<<unsigned(g.S), kBins, 0, s>>>(w.kept, w.fgkept, w.Lp, w.direct, g.L, g.T, allow_fast);
     if ((rc = launch_status("lovasz prune scan launch")) != B200_OK) return rc;
     prune_compact_kernel<<<nblk_all, kSortThreads, 0, s>>>(w.keysA, w.maxfg, w.minkey, w.kept, w.direct, w.keysB,
                                                            w.valsB, jacc, g.L, g.T, prune);
@@ -1449,18 +1562,21 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
     const unsigned nblk_hist = grid_of(8), nblk = grid_of(2);
     unsigned *tickets = w.status + 16;           // zeroed with the status word; one per kernel
 
-    // compacted segments go B -> A -> B; segments that were not compacted A -> B -> A
+    // Buffer roles as a compacted segment that takes all three passes sees them: B -> A -> B,
+    // ranked from B (other segments: see TileRef).  Fast segments sit out the first pass.
     uint32_t *kin = w.keysB, *vin = w.valsB, *kout = w.keysA, *vout = w.valsA;
     for (int pass = 0; pass < kPasses - 1; ++pass) {
         const int shift = 1 + pass * kBits;
+        const int first_pass = pass == 0 ? 1 : 0;
         sort_hist_kernel<false><<<nblk_hist, kSortThreads, 0, s>>>(kin, w.hist, nullptr, w.tilemap, w.n_tiles, kout,
-                                                                  g.L, g.T, shift);
+                                                                  g.L, g.T, shift, first_pass);
         if ((rc = launch_status("lovasz sort histogram launch")) != B200_OK) return rc;
-        sort_scan_kernel<false><<<unsigned(g.S), kBins, 0, s>>>(w.hist, nullptr, nullptr, w.Lp, g.T);
+        sort_scan_kernel<false><<<unsigned(g.S), kBins, 0, s>>>(w.hist, nullptr, nullptr, w.Lp, w.direct, g.T,
+                                                                first_pass);
         if ((rc = launch_status("lovasz sort scan launch")) != B200_OK) return rc;
         sort_scatter_kernel<<<nblk, kScatThreads, kScatterSmem, s>>>(kin, vin, kout, vout, w.hist, w.tilemap,
                                                                      w.n_tiles, tickets + pass, g.L, g.T, shift,
-                                                                     pass == 0 ? 1 : 0);
+                                                                     first_pass);
         if ((rc = launch_status("lovasz sort scatter launch")) != B200_OK) return rc;
         std::swap(kin, kout);
         std::swap(vin, vout);
@@ -1468,14 +1584,14 @@ extern "C" int b200_lovasz_forward(const void *logits, const int64_t *labels, fl
     {
         const int shift = 1 + (kPasses - 1) * kBits;
         sort_hist_kernel<true><<<nblk_hist, kSortThreads, 0, s>>>(kin, w.hist, w.fghist, w.tilemap, w.n_tiles, kout,
-                                                                 g.L, g.T, shift);
+                                                                 g.L, g.T, shift, 0);
         if ((rc = launch_status("lovasz last histogram launch")) != B200_OK) return rc;
-        sort_scan_kernel<true><<<unsigned(g.S), kBins, 0, s>>>(w.hist, w.fghist, w.n_pos, w.Lp, g.T);
+        sort_scan_kernel<true><<<unsigned(g.S), kBins, 0, s>>>(w.hist, w.fghist, w.n_pos, w.Lp, w.direct, g.T, 0);
         if ((rc = launch_status("lovasz last scan launch")) != B200_OK) return rc;
         rank_jaccard_kernel<<<nblk, kSortThreads, kJaccardSmem, s>>>(kin, vin, kout, vout, w.hist, w.fghist,
                                                                       w.n_pos, jacc,
                                                                       w.partial, w.tilemap, w.n_tiles,
-                                                                      tickets + 2, g.L, g.T, shift);
+                                                                      tickets + 3, g.L, g.T, shift);
         if ((rc = launch_status("lovasz rank+jaccard launch")) != B200_OK) return rc;
     }
     loss_kernel<<<unsigned(g.S), 32, 0, s>>>(w.partial, loss, w.Lp, g.T);

@@ -180,14 +180,12 @@ __device__ __forceinline__ float grad_phase3(const PixelFinal<KIND> &fin, float 
 }
 
 // Upstream-gradient scale shared by all backward kernels: grad_mode 1 reads one device
-// float, denom (optional) is a device double; mode 2 multiplies per pixel later.  The divisor
-// may be a count that is still being added over the GPUs (resolve_count): all 32 lanes of
-// warp 0 of every block must make this call.
+// float, denom (optional) is a device double; mode 2 multiplies per pixel later.
 __device__ __forceinline__ float uniform_grad_scale(const void *grad_out, int grad_mode,
-                                                    const double *denom, void *workspace) {
+                                                    const double *denom) {
     double g = 1.0;
     if (grad_mode == 1) g = double(*static_cast<const float *>(grad_out));
-    if (denom) g /= resolve_count(denom, workspace);
+    if (denom) g /= *denom;
     return static_cast<float>(g);
 }
 

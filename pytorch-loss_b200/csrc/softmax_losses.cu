@@ -85,7 +85,7 @@ tile_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap map_in,
     __syncthreads();
 
     float gscale = 1.f;
-    if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom, prm.workspace);
+    if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
 
     double acc_loss = 0.0, acc_cnt = 0.0;
     uint32_t phase = 0;
@@ -257,7 +257,7 @@ rows_kernel(const SoftmaxParams prm) {
     }
     __syncthreads();
     float gscale = 1.f;
-    if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom, prm.workspace);
+    if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
     double acc_loss = 0.0, acc_cnt = 0.0;
     uint32_t phase = 0;
     const uint32_t row_bytes = uint32_t(C) * sizeof(T);
@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(kThreads) sweep_kernel(const SoftmaxParams prm
     const T *gout = static_cast<const T *>(prm.grad_out);
     const int C = static_cast<int>(prm.C);
     float gscale = 1.f;
-    if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom, prm.workspace);
+    if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
     double acc_loss = 0.0, acc_cnt = 0.0;
     const int64_t P = prm.N * prm.M;
     for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < P;
@@ -545,7 +545,7 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
         T *losses = static_cast<T *>(prm.losses);
         const LossConsts kc = prm.k;
         float gscale = 1.f;
-        if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom, prm.workspace);
+        if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
         float acc32 = 0.f;
         int cnt32 = 0;
         int k = 0;
@@ -1147,7 +1147,7 @@ tile_chunk_bwd_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorM
         const int bxo = (pix / kChunkTP) * int(lay.box_elems) + (pix % kChunkTP);
         const T *gout = static_cast<const T *>(prm.grad_out);
         const LossConsts kc = prm.k;
-        const float gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom, prm.workspace);
+        const float gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
         int k = 0;
         bool alive = true;
         for (int64_t t = first; t < total_tiles && alive; t += stride) {
@@ -1342,7 +1342,7 @@ rows_pipe_kernel(const SoftmaxParams prm) {
         T *losses = static_cast<T *>(prm.losses);
         const LossConsts kc = prm.k;
         float gscale = 1.f;
-        if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom, prm.workspace);
+        if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
         int k = 0;
         for (int64_t r = first; r < prm.N; r += stride, ++k) {
             const int s = k % NS;
@@ -2127,8 +2127,7 @@ __global__ void __launch_bounds__(256) count_valid_kernel(const int64_t *labels,
     }
     for (int64_t j = nvec * 2 + int64_t(blockIdx.x) * 256 + threadIdx.x; j < P; j += stride)
         cnt += int(labels[j] != ignore);
-    // across GPUs: post the count and leave; the kernel that divides by it collects the sum
-    grid_reduce_finish(0.0, double(cnt), workspace, out, sh, kTagCount, /*defer=*/true);
+    grid_reduce_finish(0.0, double(cnt), workspace, out, sh, kTagCount);
 }
 
 }  // namespace

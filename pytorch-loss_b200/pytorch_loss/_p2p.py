@@ -39,7 +39,7 @@ class Exchange:
         self.device, self.world, self.rank = device, world, rank
         self.local_slots = local_slots              # keeps the shared allocation alive
         self.peer_slots = peer_slots                # rank -> device address of that rank's array here
-        self.seq = torch.zeros(8, dtype=torch.int64, device=device)   # [0] call counter, [1] pending count
+        self.seq = torch.zeros(8, dtype=torch.int64, device=device)   # the call counter (eight words reserved)
         ptrs = [0] * MAX_RANKS
         for p in range(world):
             ptrs[p] = local_slots.data_ptr() if p == rank else int(peer_slots[p])

@@ -103,9 +103,8 @@ _ENTRY_FUSED = {
 
 
 def count_valid(labels, ignore_index, exchange=None):
-    """Device double: the number of labels != ignore_index.  With an `_p2p.Exchange` the kernel
-    posts this rank's count to the peers and the value stays "pending" until the gradient kernel
-    that divides by it collects the global count (no kernel waits in between)."""
+    """Device double: the number of labels != ignore_index, added over the ranks of an
+    `_p2p.Exchange` inside the kernel when one is given."""
     dev = labels.device
     lib = _cabi.load_library()
     if labels.dtype != torch.int64:

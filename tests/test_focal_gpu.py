@@ -204,11 +204,12 @@ def test_exchange_foreign_tag_is_reported():
     assert bool(torch.isnan(rec[4]))
 
 
-def test_deferred_count_is_collected_by_the_gradient_kernel():
-    """Two emulated ranks on one GPU (two exchange contexts over each other's slot arrays, kernels
-    launched one after the other, so nothing waits on a kernel that has not run): both post their
-    label counts (no wait), then rank 0's fused label-smooth step collects the global count while
-    it runs and divides its gradient by it."""
+def test_two_emulated_ranks_exchange_the_label_count():
+    """Two emulated ranks on one GPU: two exchange contexts over each other's slot arrays, their
+    kernels launched one after the other, so no kernel ever waits on one that has not run.  Rank 1's
+    count kernel runs first: it posts its count and gives up waiting for rank 0 (bounded, NaN, status
+    bit).  Rank 0's count kernel then finds both messages and gets the GLOBAL count, which its fused
+    label-smooth step divides by; that step's own sum exchange times out (rank 1 posts no sum)."""
     import pytorch_loss  # noqa: F401
     from pytorch_loss import _cabi, _p2p
     from oracle import losses as O
@@ -217,7 +218,7 @@ def test_deferred_count_is_collected_by_the_gradient_kernel():
     st = _cabi.stream_ptr(dev)
     nbytes = int(lib.b200_exchange_slot_bytes(2))
     arrays = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(2)]
-    ranks = [_p2p.Exchange(dev, 2, r, arrays[r], {1 - r: arrays[1 - r].data_ptr()}, 2000) for r in range(2)]
+    ranks = [_p2p.Exchange(dev, 2, r, arrays[r], {1 - r: arrays[1 - r].data_ptr()}, 500) for r in range(2)]
     g = torch.Generator().manual_seed(91)
     logits = torch.randn(4, 19, 32, 32, generator=g)
     labels = torch.randint(0, 19, (4, 32, 32), generator=g)
@@ -226,14 +227,15 @@ def test_deferred_count_is_collected_by_the_gradient_kernel():
     xs = [logits[2 * r:2 * r + 2].to(dev) for r in range(2)]
     ys = [labels[2 * r:2 * r + 2].to(dev) for r in range(2)]
     cnts = [_cabi.new_record(dev) for _ in range(2)]
-    for r in range(2):
+    for r in (1, 0):
         ws = ranks[r].workspace()
         _cabi.check(lib.b200_count_valid(_cabi.ptr(ys[r]), ys[r].numel(), 255, _cabi.ptr(cnts[r]), _cabi.ptr(ws),
                                          ws.numel(), st))
     torch.cuda.synchronize()
-    assert float(cnts[0][:4].view(torch.float64)[1]) == -1.0        # posted, not yet collected
-    # rank 1's loss sum is not there when rank 0's step ends, so rank 0's sum exchange times out;
-    # its gradient only needs the counts, which both ranks have posted
+    w1 = ranks[1].workspace()
+    assert lib.b200_read_status(_cabi.ptr(w1), st) == 4 and b"0x100" in lib.b200_last_error()
+    assert bool(torch.isnan(cnts[1][:4].view(torch.float64)[1]))
+    assert float(cnts[0][:4].view(torch.float64)[1]) == float((labels != 255).sum())   # the GLOBAL count
     grad = torch.empty_like(xs[0])
     rec = _cabi.new_record(dev)
     ws = ranks[0].workspace()
@@ -241,9 +243,9 @@ def test_deferred_count_is_collected_by_the_gradient_kernel():
         _cabi.ptr(xs[0]), _cabi.ptr(ys[0]), _cabi.ptr(grad), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
         _cabi._vp(cnts[0].data_ptr() + 8), 2, 19, 32 * 32, _cabi.F32, 255, 0.1, st))
     torch.cuda.synchronize()
-    assert float(cnts[0][:4].view(torch.float64)[1]) == float((labels != 255).sum())   # the GLOBAL count
     assert_grad_close(grad, want_grad[:2])
     assert lib.b200_read_status(_cabi.ptr(ws), st) == 4 and b"0x100" in lib.b200_last_error()
+    assert bool(torch.isnan(rec[4]))
 
 
 def test_focal_predicted_count_correction():
