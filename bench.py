@@ -323,7 +323,7 @@ def direct_calls(wl, sets, device):
         # the module's training step: fused forward+backward kernel, then the rescale kernel that
         # leaves at once for an upstream gradient of 1
         fwd = lambda i: _cabi.check(lib.b200_focal_forward_backward_reduced(
-            P(xs[i]), P(ys[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(), None, 1.0 / e, e, dt, 2.0, 0.25, st))
+            P(xs[i]), P(ys[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(), None, 1.0 / e, e, dt, 2.0, 0.25, 0, st))
         return fwd, rescale
     if wl.kind == "lovasz":
         nbytes = int(lib.b200_lovasz_workspace_bytes(n, c, m, 1))
@@ -349,7 +349,7 @@ def direct_calls(wl, sets, device):
             _cabi.check(lib.b200_count_valid(P(new_labels[i]), n * m, 255, P(cnts[i]), P(ws), ws.numel(), st))
             _cabi.check(lib.b200_lsr_forward_backward_reduced(
                 P(xs[i]), P(new_labels[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(),
-                _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255, 0.0, st))
+                _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255, 0.0, 0, st))
         return fwd, rescale
     stem, hyper, ign = {"lsr": ("lsr", 0.1, 255), "lsr_rows": ("lsr", 0.1, -100), "lmargin": ("lmargin", 0.3, 255)}[wl.kind]
     if wl.fused_softmax():
@@ -363,7 +363,7 @@ def direct_calls(wl, sets, device):
         def fwd(i):
             _cabi.check(lib.b200_count_valid(P(ys[i]), n * m, ign, P(cnts[i]), P(ws), ws.numel(), st))
             _cabi.check(f_step(P(xs[i]), P(ys[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(),
-                               _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, ign, hyper, st))
+                               _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, ign, hyper, 0, st))
         return fwd, rescale
     one = torch.ones(1, dtype=torch.float32, device=device)
     if lib.b200_softmax_stats_path(P(xs[0]), P(ys[0]), P(grads[0]), n, c, m, dt):

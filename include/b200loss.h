@@ -91,13 +91,26 @@ int b200_read_status(void *workspace, void *stream);
 int b200_focal_forward_backward_reduced(const void *logits, const void *labels, void *grad_logits,
                                         void *out, void *workspace, size_t workspace_bytes,
                                         const void *denom, float grad_scale, int64_t E, int dtype,
-                                        float gamma, float alpha, void *stream);
+                                        float gamma, float alpha, int defer, void *stream);
 int b200_focal_forward_backward_predicted(const void *logits, const void *labels, void *grad_logits,
                                           void *out, void *workspace, size_t workspace_bytes,
                                           void *denom_state, float *correction, int64_t E, int dtype,
-                                          float gamma, float alpha, void *stream);
+                                          float gamma, float alpha, int defer, void *stream);
 int b200_rescale_gradient(void *grad, const float *grad_out, const float *correction, int64_t E, int dtype,
                           void *stream);
+/* `defer` (fused steps; only acts on a workspace with ranks attached, see "cross-GPU sum"): the
+ * kernel posts this rank's [sum, count] to the peers and returns without waiting for theirs; the
+ * record's float fields stay NaN (and *correction unwritten) until a later call on the same
+ * stream completes it:
+ *   b200_rescale_gradient_finish: what b200_rescale_gradient does, after collecting the ranks'
+ *       sums into `out` (block 0; `correction` and `denom_state` as given to the _predicted step,
+ *       else NULL) -- the wait for the slowest rank and the link overlaps the launch in between;
+ *   b200_exchange_finish: only completes `out` (a loss that is read before or without backward).
+ * Both do nothing extra when the record is complete already.  One record per workspace may be
+ * pending at a time; complete it before the next reducing call on that workspace. */
+int b200_rescale_gradient_finish(void *grad, const float *grad_out, float *correction, int64_t E, int dtype,
+                                 void *workspace, void *out, void *denom_state, void *stream);
+int b200_exchange_finish(void *workspace, void *out, void *denom_state, float *correction, void *stream);
 int b200_exchange_count(double count, void *out, void *workspace, size_t workspace_bytes, void *stream);
 
 /* The same fusion for the two softmax losses (no counterpart in the reference, whose
@@ -118,11 +131,11 @@ int b200_count_valid(const int64_t *labels, int64_t P, int64_t ignore_index, voi
 int b200_lsr_forward_backward_reduced(const void *logits, const int64_t *labels, void *grad_logits,
                                       void *out, void *workspace, size_t workspace_bytes,
                                       const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
-                                      int64_t ignore_index, float smooth, void *stream);
+                                      int64_t ignore_index, float smooth, int defer, void *stream);
 int b200_lmargin_forward_backward_reduced(const void *logits, const int64_t *labels, void *grad_logits,
                                           void *out, void *workspace, size_t workspace_bytes,
                                           const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
-                                          int64_t ignore_index, float lam, void *stream);
+                                          int64_t ignore_index, float lam, int defer, void *stream);
 
 /* ------------------------------------------------- cross-GPU sum (optional) ---
  * No counterpart in the reference (it has no multi-GPU path for these losses).
@@ -136,7 +149,8 @@ int b200_lmargin_forward_backward_reduced(const void *logits, const int64_t *lab
  *
  * The context is `b200_exchange_ctx_bytes()` bytes of device memory laid out as
  *     int32 world; int32 rank; uint32 poll_limit; uint32 reserved;
- *     uint64 *seq;              // eight zero-initialised uint64 in this rank's memory
+ *     uint64 *seq;              // eight zero-initialised uint64 in this rank's memory (call
+ *                               // counter; sequence number of a deferred sum)
  *     void  *slots[16];         // slots[p]: rank p's slot array as mapped in THIS
  *                               // process (p == rank: the local array); each array is
  *                               // b200_exchange_slot_bytes(world) bytes, zero-initialised

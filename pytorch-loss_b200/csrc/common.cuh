@@ -60,7 +60,8 @@ struct ExchangeCtx {        // lives in device memory; filled by the host once (
     int rank;
     unsigned poll_limit;    // polls of one slot before a wait gives up (status bit 0x100)
     unsigned reserved;
-    unsigned long long *seq;                    // this rank's call counter (eight words reserved)
+    unsigned long long *seq;                    // [0] this rank's call counter; [1] sequence number of a
+                                                // loss sum that is posted but not yet collected (0: none)
     ExchangeSlot *slots[kMaxExchangeRanks];     // slots[p]: rank p's array [kExchangeSets][world]
 };
 constexpr size_t kExchangeCtxOffset = 8;
@@ -231,16 +232,42 @@ __device__ __forceinline__ ExchangeCtx *exchange_of(void *workspace) {
                      : nullptr;
 }
 
+// Collects a loss sum that grid_reduce_finish<defer> posted earlier and completes its record.
+// One full warp calls it.  Nothing pending: returns at once (so it may be called twice).
+// Returns true in lane 0 when it has just written the record.
+__device__ __forceinline__ bool exchange_finish_pending(void *workspace, ReduceRecord *out) {
+    ExchangeCtx *ex = exchange_of(workspace);
+    if (!ex) return false;
+    const unsigned long long seq = ex->seq[1];
+    if (seq == 0ull) return false;
+    double a, b;
+    const unsigned bad = exchange_collect(ex, seq, kTagSum, a, b);
+    if ((threadIdx.x & 31) != 0) return false;
+    if (bad) {
+        atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, bad);
+        a = b = __longlong_as_double(0x7ff8000000000000ll);
+    }
+    out->sum = a;
+    out->count = b;
+    out->mean = static_cast<float>(a / b);
+    out->sum32 = static_cast<float>(a);
+    ex->seq[1] = 0ull;
+    return true;
+}
+
 // Final step of a reducing forward kernel.  Every block calls it once with its
 // partial (sum, count).  The block that takes the last ticket adds all partials
 // in a fixed order, writes the record and re-arms the ticket: deterministic,
 // no spinning, no second launch.  blockDim.x must be a multiple of 32, <= 1024.
 // With an exchange attached to the workspace the pair is first added over the ranks (message
-// tag `tag`).
+// tag `tag`).  `defer` (and an exchange): this rank's pair is only POSTED; the record keeps
+// NaN in its float fields until a later kernel of the stream collects the ranks' pairs
+// (exchange_finish_pending) -- the wait for the slowest rank and for the link then overlaps
+// whatever runs in between instead of holding this kernel.
 // Returns true in exactly one thread of the grid: the one that has just written the record.
 __device__ __forceinline__ bool grid_reduce_finish(double sum, double cnt, void *workspace,
                                                    ReduceRecord *out, double *sh,
-                                                   unsigned tag = kTagSum) {
+                                                   unsigned tag = kTagSum, bool defer = false) {
     block_sum2(sum, cnt, sh);
     unsigned *ticket = reinterpret_cast<unsigned *>(workspace);
     double2 *partials =
@@ -264,25 +291,32 @@ __device__ __forceinline__ bool grid_reduce_finish(double sum, double cnt, void 
     block_sum2(a, b, sh);
     if (threadIdx.x >= 32) return false;
     ExchangeCtx *ex = exchange_of(workspace);
+    bool pending = false;
     if (ex) {
         a = __shfl_sync(0xffffffffu, a, 0);
         b = __shfl_sync(0xffffffffu, b, 0);
         const unsigned long long seq = exchange_post(ex, tag, a, b);
-        const unsigned bad = exchange_collect(ex, seq, tag, a, b);
-        if (bad) {
-            if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, bad);
-            a = b = __longlong_as_double(0x7ff8000000000000ll);
+        if (defer) {
+            if (threadIdx.x == 0) ex->seq[1] = seq;
+            pending = true;
+        } else {
+            const unsigned bad = exchange_collect(ex, seq, tag, a, b);
+            if (bad) {
+                if (threadIdx.x == 0) atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, bad);
+                a = b = __longlong_as_double(0x7ff8000000000000ll);
+            }
         }
     }
     if (threadIdx.x == 0) {
-        out->sum = a;
+        const float nan32 = __int_as_float(0x7fc00000);
+        out->sum = a;                   // (pending: this rank's sums for now)
         out->count = b;
-        out->mean = static_cast<float>(a / b);
-        out->sum32 = static_cast<float>(a);
+        out->mean = pending ? nan32 : static_cast<float>(a / b);
+        out->sum32 = pending ? nan32 : static_cast<float>(a);
         out->pad[0] = 0.f;
         out->pad[1] = 0.f;
         *ticket = 0u;
-        return true;
+        return !pending;
     }
     return false;
 }

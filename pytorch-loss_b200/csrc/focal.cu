@@ -40,6 +40,7 @@ struct FocalParams {
     float host_scale;    // extra factor on the gradient (0 is read as 1): 1/E of a fused 'mean' step
     double *denom_state; // optional: predicted divisor, replaced by the reduced count after the sum
     float *correction;   // with denom_state: predicted / actual divisor of this call
+    int defer;           // cross-GPU sum: post only; b200_exchange_finish / b200_rescale_gradient_finish collect
 };
 
 // The fused step of a batch sharded over GPUs divides by the GLOBAL element count, which the
@@ -48,11 +49,14 @@ struct FocalParams {
 // the rescale kernel and the actual count for the next call.  With unchanged shapes the
 // correction is exactly 1.  Every block has read *denom_state before it took its ticket, so
 // the overwrite cannot be seen by this launch.
+__device__ __forceinline__ void publish_denominator(double *denom_state, float *correction, const ReduceRecord *out) {
+    if (!denom_state) return;
+    const double used = *denom_state, actual = out->count;
+    *correction = static_cast<float>(used / actual);
+    *denom_state = actual;
+}
 __device__ __forceinline__ void publish_denominator(const FocalParams &prm) {
-    if (!prm.denom_state) return;
-    const double used = *prm.denom_state, actual = prm.out->count;
-    *prm.correction = static_cast<float>(used / actual);
-    *prm.denom_state = actual;
+    publish_denominator(prm.denom_state, prm.correction, prm.out);
 }
 
 template <bool GAMMA2>
@@ -157,7 +161,7 @@ __global__ void __launch_bounds__(kThreads) focal_kernel(const FocalParams prm) 
     if (REDUCE) {
         __shared__ double sh[64];
         const double cnt = (blockIdx.x == 0 && threadIdx.x == 0) ? double(prm.E) : 0.0;
-        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh)) publish_denominator(prm);
+        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh, kTagSum, prm.defer != 0)) publish_denominator(prm);
     }
 }
 
@@ -284,7 +288,7 @@ __global__ void __launch_bounds__(kRingBlock) focal_ring_kernel(const FocalParam
     }
     if (REDUCE) {
         const double cnt = (blockIdx.x == 0 && tid == 0) ? double(prm.E) : 0.0;
-        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh)) publish_denominator(prm);
+        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh, kTagSum, prm.defer != 0)) publish_denominator(prm);
     }
 }
 
@@ -318,7 +322,7 @@ __global__ void __launch_bounds__(kThreads) focal_kernel_unaligned(const FocalPa
     if (REDUCE) {
         __shared__ double sh[64];
         const double cnt = (blockIdx.x == 0 && threadIdx.x == 0) ? double(prm.E) : 0.0;
-        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh)) publish_denominator(prm);
+        if (grid_reduce_finish(acc, cnt, prm.workspace, prm.out, sh, kTagSum, prm.defer != 0)) publish_denominator(prm);
     }
 }
 
@@ -472,7 +476,7 @@ extern "C" int b200_focal_forward_backward(const void *logits, const void *label
 extern "C" int b200_focal_forward_backward_reduced(const void *logits, const void *labels, void *grad_logits,
                                                    void *out, void *workspace, size_t workspace_bytes,
                                                    const void *denom, float grad_scale, int64_t E, int dtype,
-                                                   float gamma, float alpha, void *stream) {
+                                                   float gamma, float alpha, int defer, void *stream) {
     if (E < 0 || !out) {
         set_error("b200_focal_forward_backward_reduced: need E >= 0 and out");
         return B200_ERR_ARG;
@@ -496,6 +500,7 @@ extern "C" int b200_focal_forward_backward_reduced(const void *logits, const voi
     prm.gamma = gamma;
     prm.alpha = alpha;
     prm.host_scale = grad_scale;
+    prm.defer = defer;
     return dispatch_focal<kFwdBwd, true>(prm, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -507,7 +512,7 @@ extern "C" int b200_focal_forward_backward_reduced(const void *logits, const voi
 extern "C" int b200_focal_forward_backward_predicted(const void *logits, const void *labels, void *grad_logits,
                                                      void *out, void *workspace, size_t workspace_bytes,
                                                      void *denom_state, float *correction, int64_t E, int dtype,
-                                                     float gamma, float alpha, void *stream) {
+                                                     float gamma, float alpha, int defer, void *stream) {
     if (E < 0 || !out || !denom_state || !correction) {
         set_error("b200_focal_forward_backward_predicted: need E >= 0, out, denom_state and correction");
         return B200_ERR_ARG;
@@ -532,6 +537,7 @@ extern "C" int b200_focal_forward_backward_predicted(const void *logits, const v
     prm.E = E;
     prm.gamma = gamma;
     prm.alpha = alpha;
+    prm.defer = defer;
     return dispatch_focal<kFwdBwd, true>(prm, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -540,9 +546,43 @@ namespace {
 // grad *= *g unless *g == 1 (the usual upstream gradient of a scalar loss): then every block
 // leaves at once and the stored gradient is already the answer.
 constexpr int kRescaleThreads = 1024;
+// With `workspace`: a loss sum of this stream may be posted to the other GPUs but not collected
+// yet (grid_reduce_finish<defer>).  Warp 0 of block 0 collects it and completes the record `out`
+// (and, for the focal step that divided by a predicted count, the correction and the count for
+// the next call) before anything else; blocks that need the correction wait for that (bounded).
+// E == 0: only that.
 template <typename T>
-__global__ void __launch_bounds__(kRescaleThreads) rescale_kernel(T *grad, const float *g, const float *corr, int64_t E) {
-    const float f = corr ? *g * *corr : *g;
+__global__ void __launch_bounds__(kRescaleThreads) rescale_kernel(T *grad, const float *g, float *corr, int64_t E,
+                                                                  void *workspace, ReduceRecord *out,
+                                                                  double *denom_state) {
+    if (workspace) {
+        volatile float *done = &out->pad[0];
+        if (blockIdx.x == 0 && threadIdx.x < 32) {
+            if (exchange_finish_pending(workspace, out)) publish_denominator(denom_state, corr, out);
+            if (threadIdx.x == 0) {
+                __threadfence();
+                *done = 1.f;
+            }
+        }
+        if (corr && E > 0) {
+            if (threadIdx.x == 0) {                      // one poller per block
+                const ExchangeCtx *ex = exchange_of(workspace);
+                const unsigned limit = ex ? ex->poll_limit : (1u << 20);
+                unsigned polls = 0;
+                while (*done != 1.f) {
+                    if (++polls > limit) {
+                        atomicOr(reinterpret_cast<unsigned *>(workspace) + 1, 0x100u);
+                        break;
+                    }
+                    __nanosleep(32);
+                }
+                __threadfence();
+            }
+            __syncthreads();
+        }
+    }
+    if (E == 0) return;
+    const float f = corr ? *g * *static_cast<volatile float *>(corr) : *g;
     if (f == 1.f) return;
     constexpr int V = 16 / int(sizeof(T));                 // elements per 16-byte access
     const bool aligned = (reinterpret_cast<uintptr_t>(grad) & 15) == 0;
@@ -579,6 +619,32 @@ __global__ void count_exchange_kernel(double count, void *workspace, ReduceRecor
 }  // namespace
 }  // namespace b200
 
+namespace {
+int launch_rescale(void *grad, const float *grad_out, float *correction, int64_t E, int dtype, void *workspace,
+                   void *out, void *denom_state, void *stream) {
+    // one block of 1024 threads per SM at most: the usual call (upstream gradient 1) only has to
+    // start and leave, and 148 x 1024 threads x 4 vectors in flight still cover the memory latency
+    int64_t grid = (E + kRescaleThreads * 16 - 1) / (kRescaleThreads * 16);
+    const int64_t cap = int64_t(sm_count());
+    if (grid > cap) grid = cap;
+    if (grid < 1) grid = 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ReduceRecord *rec = static_cast<ReduceRecord *>(out);
+    double *ds = static_cast<double *>(denom_state);
+    if (dtype == B200_F32)
+        rescale_kernel<float><<<unsigned(grid), E > 0 ? kRescaleThreads : 32, 0, s>>>(static_cast<float *>(grad), grad_out,
+                                                                                     correction, E, workspace, rec, ds);
+    else if (dtype == B200_F16)
+        rescale_kernel<__half><<<unsigned(grid), kRescaleThreads, 0, s>>>(static_cast<__half *>(grad), grad_out,
+                                                                          correction, E, workspace, rec, ds);
+    else {
+        set_error("rescale: unknown dtype code %d", dtype);
+        return B200_ERR_ARG;
+    }
+    return launch_status("gradient rescale kernel launch");
+}
+}  // namespace
+
 // In place: grad[i] *= *grad_out * *correction (floats in device memory; correction may be
 // null = 1); a no-op kernel when the product is 1.
 extern "C" int b200_rescale_gradient(void *grad, const float *grad_out, const float *correction, int64_t E,
@@ -588,19 +654,29 @@ extern "C" int b200_rescale_gradient(void *grad, const float *grad_out, const fl
         return B200_ERR_ARG;
     }
     if (E == 0) return B200_OK;
-    // one block of 1024 threads per SM at most: the usual call (upstream gradient 1) only has to
-    // start and leave, and 148 x 1024 threads x 4 vectors in flight still cover the memory latency
-    int64_t grid = (E + kRescaleThreads * 16 - 1) / (kRescaleThreads * 16);
-    const int64_t cap = int64_t(sm_count());
-    if (grid > cap) grid = cap;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == B200_F32) rescale_kernel<float><<<unsigned(grid), kRescaleThreads, 0, s>>>(static_cast<float *>(grad), grad_out, correction, E);
-    else if (dtype == B200_F16) rescale_kernel<__half><<<unsigned(grid), kRescaleThreads, 0, s>>>(static_cast<__half *>(grad), grad_out, correction, E);
-    else {
-        set_error("b200_rescale_gradient: unknown dtype code %d", dtype);
+    return launch_rescale(grad, grad_out, const_cast<float *>(correction), E, dtype, nullptr, nullptr, nullptr, stream);
+}
+
+// The same, after completing a reduction record whose cross-GPU sum was deferred (`defer` of the
+// fused steps): the kernel first collects the ranks' sums into `out` (and writes `correction` and
+// `denom_state` for the focal step with a predicted count; both may be null otherwise).
+extern "C" int b200_rescale_gradient_finish(void *grad, const float *grad_out, float *correction, int64_t E, int dtype,
+                                            void *workspace, void *out, void *denom_state, void *stream) {
+    if (E < 0 || (E > 0 && (!grad || !grad_out)) || !workspace || !out) {
+        set_error("b200_rescale_gradient_finish: bad arguments");
         return B200_ERR_ARG;
     }
-    return launch_status("gradient rescale kernel launch");
+    return launch_rescale(grad, grad_out, correction, E, dtype, workspace, out, denom_state, stream);
+}
+
+// Completes a deferred record without a gradient to rescale (a loss that is read before, or
+// without, backward).  Does nothing when the record is complete already.
+extern "C" int b200_exchange_finish(void *workspace, void *out, void *denom_state, float *correction, void *stream) {
+    if (!workspace || !out) {
+        set_error("b200_exchange_finish: workspace and out are required");
+        return B200_ERR_ARG;
+    }
+    return launch_rescale(nullptr, nullptr, correction, 0, B200_F32, workspace, out, denom_state, stream);
 }
 
 // out->count = `count` added over the ranks attached to `workspace` (out->sum = 0): the global

@@ -50,6 +50,7 @@ struct SoftmaxParams {
     int nbx;                 // boxes of TP pixels per tile (pair kernel)
     int stages;              // ring depth of the pipelined kernels
     int64_t tiles_per_image, total_tiles;
+    int defer;               // cross-GPU sum of the fused step: post only (see grid_reduce_finish)
 };
 
 // ------------------------------------------------------------------ tile regime
@@ -196,7 +197,7 @@ tile_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap map_in,
         }
     }
     if (TMA && BWD && tid == 0) bulk_wait_all();
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
 // ------------------------------------------------------------------ rows regime
@@ -354,7 +355,7 @@ rows_kernel(const SoftmaxParams prm) {
         }
     }
     if (BULK && BWD && tid == 0) bulk_wait_all();
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
 // ----------------------------------------------------------------- sweep regime
@@ -408,7 +409,7 @@ __global__ void __launch_bounds__(kThreads) sweep_kernel(const SoftmaxParams prm
                 g[int64_t(j) * prm.M] = from_f32<T>(fin.grad(to_f32(x[int64_t(j) * prm.M]), j == lb, prm.k) * pscale);
         }
     }
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
 
@@ -830,7 +831,7 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
         acc_loss += double(acc32);
         acc_cnt += double(cnt32);
     }
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
 // ---------------------------------------------------- many channels, forward: chunked sweep
@@ -1054,7 +1055,7 @@ tile_chunk_fwd_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorM
         acc_loss += double(acc32);
         acc_cnt += double(cnt32);
     }
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
 // ---------------------------------------------- many channels, backward from saved statistics
@@ -1533,7 +1534,7 @@ rows_pipe_kernel(const SoftmaxParams prm) {
         acc_loss = sh_acc[0];
         acc_cnt = sh_acc[1];
     }
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
 // -------------------------------------------------------------------- dispatch
@@ -1724,7 +1725,7 @@ rows_warp_fwd_kernel(const SoftmaxParams prm) {
             }
         }
     }
-    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red);
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
 // Integer tuning override from the environment (tile size, ring depth, blocks per SM);
@@ -2073,7 +2074,7 @@ inline bool fused_step_eligible(size_t es, const void *logits, const void *grads
 template <int KIND>
 int fused_step(const char *who, const void *logits, const int64_t *labels, void *grad_logits, void *out,
                void *workspace, size_t workspace_bytes, const void *denom, int64_t N, int64_t C, int64_t M,
-               int dtype, int64_t ignore_index, float hp, void *stream) {
+               int dtype, int64_t ignore_index, float hp, int defer, void *stream) {
     int rc = check_shape(who, N, C, M);
     if (rc != B200_OK) return rc;
     if (!out || !workspace || workspace_bytes < kReduceWorkspaceBytes) {
@@ -2101,6 +2102,7 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
     prm.M = M;
     prm.ignore = ignore_index;
     prm.k = make_consts(KIND, C, hp);
+    prm.defer = defer;
     return dispatch<KIND, true>(prm, dtype, true, static_cast<cudaStream_t>(stream));
 }
 
@@ -2170,18 +2172,18 @@ extern "C" int b200_softmax_fused_step_path(const void *logits, const int64_t *l
 extern "C" int b200_lsr_forward_backward_reduced(const void *logits, const int64_t *labels, void *grad_logits,
                                                  void *out, void *workspace, size_t workspace_bytes,
                                                  const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
-                                                 int64_t ignore_index, float smooth, void *stream) {
+                                                 int64_t ignore_index, float smooth, int defer, void *stream) {
     return fused_step<kLSR>("b200_lsr_forward_backward_reduced", logits, labels, grad_logits, out, workspace,
-                            workspace_bytes, denom, N, C, M, dtype, ignore_index, smooth, stream);
+                            workspace_bytes, denom, N, C, M, dtype, ignore_index, smooth, defer, stream);
 }
 
 // The same for the large-margin softmax loss.
 extern "C" int b200_lmargin_forward_backward_reduced(const void *logits, const int64_t *labels, void *grad_logits,
                                                      void *out, void *workspace, size_t workspace_bytes,
                                                      const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
-                                                     int64_t ignore_index, float lam, void *stream) {
+                                                     int64_t ignore_index, float lam, int defer, void *stream) {
     return fused_step<kLMargin>("b200_lmargin_forward_backward_reduced", logits, labels, grad_logits, out, workspace,
-                           workspace_bytes, denom, N, C, M, dtype, ignore_index, lam, stream);
+                           workspace_bytes, denom, N, C, M, dtype, ignore_index, lam, defer, stream);
 }
 
 extern "C" int b200_lsr_forward(const void *logits, const int64_t *labels, void *losses, void *out,

@@ -14,7 +14,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200loss.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 F32, F16 = 0, 1
 
 _c = ctypes
@@ -37,14 +37,16 @@ SIGNATURES = {
     "b200_focal_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _int, _f32, _f32, _vp]),
     "b200_focal_backward": (_int, [_vp, _vp, _vp, _int, _vp, _vp, _i64, _int, _f32, _f32, _vp]),
     "b200_focal_forward_backward": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _f32, _f32, _vp]),
-    "b200_focal_forward_backward_reduced": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _f32, _i64, _int, _f32, _f32, _vp]),
-    "b200_focal_forward_backward_predicted": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _i64, _int, _f32, _f32, _vp]),
+    "b200_focal_forward_backward_reduced": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _f32, _i64, _int, _f32, _f32, _int, _vp]),
+    "b200_focal_forward_backward_predicted": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _i64, _int, _f32, _f32, _int, _vp]),
     "b200_rescale_gradient": (_int, [_vp, _vp, _vp, _i64, _int, _vp]),
+    "b200_rescale_gradient_finish": (_int, [_vp, _vp, _vp, _i64, _int, _vp, _vp, _vp, _vp]),
+    "b200_exchange_finish": (_int, [_vp, _vp, _vp, _vp, _vp]),
     "b200_exchange_count": (_int, [_f64, _vp, _vp, _sz, _vp]),
     "b200_softmax_fused_step_path": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int]),
     "b200_count_valid": (_int, [_vp, _i64, _i64, _vp, _vp, _sz, _vp]),
-    "b200_lsr_forward_backward_reduced": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
-    "b200_lmargin_forward_backward_reduced": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
+    "b200_lsr_forward_backward_reduced": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _f32, _int, _vp]),
+    "b200_lmargin_forward_backward_reduced": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _f32, _int, _vp]),
     "b200_focal_forward_noalloc": (_int, [_vp, _vp, _vp, _vp, _i64, _int, _f32, _f32, _vp]),
     "b200_lsr_forward": (_int, [_vp, _vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _int, _i64, _f32, _vp]),
     "b200_lsr_backward": (_int, [_vp, _vp, _vp, _int, _vp, _vp, _i64, _i64, _i64, _int, _i64, _f32, _vp]),

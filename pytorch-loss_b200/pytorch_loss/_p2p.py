@@ -47,9 +47,36 @@ class Exchange:
         assert len(blob) == int(lib.b200_exchange_ctx_bytes())
         self.ctx = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(device)
         self._workspaces = {}
+        # a loss sum that a fused step has posted to the peers but nobody has collected yet:
+        # (record, workspace, denom_state or None, correction or None)
+        self.pending = None
+
+    def defer(self, record, workspace, denom_state=None, correction=None):
+        self.pending = (record, workspace, denom_state, correction)
+
+    def take_pending(self, record):
+        """The pending entry if it belongs to `record` (then it is cleared), else None."""
+        p = self.pending
+        if p is not None and p[0] is record:
+            self.pending = None
+            return p
+        return None
+
+    def finish_pending(self):
+        """Completes a deferred record now (one small kernel): before the next exchange of this
+        context, or when the loss is read ahead of backward."""
+        p, self.pending = self.pending, None
+        if p is None:
+            return
+        rec, ws, state, corr = p
+        with torch.cuda.device(self.device):
+            _cabi.check(_cabi.load_library().b200_exchange_finish(
+                _cabi.ptr(ws), _cabi.ptr(rec), _cabi.ptr(state), _cabi.ptr(corr), _cabi.stream_ptr(self.device)))
 
     def workspace(self):
-        """The reduction workspace of the current stream with this context attached."""
+        """The reduction workspace of the current stream with this context attached.  Asking for
+        it announces a new exchange: a deferred one is completed first."""
+        self.finish_pending()
         stream = torch.cuda.current_stream(self.device)
         ws = self._workspaces.get(stream.cuda_stream)
         if ws is None:
@@ -60,6 +87,39 @@ class Exchange:
                                                             _cabi.stream_ptr(self.device)))
             self._workspaces[stream.cuda_stream] = ws
         return ws
+
+
+class DeferredLoss(torch.Tensor):
+    """The loss a sharded fused step returns while its cross-GPU sum is still in flight: the step's
+    kernel has posted this rank's sums and left; backward's first kernel collects the peers' (so
+    the wait overlaps the launch in between).  Anything that reads the VALUE before backward --
+    `.item()`, `float()`, printing, arithmetic -- first completes the record with one small
+    kernel; `backward()` and attribute reads (shape, dtype, grad_fn) do not.  Results of
+    operations on it are plain tensors."""
+
+    @staticmethod
+    def wrap(tensor, exchange):
+        out = tensor.as_subclass(DeferredLoss)
+        out._b200_exchange = exchange
+        return out
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        reads_value = func is not torch.Tensor.backward and getattr(func, "__name__", "") != "__get__"
+        if reads_value:
+            from torch.utils._pytree import tree_leaves
+            for a in tree_leaves((args, kwargs)):
+                ex = getattr(a, "_b200_exchange", None) if isinstance(a, DeferredLoss) else None
+                if ex is not None:
+                    ex.finish_pending()
+        with torch._C.DisableTorchFunctionSubclass():
+            return func(*args, **kwargs)
+
+
+def defer_enabled():
+    """B200_LOSS_DEFER=0 keeps the wait for the peers' sums inside the step's own kernel."""
+    return os.environ.get("B200_LOSS_DEFER", "1") != "0"
 
 
 def local_exchange_for_tests(device, world, rank, poll_limit):
@@ -134,3 +194,13 @@ def get_exchange(group, device):
         if key not in _contexts:
             _contexts[key] = _build(group, device)
         return _contexts[key]
+
+
+def wrap_if_deferred(loss, group, like):
+    """`loss` as a DeferredLoss when the step that produced it left its cross-GPU sum pending."""
+    if not like.is_cuda or not _sharding.group_is_active(group):
+        return loss
+    ex = get_exchange(group, like.device)
+    if ex is not None and ex.pending is not None:
+        return DeferredLoss.wrap(loss, ex)
+    return loss

@@ -134,10 +134,16 @@ def fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange, denom=
     st = _cabi.stream_ptr(dev)
     if mean and denom is None:
         denom = count_valid(labels, ignore_index, exchange)
+    # across GPUs the kernel only posts its sums; backward's rescale kernel collects the peers'
+    # (or whatever reads the loss first, see _p2p.DeferredLoss)
+    defer = 1 if (exchange is not None and _p2p.defer_enabled()) else 0
     with torch.cuda.device(dev):
         _cabi.check(getattr(lib, _ENTRY_FUSED[kind])(
             _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
-            None if not mean else _cabi._vp(denom.data_ptr()), n, c, m, dt, int(ignore_index), float(hyper), st))
+            None if not mean else _cabi._vp(denom.data_ptr()), n, c, m, dt, int(ignore_index), float(hyper),
+            defer, st))
+    if defer:
+        exchange.defer(rec, ws)
     return rec, grads, logits, labels
 
 
@@ -154,6 +160,7 @@ class ReducedLossFunc(torch.autograd.Function):
     def forward(ctx, logits, labels, kind, hyper, ignore_index, mean, group):
         exchange = _p2p.get_exchange(group, logits.device) if logits.is_cuda else None
         ctx.fused = None
+        ctx.deferred = None
         nccl_group = exchange is None and _sharding.group_is_active(group)
         denom = None
         if exchange is not None and mean:
@@ -169,6 +176,7 @@ class ReducedLossFunc(torch.autograd.Function):
             if step is not None:
                 rec, grads, logits, labels = step
                 ctx.fused = grads
+                ctx.deferred = (exchange, rec) if (exchange is not None and exchange.pending is not None) else None
                 ctx.variables = (logits, labels, kind, hyper, ignore_index,
                                  (rec[:4].view(torch.float64)[1:] if mean else None), None)
                 return rec[4] if mean else rec[5]
@@ -191,10 +199,21 @@ class ReducedLossFunc(torch.autograd.Function):
             # first trip through the graph: the gradient is there, times the upstream gradient
             grads, ctx.fused = ctx.fused, None
             g = grad_output.to(torch.float32).reshape(-1)[:1].contiguous()
+            lib = _cabi.load_library()
+            pending = ctx.deferred[0].take_pending(ctx.deferred[1]) if ctx.deferred else None
             with torch.cuda.device(logits.device):
-                _cabi.check(_cabi.load_library().b200_rescale_gradient(
-                    _cabi.ptr(grads), _cabi.ptr(g), None, grads.numel(), _cabi.dtype_code(grads),
-                    _cabi.stream_ptr(logits.device)))
+                if pending is not None:
+                    rec, ws, _, _ = pending
+                    _cabi.check(lib.b200_rescale_gradient_finish(
+                        _cabi.ptr(grads), _cabi.ptr(g), None, grads.numel(), _cabi.dtype_code(grads),
+                        _cabi.ptr(ws), _cabi.ptr(rec), None, _cabi.stream_ptr(logits.device)))
+                else:
+                    _cabi.check(lib.b200_rescale_gradient(
+                        _cabi.ptr(grads), _cabi.ptr(g), None, grads.numel(), _cabi.dtype_code(grads),
+                        _cabi.stream_ptr(logits.device)))
             return grads, None, None, None, None, None, None
         grads = backward(kind, logits, labels, grad_output, denom, ignore_index, hyper, stats)
         return grads, None, None, None, None, None, None
+
+
+wrap_if_deferred = _p2p.wrap_if_deferred

@@ -143,15 +143,22 @@ class _FocalReducedFunc(torch.autograd.Function):
                     correction = torch.empty(1, dtype=torch.float32, device=dev)
             elif mean:
                 scale = 1.0 / max(n, 1)
+            # across GPUs the kernel only posts its sums; backward's rescale kernel collects the
+            # peers' (or whatever reads the loss first, see _p2p.DeferredLoss)
+            defer = 1 if (exchange is not None and _p2p.defer_enabled()) else 0
             if correction is not None:
                 _cabi.check(lib.b200_focal_forward_backward_predicted(
                     _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws),
-                    ws.numel(), _cabi.ptr(predicted), _cabi.ptr(correction), n, dt, float(gamma), float(alpha), st))
+                    ws.numel(), _cabi.ptr(predicted), _cabi.ptr(correction), n, dt, float(gamma), float(alpha),
+                    defer, st))
             else:
                 _cabi.check(lib.b200_focal_forward_backward_reduced(
                     _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
                     None if denom is None else _cabi._vp(denom.data_ptr()), float(scale), n, dt, float(gamma),
-                    float(alpha), st))
+                    float(alpha), defer, st))
+            if defer:
+                exchange.defer(rec, ws, predicted if correction is not None else None, correction)
+        ctx.deferred = (exchange, rec) if defer else None
         ctx.fused = [grads, correction]      # handed out by the first backward
         ctx.variables = logits, labels, alpha, gamma, (rec[:4].view(torch.float64)[1:] if mean else None)
         return rec[4] if mean else rec[5]
@@ -162,6 +169,7 @@ class _FocalReducedFunc(torch.autograd.Function):
         dev, logits, labels, dt = _prep(logits, labels)
         lib = _cabi.load_library()
         ctx.fused = None
+        ctx.deferred = None
         nccl_group = _sharding.group_is_active(group) and _p2p.get_exchange(group, dev) is None
         if ctx.needs_input_grad[0] and logits.numel() > 0 and not nccl_group and \
                 os.environ.get("B200_FOCAL_FUSED", "1") != "0":
@@ -190,10 +198,18 @@ class _FocalReducedFunc(torch.autograd.Function):
             grads, correction = ctx.fused
             ctx.fused = None
             g = grad_output.to(torch.float32).reshape(-1)[:1].contiguous()
+            lib = _cabi.load_library()
+            pending = ctx.deferred[0].take_pending(ctx.deferred[1]) if ctx.deferred else None
             with torch.cuda.device(logits.device):
-                _cabi.check(_cabi.load_library().b200_rescale_gradient(
-                    _cabi.ptr(grads), _cabi.ptr(g), _cabi.ptr(correction), grads.numel(), _cabi.dtype_code(grads),
-                    _cabi.stream_ptr(logits.device)))
+                if pending is not None:
+                    rec, ws, state, _ = pending
+                    _cabi.check(lib.b200_rescale_gradient_finish(
+                        _cabi.ptr(grads), _cabi.ptr(g), _cabi.ptr(correction), grads.numel(), _cabi.dtype_code(grads),
+                        _cabi.ptr(ws), _cabi.ptr(rec), _cabi.ptr(state), _cabi.stream_ptr(logits.device)))
+                else:
+                    _cabi.check(lib.b200_rescale_gradient(
+                        _cabi.ptr(grads), _cabi.ptr(g), _cabi.ptr(correction), grads.numel(), _cabi.dtype_code(grads),
+                        _cabi.stream_ptr(logits.device)))
             return grads, None, None, None, None, None, None
         grads = _focal_backward(logits, labels, grad_output, denom, alpha, gamma)
         return grads, None, None, None, None, None, None
@@ -222,6 +238,7 @@ class FocalLossV3(nn.Module):
 
     def forward(self, logits, label):
         if self.reduction == 'mean' or self.reduction == 'sum':
-            return _FocalReducedFunc.apply(logits, label, self.alpha, self.gamma,
+            loss = _FocalReducedFunc.apply(logits, label, self.alpha, self.gamma,
                                            self.reduction == 'mean', self.process_group, self._count_state)
+            return _p2p.wrap_if_deferred(loss, self.process_group, logits)
         return FocalSigmoidLossFuncV3.apply(logits, label, self.alpha, self.gamma)

@@ -56,6 +56,7 @@ class LabelSmoothSoftmaxCEV3(nn.Module):
 
     def forward(self, logits, labels):
         if self.reduction == 'mean' or self.reduction == 'sum':
-            return _sf.ReducedLossFunc.apply(logits, labels, "lsr", self.lb_smooth, self.lb_ignore,
+            loss = _sf.ReducedLossFunc.apply(logits, labels, "lsr", self.lb_smooth, self.lb_ignore,
                                              self.reduction == 'mean', self.process_group)
+            return _sf.wrap_if_deferred(loss, self.process_group, logits)
         return LSRCrossEntropyFunctionV3.apply(logits, labels, self.lb_smooth, self.lb_ignore)

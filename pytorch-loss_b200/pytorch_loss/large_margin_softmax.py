@@ -76,6 +76,7 @@ class LargeMarginSoftmaxV3(nn.Module):
 
     def forward(self, logits, labels):
         if self.reduction == 'mean' or self.reduction == 'sum':
-            return _sf.ReducedLossFunc.apply(logits, labels, "lmargin", self.lam, self.ignore_index,
+            loss = _sf.ReducedLossFunc.apply(logits, labels, "lmargin", self.lam, self.ignore_index,
                                              self.reduction == 'mean', self.process_group)
+            return _sf.wrap_if_deferred(loss, self.process_group, logits)
         return LargeMarginSoftmaxFuncV3.apply(logits, labels, self.lam, self.ignore_index)

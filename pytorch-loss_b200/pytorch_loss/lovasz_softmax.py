@@ -117,8 +117,9 @@ class LovaszSoftmaxV3(nn.Module):
         if self.reduction not in ('sum', 'mean'):
             return losses
         if _sharding.group_is_active(self.process_group):
+            # (the count is made on the device: a host tensor could not be copied during graph capture)
             pair = torch.stack([losses.sum().double(),
-                                torch.tensor(float(losses.numel()), dtype=torch.float64, device=losses.device)])
+                                torch.full((), float(losses.numel()), dtype=torch.float64, device=losses.device)])
             pair = _AllReduceSumCount.apply(pair, self.process_group)
             return (pair[0] / pair[1] if self.reduction == 'mean' else pair[0]).float()
         return losses.sum() if self.reduction == 'sum' else losses.mean()

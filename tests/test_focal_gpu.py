@@ -241,7 +241,7 @@ def test_two_emulated_ranks_exchange_the_label_count():
     ws = ranks[0].workspace()
     _cabi.check(lib.b200_lsr_forward_backward_reduced(
         _cabi.ptr(xs[0]), _cabi.ptr(ys[0]), _cabi.ptr(grad), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
-        _cabi._vp(cnts[0].data_ptr() + 8), 2, 19, 32 * 32, _cabi.F32, 255, 0.1, st))
+        _cabi._vp(cnts[0].data_ptr() + 8), 2, 19, 32 * 32, _cabi.F32, 255, 0.1, 0, st))
     torch.cuda.synchronize()
     assert_grad_close(grad, want_grad[:2])
     assert lib.b200_read_status(_cabi.ptr(ws), st) == 4 and b"0x100" in lib.b200_last_error()
@@ -274,7 +274,7 @@ def test_focal_predicted_count_correction():
         corr = torch.zeros(1, dtype=torch.float32, device=dev)
         _cabi.check(lib.b200_focal_forward_backward_predicted(
             _cabi.ptr(x), _cabi.ptr(y), _cabi.ptr(grad), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
-            _cabi.ptr(state), _cabi.ptr(corr), x.numel(), _cabi.F32, 2.0, 0.25, st))
+            _cabi.ptr(state), _cabi.ptr(corr), x.numel(), _cabi.F32, 2.0, 0.25, 0, st))
         one = torch.ones(1, dtype=torch.float32, device=dev)
         _cabi.check(lib.b200_rescale_gradient(_cabi.ptr(grad), _cabi.ptr(one), _cabi.ptr(corr), x.numel(),
                                               _cabi.F32, st))
@@ -282,4 +282,44 @@ def test_focal_predicted_count_correction():
         assert abs(float(corr) - predicted / x.numel()) <= 1e-6 * predicted / x.numel()
         assert float(state) == x.numel()
         assert_grad_close(grad, want_grad, atol=1e-7)
+    _cabi.check(lib.b200_read_status(_cabi.ptr(ws), st))
+
+
+def test_deferred_sum_is_completed_by_the_rescale_kernel():
+    """`defer`: the fused step posts its sums and leaves the record incomplete (NaN mean, no
+    correction); the rescale kernel that follows collects them, completes the record, writes the
+    correction and rescales with it.  A world of one rank, batch size changing between calls.
+    Also the stand-alone completion (loss read without backward), which may be called twice."""
+    from pytorch_loss import _cabi, _p2p
+    from oracle import losses as O
+    dev = torch.device("cuda", 0)
+    lib = _cabi.load_library()
+    st = _cabi.stream_ptr(dev)
+    ex = _p2p.local_exchange_for_tests(dev, 1, 0, 1000)
+    ws = ex.workspace()
+    g = torch.Generator().manual_seed(93)
+    state = torch.tensor([2.0 * 5 * 77], dtype=torch.float64, device=dev)
+    for i, shape in enumerate(((3, 5, 77), (3, 5, 77), (2, 5, 77))):
+        logits = torch.randn(shape, generator=g) * 2
+        labels = (torch.rand(shape, generator=g) < 0.3).float()
+        want_loss, want_grad = O.focal_loss(logits, labels, 0.25, 2.0, 'mean')
+        x, y = logits.to(dev), labels.to(dev)
+        grad = torch.empty_like(x)
+        rec = _cabi.new_record(dev)
+        corr = torch.full((1,), float("nan"), dtype=torch.float32, device=dev)
+        _cabi.check(lib.b200_focal_forward_backward_predicted(
+            _cabi.ptr(x), _cabi.ptr(y), _cabi.ptr(grad), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
+            _cabi.ptr(state), _cabi.ptr(corr), x.numel(), _cabi.F32, 2.0, 0.25, 1, st))
+        torch.cuda.synchronize()
+        assert bool(torch.isnan(rec[4])) and bool(torch.isnan(corr[0]))           # posted, not collected
+        up = torch.full((1,), 2.0, dtype=torch.float32, device=dev)
+        if i == 2:                       # the loss is read first: stand-alone completion, twice
+            for _ in range(2):
+                _cabi.check(lib.b200_exchange_finish(_cabi.ptr(ws), _cabi.ptr(rec), _cabi.ptr(state), _cabi.ptr(corr), st))
+            assert_loss_close(rec[4], want_loss)
+        _cabi.check(lib.b200_rescale_gradient_finish(_cabi.ptr(grad), _cabi.ptr(up), _cabi.ptr(corr), x.numel(),
+                                                     _cabi.F32, _cabi.ptr(ws), _cabi.ptr(rec), _cabi.ptr(state), st))
+        assert_loss_close(rec[4], want_loss)
+        assert float(rec[:4].view(torch.float64)[1]) == x.numel() == float(state)
+        assert_grad_close(grad, 2.0 * want_grad, atol=1e-7)
     _cabi.check(lib.b200_read_status(_cabi.ptr(ws), st))

@@ -77,6 +77,21 @@ def _worker(rank, world, port, out, p2p):
         want_loss, want_grad = cases[2][2]
         errs.append((abs(float(loss) - float(want_loss)) / abs(float(want_loss)),
                      float((x.grad.cpu() - want_grad[a:b]).abs().max())))
+    # A sharded fused step leaves its cross-GPU sum in flight for backward to collect; the loss it
+    # returns completes itself when it is read first.  Both orders, for all three losses.
+    from pytorch_loss import _p2p as P2P
+    for crit, lab, (want_loss, want_grad) in cases[:3]:
+        for read_first in (True, False):
+            x = logits[lo:hi].to(dev).requires_grad_(True)
+            loss = crit(x, lab[lo:hi].to(dev))
+            if p2p:
+                assert isinstance(loss, P2P.DeferredLoss), type(loss)
+            early = float(loss) if read_first else float(want_loss)
+            loss.backward()
+            errs.append((abs(early - float(want_loss)) / abs(float(want_loss)), 0.0))
+            errs.append((abs(float(loss) - float(want_loss)) / abs(float(want_loss)),
+                         float((x.grad.cpu() - want_grad[lo:hi]).abs().max())))
+            assert type(loss * 2.0) is torch.Tensor
     from pytorch_loss import _cabi, _p2p
     _cabi.read_status(dev)
     for ex in _p2p._contexts.values():
