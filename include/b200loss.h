@@ -358,6 +358,19 @@ int b200_taylor_softmax_backward(const void *grad, const void *feat, void *grad_
                                  int64_t C, int64_t M, int dtype, int n, int use_log,
                                  void *stream);
 
+/* -------------------------------------------------- PC softmax cross entropy ---
+ * Replaces the tensor-op chain of PCSoftmaxCrossEntropyV1 / PCSoftmaxCrossEntropyFunction
+ * (reference pc_softmax.py:35-49, :52-97; the reference has no native kernel for it): with class
+ * proportions weight[C] (device floats),
+ *   losses[n, m]     = -(x_lb - max - log sum_j weight_j e^{x_j - max}), 0 at ignored pixels
+ *   grad_logits[n,j,m] = weight_j e^{x_j - max} / sum_k weight_k e^{x_k - max} - 1[j == lb], 0 at
+ *                        ignored pixels (the derivative of the loss above; the reference's V2
+ *                        backward, pc_softmax.py:104-106, scales every channel by weight_lb instead)
+ * in ONE launch; either output may be NULL.  Reduction and upstream gradient are the caller's. */
+int b200_pc_softmax_ce(const void *logits, const int64_t *labels, const float *weight, void *losses,
+                       void *grad_logits, int64_t N, int64_t C, int64_t M, int dtype,
+                       int64_t ignore_index, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

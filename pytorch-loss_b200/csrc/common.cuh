@@ -410,6 +410,34 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
         "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
         : "memory");
 }
+// The same with an L2 eviction policy for the lines the copy touches (createpolicy): a tile that
+// is read again soon is loaded evict_last, its last read and the stores next to it evict_first,
+// so the streams around it do not push it out of the L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void tma_load_3d_hint(void *dst, const CUtensorMap *map, int x, int y, int z,
+                                                 uint64_t *bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(smem_u32(dst)),
+        "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_3d_hint(const CUtensorMap *map, int x, int y, int z, const void *src,
+                                                  uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%1, %2, %3}], [%4], %5;" ::"l"(map),
+        "r"(x), "r"(y), "r"(z), "r"(smem_u32(src)), "l"(policy)
+        : "memory");
+}
 // Tiled stores shared -> global (bulk-group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map),

@@ -20,7 +20,7 @@ namespace b200 {
 // block, whatever the other blocks on the SM are doing.  Every wait is bounded; a wait that runs
 // out sets the status word and the block leaves its loop.
 
-constexpr int kMaxStages = 4;
+constexpr int kMaxStages = 6;
 
 struct PipeBarriers {
     uint64_t full[kMaxStages];

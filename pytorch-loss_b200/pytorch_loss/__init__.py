@@ -27,3 +27,6 @@ from .taylor_softmax import (TaylorSoftmaxV3, LogTaylorSoftmaxV3, TaylorCrossEnt
 
 __all__ += ["TaylorSoftmaxV3", "LogTaylorSoftmaxV3", "TaylorCrossEntropyLossV3", "TaylorSoftmaxFunc",
             "taylor_softmax_v3"]
+from .pc_softmax import PCSoftmaxCrossEntropyV2, PCSoftmaxCrossEntropyFunction
+
+__all__ += ["PCSoftmaxCrossEntropyV2", "PCSoftmaxCrossEntropyFunction"]

@@ -47,6 +47,7 @@ def load_reference(root):
         "lm_v2": load("large_margin_softmax.py", "ref_large_margin_root"),
         "lovasz": load("lovasz_softmax.py", "ref_lovasz"),
         "taylor": load("pytorch_loss/taylor_softmax.py", "ref_taylor_softmax"),
+        "pc": load("pc_softmax.py", "ref_pc_softmax"),
     }
 
 
@@ -171,6 +172,36 @@ def main():
                   f"ce{i}_loss": l1, f"ce{i}_grad": g1})
     d["n_ce_cases"] = np.array(len(ce_cases))
     out["taylor"] = d
+
+    # ---- PC softmax cross entropy: V1 (loss and its autograd gradient) and V2 (its loss; V2's own
+    # hand-written backward, which scales by the label's proportion, is stored for the record).
+    # V1's constructor moves the proportions with `.cuda()`; on this CPU-only run that one call is
+    # made a no-op while the object is built (the reference's code is not touched).
+    cases = [((2, 5, 6, 7), 255, 0.2, 'mean'), ((3, 19, 4, 4), 255, 0.0, 'sum'), ((6, 7), -100, 0.0, 'mean'),
+             ((2, 4, 5, 3), 255, 0.3, 'none')]
+    d = {}
+    for i, (shape, ign, frac, red) in enumerate(cases):
+        g = torch.Generator().manual_seed(600 + i)
+        logits = torch.randn(shape, generator=g) * 2.0
+        labels = labels_with_ignores(g, (shape[0],) + shape[2:], shape[1], ign, frac)
+        prop = torch.rand(shape[1], generator=g) + 0.05
+        prop = (prop / prop.sum()).tolist()
+        real_cuda = torch.Tensor.cuda
+        torch.Tensor.cuda = lambda self, *a, **k: self
+        try:
+            crit1 = ref["pc"].PCSoftmaxCrossEntropyV1(prop, ignore_index=ign, reduction=red)
+        finally:
+            torch.Tensor.cuda = real_cuda
+        l1, g1 = run(crit1, logits, labels)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            l2, g2 = run(ref["pc"].PCSoftmaxCrossEntropyV2(prop, red, ign), logits, labels)
+        d.update({f"c{i}_logits": logits.numpy(), f"c{i}_labels": labels.numpy(),
+                  f"c{i}_proportion": np.array(prop, dtype=np.float64),
+                  f"c{i}_hyper": np.array([ign], dtype=np.float64), f"c{i}_reduction": np.array(red),
+                  f"c{i}_loss_v1": l1, f"c{i}_grad_v1": g1, f"c{i}_loss_v2": l2, f"c{i}_grad_v2_as_written": g2})
+    d["n_cases"] = np.array(len(cases))
+    out["pc_softmax"] = d
 
     only = os.environ.get("GOLDEN_ONLY")               # e.g. GOLDEN_ONLY=taylor rewrites one file
     for name, d in out.items():

@@ -122,3 +122,17 @@ def test_ohem_oracle_matches_reference_cuda_output(golden_dir):
         want = torch.from_numpy(z[f"c{i}_new_labels"])
         got, _ = OH.score_ohem_label(logits, labels, int(ign), float(thresh), int(n_min))
         assert torch.equal(got, want), "case %d: %d labels differ" % (i, int((got != want).sum()))
+
+
+def test_pc_softmax_oracle_matches_reference(golden_dir):
+    """oracle/pc_softmax.py against PCSoftmaxCrossEntropyV1 (loss, autograd gradient) and the
+    loss of PCSoftmaxCrossEntropyV2, as make_golden.py recorded them from the reference."""
+    from oracle import pc_softmax as PC
+    z = np.load(os.path.join(golden_dir, "pc_softmax.npz"))
+    for i in range(int(z["n_cases"])):
+        x, y = torch.from_numpy(z[f"c{i}_logits"]), torch.from_numpy(z[f"c{i}_labels"])
+        red, ign = str(z[f"c{i}_reduction"]), int(z[f"c{i}_hyper"][0])
+        loss, grad = PC.pc_softmax_ce(x, y, z[f"c{i}_proportion"], ign, red)
+        for ref in (z[f"c{i}_loss_v1"], z[f"c{i}_loss_v2"]):
+            np.testing.assert_allclose(loss.numpy(), ref, rtol=RTOL, atol=ATOL)
+        np.testing.assert_allclose(grad.numpy(), z[f"c{i}_grad_v1"], rtol=RTOL, atol=ATOL)

@@ -1,0 +1,67 @@
+"""PCSoftmaxCrossEntropyV2 (CUDA, through the C ABI) against the CPU oracle and the golden file
+recorded from the reference's V1 class."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_grad_close, assert_loss_close, labels_with_ignores, run_module, TOL_F16
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(2, 5, (6, 7)), (3, 19, (16, 20)), (2, 19, (33, 35)), (1, 150, (12, 16)), (7, 10, ()), (3, 1000, ()),
+          (2, 4, (5,)), (4, 19, (128, 128))]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, (s[0], s[1]) + s[2])))
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none"])
+def test_matches_oracle(shape, reduction):
+    import pytorch_loss as P
+    from oracle import pc_softmax as PC
+    n, c, sp = shape
+    g = torch.Generator().manual_seed(700 + c + len(sp))
+    logits = torch.randn((n, c) + sp, generator=g) * 2.0
+    labels = labels_with_ignores(g, (n,) + sp, c, 255, 0.15)
+    prop = torch.rand(c, generator=g) + 0.05
+    prop = (prop / prop.sum()).tolist()
+    want_loss, want_grad = PC.pc_softmax_ce(logits, labels, prop, 255, reduction)
+    loss, grad = run_module(P.PCSoftmaxCrossEntropyV2(prop, reduction, 255), logits.cuda(), labels.cuda())
+    assert_loss_close(loss, want_loss, atol=2e-6 if reduction == "none" else 1e-7)
+    assert_grad_close(grad, want_grad)
+    ign = labels == 255
+    assert bool((grad.cpu().transpose(0, 1)[:, ign] == 0).all())
+    if reduction == "none":
+        assert bool((loss.cpu()[ign] == 0).all())
+
+
+def test_golden(golden_dir):
+    import pytorch_loss as P
+    z = np.load(os.path.join(golden_dir, "pc_softmax.npz"))
+    for i in range(int(z["n_cases"])):
+        x, y = torch.from_numpy(z[f"c{i}_logits"]), torch.from_numpy(z[f"c{i}_labels"])
+        red, ign = str(z[f"c{i}_reduction"]), int(z[f"c{i}_hyper"][0])
+        crit = P.PCSoftmaxCrossEntropyV2(z[f"c{i}_proportion"].tolist(), red, ign)
+        loss, grad = run_module(crit, x.cuda(), y.cuda())
+        assert_loss_close(loss, torch.from_numpy(z[f"c{i}_loss_v1"]), atol=2e-6, what=f"c{i} loss")
+        assert_grad_close(grad, torch.from_numpy(z[f"c{i}_grad_v1"]), what=f"c{i} grad")
+
+
+def test_fp16_per_pixel_upstream_gradient_and_errors():
+    import pytorch_loss as P
+    from oracle import pc_softmax as PC
+    g = torch.Generator().manual_seed(710)
+    logits = (torch.randn(2, 6, 9, 8, generator=g) * 2).half()
+    labels = labels_with_ignores(g, (2, 9, 8), 6, 255, 0.1)
+    prop = [0.3, 0.1, 0.2, 0.15, 0.05, 0.2]
+    want_loss, want_grad = PC.pc_softmax_ce(logits.float(), labels, prop, 255, 'none')
+    up = torch.randn(2, 9, 8, generator=g)
+    x = logits.cuda().requires_grad_(True)
+    loss = P.PCSoftmaxCrossEntropyFunction.apply(x, labels.cuda(), prop, 'none', 255)
+    loss.backward(up.cuda().half())
+    assert_loss_close(loss.float(), want_loss, rtol=TOL_F16, atol=TOL_F16)
+    assert_grad_close(x.grad.float(), want_grad * up.unsqueeze(1), atol=4 * TOL_F16, rtol=4 * TOL_F16)
+    with pytest.raises(RuntimeError):
+        P.PCSoftmaxCrossEntropyV2([0.5, 0.5])(torch.randn(2, 3, 4, 4).cuda(), torch.zeros(2, 4, 4, dtype=torch.int64).cuda())
+    with pytest.raises(RuntimeError):
+        P.PCSoftmaxCrossEntropyV2([0.5, 0.5])(torch.randn(2, 2, 4, 4), torch.zeros(2, 4, 4, dtype=torch.int64))
