@@ -14,7 +14,8 @@
  * [N, C, M] row-major with M = product of the trailing (spatial) dims, labels
  * are int64 [N, M] (focal: same dtype and shape as the logits).
  *
- * dtype codes: B200_F32 (float), B200_F16 (__half).  Arithmetic is always fp32.
+ * dtype codes: B200_F32 (float), B200_F16 (__half), B200_BF16 (__nv_bfloat16): the storage type of
+ * logits, per-pixel losses and gradients.  Arithmetic is always fp32.
  *
  * Reduction record ("out", 32 bytes, 8-byte aligned), written by the forward
  * kernels when `out` is non-NULL:
@@ -51,6 +52,7 @@ extern "C" {
 
 #define B200_F32 0
 #define B200_F16 1
+#define B200_BF16 2
 
 /* Version of this ABI (bumped on any signature change). */
 int b200_abi_version(void);

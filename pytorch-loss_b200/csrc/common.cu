@@ -88,6 +88,7 @@ bool encode_tensor_map(CUtensorMap *map, int dtype, const void *base, int rank,
     switch (dtype) {
         case B200_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
         case B200_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+        case B200_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
         default: dt = CU_TENSOR_MAP_DATA_TYPE_UINT32; break;   // raw 32-bit words
     }
     const CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void *>(base), gdim,

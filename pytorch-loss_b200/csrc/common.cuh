@@ -5,6 +5,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -86,11 +87,21 @@ template <> struct alignas(16) Vec16<__half> {
     __half v[8];
 };
 
+template <> struct alignas(16) Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __nv_bfloat16 v[8];
+};
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
 template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+// bytes of one element of a dtype code (B200_F32 / B200_F16 / B200_BF16)
+inline size_t dtype_size(int dtype) { return dtype == B200_F32 ? 4 : 2; }
+inline bool dtype_known(int dtype) { return dtype == B200_F32 || dtype == B200_F16 || dtype == B200_BF16; }
 
 // Streaming 16-byte global access (read-once data: keep it out of L1).
 template <typename V> __device__ __forceinline__ V ld_stream16(const void *p) {
@@ -408,34 +419,6 @@ __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, i
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(dst)),
         "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
-        : "memory");
-}
-// The same with an L2 eviction policy for the lines the copy touches (createpolicy): a tile that
-// is read again soon is loaded evict_last, its last read and the stores next to it evict_first,
-// so the streams around it do not push it out of the L2.
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ void tma_load_3d_hint(void *dst, const CUtensorMap *map, int x, int y, int z,
-                                                 uint64_t *bar, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
-        "[%0], [%1, {%2, %3, %4}], [%5], %6;" ::"r"(smem_u32(dst)),
-        "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)), "l"(policy)
-        : "memory");
-}
-__device__ __forceinline__ void tma_store_3d_hint(const CUtensorMap *map, int x, int y, int z, const void *src,
-                                                  uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%1, %2, %3}], [%4], %5;" ::"l"(map),
-        "r"(x), "r"(y), "r"(z), "r"(smem_u32(src)), "l"(policy)
         : "memory");
 }
 // Tiled stores shared -> global (bulk-group completion).

@@ -381,6 +381,7 @@ template <int MODE, bool REDUCE>
 int dispatch_focal(const FocalParams &prm, int dtype, cudaStream_t stream) {
     if (dtype == B200_F32) return launch_focal<float, MODE, REDUCE>(prm, stream);
     if (dtype == B200_F16) return launch_focal<__half, MODE, REDUCE>(prm, stream);
+    if (dtype == B200_BF16) return launch_focal<__nv_bfloat16, MODE, REDUCE>(prm, stream);
     set_error("focal: unknown dtype code %d", dtype);
     return B200_ERR_ARG;
 }
@@ -637,6 +638,9 @@ int launch_rescale(void *grad, const float *grad_out, float *correction, int64_t
     else if (dtype == B200_F16)
         rescale_kernel<__half><<<unsigned(grid), kRescaleThreads, 0, s>>>(static_cast<__half *>(grad), grad_out,
                                                                           correction, E, workspace, rec, ds);
+    else if (dtype == B200_BF16)
+        rescale_kernel<__nv_bfloat16><<<unsigned(grid), kRescaleThreads, 0, s>>>(
+            static_cast<__nv_bfloat16 *>(grad), grad_out, correction, E, workspace, rec, ds);
     else {
         set_error("rescale: unknown dtype code %d", dtype);
         return B200_ERR_ARG;
@@ -779,7 +783,7 @@ extern "C" int b200_focal_forward_noalloc(const void *logits, const void *labels
         set_error("b200_focal_forward_noalloc: null input pointer");
         return B200_ERR_ARG;
     }
-    if (dtype != B200_F32 && dtype != B200_F16) {
+    if (!dtype_known(dtype)) {
         set_error("b200_focal_forward_noalloc: unknown dtype code %d", dtype);
         return B200_ERR_ARG;
     }
@@ -799,5 +803,6 @@ extern "C" int b200_focal_forward_noalloc(const void *logits, const void *labels
     prm.E = E;
     prm.gamma = gamma;
     prm.alpha = alpha;
+    if (dtype == B200_BF16) return launch_focal_noalloc<__nv_bfloat16>(prm, s);
     return dtype == B200_F32 ? launch_focal_noalloc<float>(prm, s) : launch_focal_noalloc<__half>(prm, s);
 }

@@ -303,7 +303,7 @@ extern "C" int b200_ohem_label(const void *logits, const int64_t *labels, int64_
         set_error("b200_ohem_label: bad shape N=%lld C=%lld M=%lld", (long long)N, (long long)C, (long long)M);
         return B200_ERR_ARG;
     }
-    if (dtype != B200_F32 && dtype != B200_F16) {
+    if (!dtype_known(dtype)) {
         set_error("b200_ohem_label: unknown dtype code %d", dtype);
         return B200_ERR_ARG;
     }
@@ -355,9 +355,12 @@ extern "C" int b200_ohem_label(const void *logits, const int64_t *labels, int64_
     else if (dtype == B200_F32)
         ohem_score_kernel<float, 1><<<unsigned(grid), kOhemThreads, 0, s>>>(
             static_cast<const float *>(logits), labels, w.scores, w.hist, w.state, N, Ci, M, ignore_index, k_first, thresh_bits);
-    else
+    else if (dtype == B200_F16)
         ohem_score_kernel<__half, 1><<<unsigned(grid), kOhemThreads, 0, s>>>(
             static_cast<const __half *>(logits), labels, w.scores, w.hist, w.state, N, Ci, M, ignore_index, k_first, thresh_bits);
+    else
+        ohem_score_kernel<__nv_bfloat16, 1><<<unsigned(grid), kOhemThreads, 0, s>>>(
+            static_cast<const __nv_bfloat16 *>(logits), labels, w.scores, w.hist, w.state, N, Ci, M, ignore_index, k_first, thresh_bits);
     if ((rc = launch_status("ohem score kernel launch")) != B200_OK) return rc;
     int64_t pgrid = (P + kOhemThreads - 1) / kOhemThreads;
     if (pgrid > cap) pgrid = cap;

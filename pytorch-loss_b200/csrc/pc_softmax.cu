@@ -191,6 +191,7 @@ extern "C" int b200_pc_softmax_ce(const void *logits, const int64_t *labels, con
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == B200_F32) return launch_pc<float>(p, s);
     if (dtype == B200_F16) return launch_pc<__half>(p, s);
+    if (dtype == B200_BF16) return launch_pc<__nv_bfloat16>(p, s);
     set_error("b200_pc_softmax_ce: unknown dtype code %d", dtype);
     return B200_ERR_ARG;
 }

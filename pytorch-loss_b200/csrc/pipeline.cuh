@@ -20,7 +20,7 @@ namespace b200 {
 // block, whatever the other blocks on the SM are doing.  Every wait is bounded; a wait that runs
 // out sets the status word and the block leaves its loop.
 
-constexpr int kMaxStages = 6;
+constexpr int kMaxStages = 4;
 
 struct PipeBarriers {
     uint64_t full[kMaxStages];
@@ -103,6 +103,12 @@ __device__ __forceinline__ void st_pair(float *p, float2 v) { *reinterpret_cast<
 __device__ __forceinline__ void st_pair(__half *p, float2 v) {
     *reinterpret_cast<__half2 *>(p) = __float22half2_rn(v);
 }
+__device__ __forceinline__ float2 ld_pair(const __nv_bfloat16 *p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+}
+__device__ __forceinline__ void st_pair(__nv_bfloat16 *p, float2 v) {
+    *reinterpret_cast<__nv_bfloat162 *>(p) = __float22bfloat162_rn(v);
+}
 
 // The same operations on values that STAY packed in one 64-bit register pair across a loop
 // (loads and stores move the pair as one 8-byte word; only the two ex2 need the halves).
@@ -136,8 +142,10 @@ __device__ __forceinline__ pk_t pex2(pk_t t) {
 __device__ __forceinline__ pk_t psplat(float v) { return pk2(make_float2(v, v)); }
 __device__ __forceinline__ pk_t ld_pk(const float *p) { return *reinterpret_cast<const pk_t *>(p); }
 __device__ __forceinline__ pk_t ld_pk(const __half *p) { return pk2(ld_pair(p)); }
+__device__ __forceinline__ pk_t ld_pk(const __nv_bfloat16 *p) { return pk2(ld_pair(p)); }
 __device__ __forceinline__ void st_pk(float *p, pk_t v) { *reinterpret_cast<pk_t *>(p) = v; }
 __device__ __forceinline__ void st_pk(__half *p, pk_t v) { st_pair(p, upk2(v)); }
+__device__ __forceinline__ void st_pk(__nv_bfloat16 *p, pk_t v) { st_pair(p, upk2(v)); }
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;

@@ -1230,286 +1230,13 @@ tile_chunk_bwd_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorM
     }
 }
 
-// ------------------------------------- many channels, fused training step: two chunked sweeps
-//
-// Loss sum and final gradient from ONE read of the logits from HBM, for class counts where the
-// resident tile of tile_pair_kernel has to be cut into channel slices (three block-wide
-// exchanges per tile).  A tile of 512 pixels streams through the ring twice, in the same
-// 16-channel chunks as the two kernels above:
-//   sweep 0  the forward's online statistics (a thread owns two pixels over all channels) and,
-//            from them, the per-pixel loss and the per-pixel coefficients of the gradient;
-//   sweep 1  the backward's pass: every gradient element from its own logit and those
-//            coefficients, in place, TMA store.
-// The statistics never leave the registers, and sweep 1 reads the tile while it is still in L2:
-// the bytes between the two reads of a chunk are one tile per resident block (C x 512 x 4 B =
-// 300 KB at 150 classes), so the launch keeps the resident blocks x tile bytes well inside the
-// L2 (see launch_regime).  DRAM traffic is then the logits once in, the gradient once out.
-// Barriers: the loader fills stage s when `empty[s]` completes; compute warps consume it and
-// arrive on `ready[s]` in BOTH sweeps; the storer warp waits for `ready[s]`, issues the TMA store
-// if the slot belongs to sweep 1, and arrives on `empty[s]` -- one arrival pattern for all slots.
-template <typename T, int KIND>
-__global__ void __launch_bounds__(kTileBlock, 2)
-tile_chunk_step_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap map_in,
-                       const __grid_constant__ CUtensorMap map_out) {
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ PipeBarriers bars;
-    __shared__ double sh_red[64];
-    const int C = static_cast<int>(prm.C), NS = prm.stages;
-    const ChunkLayout lay = chunk_layout<T>();
-    unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
-    const int tid = threadIdx.x;
-    unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
-    const int nchunks = (C + kChunkCh - 1) / kChunkCh;
-    const int64_t tiles_per_image = (prm.M + kChunkTile - 1) / kChunkTile;
-    const int64_t total_tiles = prm.N * tiles_per_image;
-    const int64_t first = blockIdx.x, stride = gridDim.x;
-    double acc_loss = 0.0, acc_cnt = 0.0;
-
-    pipe_init<kTileCompute, true>(bars, NS);
-
-    if (tid == kTileCompute) {
-        // ---- loader: every chunk of a tile twice; the first read asks the L2 to keep the lines,
-        // the second one lets them go
-        const uint64_t keep = l2_policy_evict_last(), drop = l2_policy_evict_first();
-        int k = 0;
-        bool alive = true;
-        for (int64_t t = first; t < total_tiles && alive; t += stride) {
-            const int64_t n = t / tiles_per_image;
-            const int64_t p0 = (t % tiles_per_image) * kChunkTile;
-            int64_t npix = prm.M - p0;
-            if (npix > kChunkTile) npix = kChunkTile;
-            const int nbx = int((npix + kChunkTP - 1) / kChunkTP);
-            const uint32_t label_bytes = uint32_t(npix) * 8u;       // M % 4 == 0: a multiple of 16
-            for (int sweep = 0; sweep < 2 && alive; ++sweep) {
-                for (int c = 0; c < nchunks; ++c, ++k) {
-                    const int s = k % NS;
-                    if (k >= NS && !mbar_wait_bounded(&bars.empty[s], ((k / NS) - 1) & 1, status)) {
-                        alive = false;
-                        break;
-                    }
-                    unsigned char *stage = base + size_t(s) * lay.stage_bytes;
-                    const bool with_labels = sweep == 0 && c == 0;
-                    *reinterpret_cast<int4 *>(stage + lay.coord_off) = make_int4(int(n), int(p0), c, nbx | (sweep << 8));
-                    mbar_expect_tx(&bars.full[s],
-                                   uint32_t(nbx) * lay.box_elems * uint32_t(sizeof(T)) + (with_labels ? label_bytes : 0u));
-                    for (int bx = 0; bx < nbx; ++bx)
-                        tma_load_3d_hint(reinterpret_cast<T *>(stage) + size_t(bx) * lay.box_elems, &map_in,
-                                         int(p0) + bx * kChunkTP, c * kChunkCh, int(n), &bars.full[s],
-                                         sweep == 0 ? keep : drop);
-                    if (with_labels)
-                        bulk_load_1d(stage + lay.label_off, prm.labels + n * prm.M + p0, label_bytes, &bars.full[s]);
-                }
-            }
-        }
-    } else if (tid == kTileCompute + 32) {
-        // ---- storer: forwards every slot to the loader, after the TMA store of a sweep-1 slot
-        const int64_t total_slots = ((total_tiles - first + stride - 1) / stride) * 2 * nchunks;
-        const uint64_t drop = l2_policy_evict_first();       // the gradient is not read again here
-        for (int64_t k = 0; k < total_slots; ++k) {
-            const int s = int(k % NS);
-            if (!mbar_wait_bounded(&bars.ready[s], uint32_t(k / NS) & 1u, status)) break;
-            const unsigned char *stage = base + size_t(s) * lay.stage_bytes;
-            const int4 coord = *reinterpret_cast<const int4 *>(stage + lay.coord_off);
-            if (coord.w >> 8) {
-                const int nbx = coord.w & 0xff;
-                for (int bx = 0; bx < nbx; ++bx)
-                    tma_store_3d_hint(&map_out, coord.y + bx * kChunkTP, coord.z * kChunkCh, coord.x,
-                                      reinterpret_cast<const T *>(stage) + size_t(bx) * lay.box_elems, drop);
-                bulk_commit();
-                bulk_wait_read_all();
-            }
-            mbar_arrive(&bars.empty[s]);
-        }
-        bulk_wait_all();
-    } else if (tid < kTileCompute) {
-        const int lane = tid & 31;
-        const int pix = tid * 2;
-        const int bxo = (pix / kChunkTP) * int(lay.box_elems) + (pix % kChunkTP);
-        const LossConsts kc = prm.k;
-        const float gscale = uniform_grad_scale(nullptr, 0, prm.denom);
-        float acc32 = 0.f;
-        int cnt32 = 0;
-        int k = 0;
-        bool alive = true;
-        for (int64_t t = first; t < total_tiles && alive; t += stride) {
-            int lbi[2] = {-1, -1};
-            bool inb[2] = {false, false};
-            float2 m = splat2(kNegInf), sum = splat2(0.f), sde = splat2(0.f), sx = splat2(0.f);
-            float2 xl = splat2(0.f), xo = splat2(0.f);
-            // ---- sweep 0: statistics
-            for (int c = 0; c < nchunks; ++c, ++k) {
-                const int s = k % NS;
-                bool ok = true;
-                if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
-                if (!__shfl_sync(0xffffffffu, ok, 0)) {
-                    alive = false;
-                    break;
-                }
-                unsigned char *stage = base + size_t(s) * lay.stage_bytes;
-                T *mine = reinterpret_cast<T *>(stage) + bxo;
-                const int c0 = c * kChunkCh;
-                const int nch = min(kChunkCh, C - c0);
-                if (c == 0) {
-                    const int4 coord = *reinterpret_cast<const int4 *>(stage + lay.coord_off);
-                    const int64_t px0 = int64_t(coord.y) + pix;
-                    const int64_t *tile_labels = reinterpret_cast<const int64_t *>(stage + lay.label_off);
-#pragma unroll
-                    for (int i = 0; i < 2; ++i) {
-                        inb[i] = px0 + i < prm.M;
-                        const int64_t lb = inb[i] ? tile_labels[pix + i] : prm.ignore;
-                        const bool valid = inb[i] && lb != prm.ignore;
-                        lbi[i] = valid ? ((lb >= 0 && lb < C) ? int(lb) : -2) : -1;
-                    }
-                    if (KIND == kLMargin) {
-                        // the stand-in for the target: channel 0, or 1 when the label is 0
-                        xo.x = to_f32(mine[(lbi[0] == 0 ? 1 : 0) * kChunkTP]);
-                        xo.y = to_f32(mine[(lbi[1] == 0 ? 1 : 0) * kChunkTP + 1]);
-                    }
-                }
-                // the label channel of my pixels, if it is in this chunk (shared memory only: the
-                // second sweep reads the logits afresh)
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int j = lbi[i] - c0;
-                    if (lbi[i] >= 0 && j >= 0 && j < kChunkCh) {
-                        T *e = mine + j * kChunkTP + i;
-                        if (i == 0) xl.x = to_f32(*e); else xl.y = to_f32(*e);
-                        if (KIND == kLMargin) *e = from_f32<T>(i == 0 ? xo.x : xo.y);
-                    }
-                }
-                for (int g0 = 0; g0 < nch; g0 += kChunkGroup) {
-                    const int ng = min(kChunkGroup, nch - g0);
-                    pk_t x[kChunkGroup];
-                    float2 mn = m;
-#pragma unroll
-                    for (int q = 0; q < kChunkGroup; ++q) {
-                        x[q] = ld_pk(mine + (g0 + (q < ng ? q : 0)) * kChunkTP);
-                        mn = max2(mn, upk2(x[q]));
-                    }
-                    const float2 dm = make_float2(m.x - mn.x, m.y - mn.y);
-                    const float2 r = ex2_2(mul2(dm, splat2(kLog2e)));
-                    if (KIND == kLMargin) sde = mul2(r, fma2(dm, sum, sde));
-                    sum = mul2(sum, r);
-                    m = mn;
-                    const pk_t nml = pk2(mul2(mn, splat2(-kLog2e))), l2e = psplat(kLog2e), negm = pk2(make_float2(-mn.x, -mn.y));
-                    pk_t psum = pk2(sum), psde = pk2(sde), psx = pk2(sx);
-#pragma unroll
-                    for (int q = 0; q < kChunkGroup; ++q) {
-                        if (q < ng) {
-                            const pk_t e = pex2(pfma(x[q], l2e, nml));
-                            psum = padd(psum, e);
-                            if (KIND == kLMargin) psde = pfma(padd(x[q], negm), e, psde);
-                            psx = padd(psx, x[q]);
-                        }
-                    }
-                    sum = upk2(psum);
-                    sde = upk2(psde);
-                    sx = upk2(psx);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.ready[s]);
-            }
-            if (!alive) break;
-            // ---- per pixel: loss and the coefficients of its gradient (closed forms of the two
-            // kernels above, without the round trip through global memory)
-            float a2[2], b2[2], c2[2], m2[2], tgt[2];
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const float mi = i ? m.y : m.x, si = i ? sum.y : sum.x, sxi = i ? sx.y : sx.x;
-                const float xli = lbi[i] >= 0 ? (i ? xl.y : xl.x) : 0.f;
-                const bool valid = lbi[i] != -1;
-                const float sc = valid ? gscale : 0.f;
-                float l = 0.f;
-                m2[i] = mi;
-                a2[i] = b2[i] = c2[i] = tgt[i] = 0.f;
-                if (inb[i] && valid) {
-                    if (KIND == kLSR) {
-                        l = kc.sumy * (mi + __logf(si)) - kc.lb_neg * sxi - (kc.lb_pos - kc.lb_neg) * xli;
-                        a2[i] = kc.sumy * sc * __fdividef(1.f, si);
-                        b2[i] = -kc.lb_neg * sc;
-                        tgt[i] = -(kc.lb_pos - kc.lb_neg) * sc;
-                    } else {
-                        const bool repl = lbi[i] >= 0;
-                        const float ci = i ? xo.y : xo.x;
-                        const float dc = ci - mi;
-                        const float ec = repl ? ex2f(dc * kLog2e) : 0.f;
-                        const float s_no = si - ec;
-                        const float sde_no = (i ? sde.y : sde.x) - (repl ? dc * ec : 0.f);
-                        const float nother = repl ? float(C - 1) : float(C);
-                        const float sd = (sxi - (repl ? ci : 0.f)) - nother * mi;
-                        const float inv_s = __fdividef(1.f, s_no);
-                        const float sqx = sde_no * inv_s;
-                        const float mm = fmaxf(mi, xli);
-                        const float e_no = s_no * ex2f((mi - mm) * kLog2e);
-                        const float e_lb = repl ? ex2f((xli - mm) * kLog2e) : 0.f;
-                        const float s_all = e_no + e_lb;
-                        l = (mm + __logf(s_all)) - xli + kc.half_lam * (sqx - kc.a * sd);
-                        const float rr = __fdividef(e_no, s_all);
-                        a2[i] = (rr + kc.half_lam * (1.f - sqx)) * sc * inv_s;
-                        b2[i] = kc.half_lam * sc * inv_s;
-                        c2[i] = -kc.half_lam * kc.a * sc;
-                        tgt[i] = -rr * sc;
-                    }
-                    acc32 += l;
-                    cnt32 += 1;
-                }
-            }
-            if (cnt32 >= 32) {
-                acc_loss += double(acc32);
-                acc_cnt += double(cnt32);
-                acc32 = 0.f;
-                cnt32 = 0;
-            }
-            const pk_t pa = pk2(make_float2(a2[0], a2[1])), pb = pk2(make_float2(b2[0], b2[1]));
-            const pk_t pc = pk2(make_float2(c2[0], c2[1])), pm = pk2(make_float2(m2[0], m2[1]));
-            // ---- sweep 1: gradients in place
-            for (int c = 0; c < nchunks; ++c, ++k) {
-                const int s = k % NS;
-                bool ok = true;
-                if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
-                if (!__shfl_sync(0xffffffffu, ok, 0)) {
-                    alive = false;
-                    break;
-                }
-                unsigned char *stage = base + size_t(s) * lay.stage_bytes;
-                T *mine = reinterpret_cast<T *>(stage) + bxo;
-                const int c0 = c * kChunkCh;
-                const int nch = min(kChunkCh, C - c0);
-                {
-                    const pk_t l2e = psplat(kLog2e);
-                    const pk_t nml = pmul(pm, psplat(-kLog2e)), negm = pmul(pm, psplat(-1.f));
-                    T *q = mine;
-#pragma unroll 4
-                    for (int j = 0; j < nch; ++j, q += kChunkTP) {
-                        const pk_t x = ld_pk(q);
-                        const pk_t e = pex2(pfma(x, l2e, nml));
-                        if (KIND == kLSR) st_pk(q, pfma(e, pa, pb));
-                        else st_pk(q, pfma(e, pfma(pb, padd(x, negm), pa), pc));
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int j = lbi[i] - c0;
-                    if (lbi[i] >= 0 && j >= 0 && j < kChunkCh) {
-                        T *e = mine + j * kChunkTP + i;
-                        *e = from_f32<T>(KIND == kLSR ? to_f32(*e) + tgt[i] : tgt[i]);
-                    }
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars.ready[s]);
-            }
-        }
-        acc_loss += double(acc32);
-        acc_cnt += double(cnt32);
-    }
-    grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
-}
-
 // Pair q of a 16-byte register vector as two floats, and back.
 __device__ __forceinline__ float2 pair_of(const Vec16<float> &v, int q) { return make_float2(v.v[2 * q], v.v[2 * q + 1]); }
 __device__ __forceinline__ float2 pair_of(const Vec16<__half> &v, int q) {
     return __half22float2(__halves2half2(v.v[2 * q], v.v[2 * q + 1]));
+}
+__device__ __forceinline__ float2 pair_of(const Vec16<__nv_bfloat16> &v, int q) {
+    return make_float2(__bfloat162float(v.v[2 * q]), __bfloat162float(v.v[2 * q + 1]));
 }
 __device__ __forceinline__ void set_pair(Vec16<float> &v, int q, float2 f) {
     v.v[2 * q] = f.x;
@@ -1519,6 +1246,10 @@ __device__ __forceinline__ void set_pair(Vec16<__half> &v, int q, float2 f) {
     const __half2 h = __float22half2_rn(f);
     v.v[2 * q] = __low2half(h);
     v.v[2 * q + 1] = __high2half(h);
+}
+__device__ __forceinline__ void set_pair(Vec16<__nv_bfloat16> &v, int q, float2 f) {
+    v.v[2 * q] = __float2bfloat16_rn(f.x);
+    v.v[2 * q + 1] = __float2bfloat16_rn(f.y);
 }
 
 // Reduce two values over the first n threads of the block (sum or max); every thread gets
@@ -1649,7 +1380,7 @@ rows_pipe_kernel(const SoftmaxParams prm) {
             // ---- phase 1: maximum (half rows: on the packed halves, exact and four values per
             // instruction-pair instead of a conversion and a compare each)
             float2 m2 = splat2(kNegInf);
-            if constexpr (sizeof(T) == 2) {
+            if constexpr (std::is_same<T, __half>::value) {
                 __half2 hm = __float2half2_rn(-65504.f);
                 for (int v = tid; v < nvec; v += kRowsCompute) {
                     const uint4 raw = *reinterpret_cast<const uint4 *>(row + v * VN);
@@ -2097,39 +1828,6 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
                 return launch_status("softmax chunked forward kernel launch");
             }
         }
-        if constexpr (BWD && REDUCE) {
-            // many channels, fused training step: the resident tile would be cut into channel slices
-            // (KS > 1); two chunked sweeps instead, the second one out of L2
-            if (prm.KS > 1 && prm.grad_mode == 0 && !getenv("B200_NO_CHUNK_STEP") &&
-                chunk_eligible(es, prm.logits, prm.grads, prm.labels, prm.N, prm.C, prm.M)) {
-                const ChunkLayout lay = chunk_layout<T>();
-                // Resident blocks x tile bytes must stay well inside the L2 for the second sweep to hit:
-                // two blocks per SM while that product is below ~96 MB, else one (deeper ring).
-                const size_t tile_bytes = size_t(prm.C) * kChunkTile * es;
-                int per_sm = tune_int("B200_STEP_CTAS", 2 * size_t(sms) * tile_bytes <= (size_t(96) << 20) ? 2 : 1);
-                if (per_sm < 1) per_sm = 1;
-                int stages = tune_int("B200_STEP_STAGES", per_sm >= 2 ? 3 : 6);
-                if (stages > kMaxStages) stages = kMaxStages;
-                while (stages > 2 && (128 + size_t(stages) * lay.stage_bytes + 2048) * per_sm > size_t(224) * 1024) --stages;
-                prm.stages = stages;
-                const size_t smem = 128 + size_t(stages) * lay.stage_bytes;
-                const int64_t tiles = prm.N * ((prm.M + kChunkTile - 1) / kChunkTile);
-                int64_t grid = int64_t(sms) * per_sm;
-                if (grid > tiles) grid = tiles;
-                if (grid > kMaxPartials) grid = kMaxPartials;
-                CUtensorMap map_in{}, map_out{};
-                const uint64_t dims[3] = {uint64_t(prm.M), uint64_t(prm.C), uint64_t(prm.N)};
-                const uint64_t strides[3] = {es, uint64_t(prm.M) * es, uint64_t(prm.C) * prm.M * es};
-                const uint32_t box[3] = {uint32_t(kChunkTP), uint32_t(kChunkCh), 1u};
-                if (!encode_tensor_map(&map_in, dtype, prm.logits, 3, dims, strides, box)) return B200_ERR_LAUNCH;
-                if (!encode_tensor_map(&map_out, dtype, prm.grads, 3, dims, strides, box)) return B200_ERR_LAUNCH;
-                auto kern = tile_chunk_step_kernel<T, KIND>;
-                int rc2;
-                if ((rc2 = set_smem(kern, smem)) != B200_OK) return rc2;
-                kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in, map_out);
-                return launch_status("softmax chunked step kernel launch");
-            }
-        }
         if constexpr (BWD) {
             // many channels, backward from the statistics the chunked forward saved
             if (prm.stats && aligned16(prm.stats) &&
@@ -2284,6 +1982,9 @@ int dispatch(const SoftmaxParams &prm, int dtype, bool reduce, cudaStream_t stre
     if (dtype == B200_F16)
         return reduce ? launch_regime<__half, KIND, BWD, true>(prm, dtype, stream)
                       : launch_regime<__half, KIND, BWD, false>(prm, dtype, stream);
+    if (dtype == B200_BF16)
+        return reduce ? launch_regime<__nv_bfloat16, KIND, BWD, true>(prm, dtype, stream)
+                      : launch_regime<__nv_bfloat16, KIND, BWD, false>(prm, dtype, stream);
     set_error("unknown dtype code %d", dtype);
     return B200_ERR_ARG;
 }
@@ -2394,7 +2095,7 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
         set_error("%s: null pointer", who);
         return B200_ERR_ARG;
     }
-    const size_t es = dtype == B200_F16 ? 2 : 4;
+    const size_t es = dtype_size(dtype);
     if (!fused_step_eligible(es, logits, grad_logits, labels, N, C, M)) {
         set_error("%s: this layout has no fused step (ask b200_softmax_fused_step_path first)", who);
         return B200_ERR_UNSUPPORTED;
@@ -2471,9 +2172,9 @@ extern "C" int b200_count_valid(const int64_t *labels, int64_t P, int64_t ignore
 // 1 when (logits, labels, grad_logits, N, C, M, dtype) has a fused training step, else 0.
 extern "C" int b200_softmax_fused_step_path(const void *logits, const int64_t *labels, const void *grad_logits,
                                             int64_t N, int64_t C, int64_t M, int dtype) {
-    if (dtype != B200_F32 && dtype != B200_F16) return 0;
+    if (!dtype_known(dtype)) return 0;
     if (C < 1 || C >= (int64_t(1) << 31)) return 0;
-    return fused_step_eligible(dtype == B200_F16 ? 2 : 4, logits, grad_logits, labels, N, C, M) ? 1 : 0;
+    return fused_step_eligible(dtype_size(dtype), logits, grad_logits, labels, N, C, M) ? 1 : 0;
 }
 
 // Loss sum (record in `out`) and FINAL gradient (divided by *denom when given: a device double,
@@ -2527,7 +2228,7 @@ extern "C" int b200_lmargin_backward(const void *logits, const int64_t *labels,
 // ---- the same four entry points with per-pixel statistics handed from forward to backward
 extern "C" int b200_softmax_stats_path(const void *logits, const int64_t *labels, const void *grad_logits,
                                        int64_t N, int64_t C, int64_t M, int dtype) {
-    const size_t es = dtype == B200_F16 ? 2 : 4;
+    const size_t es = dtype_size(dtype);
     return chunk_eligible(es, logits, grad_logits ? grad_logits : logits, labels, N, C, M) ? 1 : 0;
 }
 extern "C" int b200_lsr_forward_ex(const void *logits, const int64_t *labels, void *losses, void *out,

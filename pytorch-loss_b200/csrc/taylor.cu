@@ -222,6 +222,9 @@ int dispatch_taylor(TaylorParams &p, int dtype, int order, int use_log, const ch
     if (dtype == B200_F16)
         return use_log ? launch_taylor_order<__half, BWD, true>(p, stream)
                        : launch_taylor_order<__half, BWD, false>(p, stream);
+    if (dtype == B200_BF16)
+        return use_log ? launch_taylor_order<__nv_bfloat16, BWD, true>(p, stream)
+                       : launch_taylor_order<__nv_bfloat16, BWD, false>(p, stream);
     set_error("%s: unknown dtype code %d", who, dtype);
     return B200_ERR_ARG;
 }

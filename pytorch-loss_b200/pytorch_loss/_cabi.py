@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200loss.so")
 
 ABI_VERSION = 2
-F32, F16 = 0, 1
+F32, F16, BF16 = 0, 1, 2
 
 _c = ctypes
 _vp, _i64, _int, _f32, _f64, _sz = _c.c_void_p, _c.c_int64, _c.c_int, _c.c_float, _c.c_double, _c.c_size_t
@@ -117,7 +117,9 @@ def dtype_code(t):
         return F32
     if t.dtype == torch.float16:
         return F16
-    raise RuntimeError("libb200loss supports float32 and float16 logits, got %s" % t.dtype)
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise RuntimeError("libb200loss supports float32, float16 and bfloat16 logits, got %s" % t.dtype)
 
 
 def require_cuda(*tensors):

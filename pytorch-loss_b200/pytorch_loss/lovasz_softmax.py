@@ -23,8 +23,8 @@ def lovasz_forward(logits, labels, ignore_index, per_image=False):
     shaped [C, N*M] ([N, C, M] per image); both float32."""
     dev = _cabi.require_cuda(logits, labels)
     n, c, m = _cabi.split_shape(logits, labels)
-    if logits.dtype not in (torch.float32, torch.float16):
-        raise RuntimeError("lovasz softmax supports float32 and float16 logits, got %s" % logits.dtype)
+    if logits.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise RuntimeError("lovasz softmax supports float32, float16 and bfloat16 logits, got %s" % logits.dtype)
     x = logits.contiguous().float()          # half inputs are computed in fp32, as under autocast
     labels = labels.contiguous()
     lib = _cabi.load_library()

@@ -48,10 +48,10 @@ class PCSoftmaxCrossEntropyFunction(torch.autograd.Function):
         losses, grads = pc_softmax_ce(logits, label, lb_proportion, ignore_index, ctx.needs_input_grad[0])
         n_valid = (label != ignore_index).sum()
         ctx.vars = grads, reduction, n_valid
-        if reduction == 'mean':
-            return losses.sum() / n_valid
+        if reduction == 'mean':               # (half inputs: the sum is taken in fp32)
+            return losses.sum(dtype=torch.float32) / n_valid
         if reduction == 'sum':
-            return losses.sum()
+            return losses.sum(dtype=torch.float32)
         return losses
 
     @staticmethod
