@@ -1482,6 +1482,7 @@ using namespace b200;
 
 extern "C" size_t b200_lovasz_workspace_bytes(int64_t N, int64_t C, int64_t M, int per_image) {
     if (N <= 0 || C <= 0 || M <= 0) return 256;
+    if (N * M >= (int64_t(1) << 31) || C > 1024) return 0;      // a size b200_lovasz_forward refuses
     LovaszGeom g{};
     make_geom(g, N, C, M, per_image);
     return carve(nullptr, g).bytes;

@@ -21,10 +21,25 @@ _ENTRY_EX = {
 }
 
 
+def kernel_layout(logits):
+    """(tensor whose memory the kernels read, N, C, M).  NCHW-contiguous logits go as they are.
+    Channels-last logits (NHWC in memory, as `memory_format=torch.channels_last` gives) go as
+    they are too: every pixel is a row of C contiguous logits, i.e. the kernels' M == 1 layout
+    with N*H*W rows -- no copy (the reference calls `.contiguous()`, csrc/lsr_kernel.cu:222-224).
+    Gradients made with `empty_like` keep the same memory format.  Anything else is copied."""
+    n, c, m = _cabi.split_shape(logits)
+    if logits.is_contiguous():
+        return logits, n, c, m
+    if logits.dim() >= 3 and logits.movedim(1, -1).is_contiguous():
+        return logits, n * m, c, 1
+    return logits.contiguous(), n, c, m
+
+
 def _prep(logits, labels):
     dev = _cabi.require_cuda(logits, labels)
-    n, c, m = _cabi.split_shape(logits, labels)
-    return dev, logits.contiguous(), labels.contiguous(), n, c, m, _cabi.dtype_code(logits)
+    _cabi.split_shape(logits, labels)                       # shape and dtype checks
+    logits, n, c, m = kernel_layout(logits)
+    return dev, logits, labels.contiguous(), n, c, m, _cabi.dtype_code(logits)
 
 
 def forward_per_pixel(kind, logits, labels, ignore_index, hyper):
@@ -74,7 +89,7 @@ def backward(kind, logits, labels, grad_output, denom, ignore_index, hyper, stat
     value per pixel) and the optional device-resident divisor are applied in the kernel.
     `stats`: what the forward of the same inputs returned, if anything."""
     dev = logits.device
-    n, c, m = _cabi.split_shape(logits)
+    logits, n, c, m = kernel_layout(logits)
     lib = _cabi.load_library()
     grads = torch.empty_like(logits)
     if grad_output is None:

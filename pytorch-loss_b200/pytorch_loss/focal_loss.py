@@ -26,7 +26,12 @@ def _prep(logits, labels):
     if labels.shape != logits.shape:
         raise RuntimeError("focal loss: labels shape %s != logits shape %s"
                            % (tuple(labels.shape), tuple(logits.shape)))
-    return dev, logits.contiguous(), labels.contiguous(), _cabi.dtype_code(logits)
+    # elementwise: any dense layout goes as it is when both tensors share it (channels-last
+    # included; outputs made with empty_like keep it); otherwise both are made contiguous
+    dense = logits.is_contiguous() or (logits.dim() >= 3 and logits.movedim(1, -1).is_contiguous())
+    if not (dense and labels.stride() == logits.stride()):
+        logits, labels = logits.contiguous(), labels.contiguous()
+    return dev, logits, labels, _cabi.dtype_code(logits)
 
 
 def _focal_backward(logits, labels, grad_output, denom, alpha, gamma):
@@ -40,6 +45,8 @@ def _focal_backward(logits, labels, grad_output, denom, alpha, gamma):
         mode, g = _cabi.grad_mode_of(grad_output, logits.shape)
         if mode == 2:
             g = g.to(logits.dtype)
+            if not logits.is_contiguous():       # elementwise kernel: same memory layout as the logits
+                g = torch.empty_like(logits).copy_(g)
     with torch.cuda.device(dev):
         _cabi.check(lib.b200_focal_backward(
             _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(g), mode,
