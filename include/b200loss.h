@@ -15,7 +15,8 @@
  * are int64 [N, M] (focal: same dtype and shape as the logits).
  *
  * dtype codes: B200_F32 (float), B200_F16 (__half), B200_BF16 (__nv_bfloat16): the storage type of
- * logits, per-pixel losses and gradients.  Arithmetic is always fp32.
+ * logits, per-pixel losses and gradients; arithmetic is fp32.  B200_F64 (double, arithmetic in double)
+ * is accepted by b200_{lsr,lmargin}_{forward,backward} and b200_focal_{forward,backward,forward_backward}.
  *
  * Reduction record ("out", 32 bytes, 8-byte aligned), written by the forward
  * kernels when `out` is non-NULL:
@@ -53,6 +54,7 @@ extern "C" {
 #define B200_F32 0
 #define B200_F16 1
 #define B200_BF16 2
+#define B200_F64 3   /* double: per-pixel forward/backward entry points of label smooth, large margin, focal */
 
 /* Version of this ABI (bumped on any signature change). */
 int b200_abi_version(void);

@@ -22,6 +22,15 @@ void set_error(const char *fmt, ...);
 int launch_status(const char *what);   // cudaGetLastError -> B200_OK / B200_ERR_LAUNCH; counts the launch
 int sm_count();                         // SMs of the current device (cached per device)
 
+// float64 paths (fp64.cu), called by the per-pixel entry points when dtype == B200_F64
+int f64_softmax_forward(int kind, const void *logits, const int64_t *labels, void *losses, void *out, void *workspace,
+                        int64_t N, int64_t C, int64_t M, int64_t ignore_index, float hp, void *stream);
+int f64_softmax_backward(int kind, const void *logits, const int64_t *labels, const void *grad_out, int grad_mode,
+                         const void *denom, void *grad_logits, int64_t N, int64_t C, int64_t M,
+                         int64_t ignore_index, float hp, void *stream);
+int f64_focal(const void *logits, const void *labels, void *losses, void *grads, const void *grad_out, int grad_mode,
+              const void *denom, void *out, void *workspace, int64_t E, float gamma, float alpha, void *stream);
+
 // Workspace layout shared by all reducing kernels.
 //   [0]   uint32  ticket   (must be zero between kernels; kernels reset it)
 //   [4]   uint32  status   (non-zero: a bounded wait gave up)

@@ -409,6 +409,8 @@ extern "C" int b200_focal_forward(const void *logits, const void *labels, void *
         return B200_ERR_WORKSPACE;
     }
     if (E == 0 && !out) return B200_OK;
+    if (dtype == B200_F64)
+        return f64_focal(logits, labels, losses, nullptr, nullptr, 0, nullptr, out, workspace, E, gamma, alpha, stream);
     FocalParams prm{};
     prm.logits = logits;
     prm.labels = labels;
@@ -434,6 +436,9 @@ extern "C" int b200_focal_backward(const void *logits, const void *labels, const
         set_error("b200_focal_backward: null pointer");
         return B200_ERR_ARG;
     }
+    if (dtype == B200_F64)
+        return f64_focal(logits, labels, nullptr, grad_logits, grad_out, grad_mode, denom, nullptr, nullptr, E, gamma,
+                         alpha, stream);
     FocalParams prm{};
     prm.logits = logits;
     prm.labels = labels;
@@ -459,6 +464,9 @@ extern "C" int b200_focal_forward_backward(const void *logits, const void *label
         set_error("b200_focal_forward_backward: null pointer");
         return B200_ERR_ARG;
     }
+    if (dtype == B200_F64)
+        return f64_focal(logits, labels, losses, grad_logits, nullptr, 0, nullptr, nullptr, nullptr, E, gamma, alpha,
+                         stream);
     FocalParams prm{};
     prm.logits = logits;
     prm.labels = labels;

@@ -2021,6 +2021,9 @@ int forward(const char *who, const void *logits, const int64_t *labels, void *lo
         set_error("%s: null input pointer", who);
         return B200_ERR_ARG;
     }
+    if (dtype == B200_F64)
+        return stats ? (set_error("%s: no per-pixel statistics in float64", who), B200_ERR_UNSUPPORTED)
+                     : f64_softmax_forward(KIND, logits, labels, losses, out, workspace, N, C, M, ignore_index, hp, stream);
     SoftmaxParams prm{};
     prm.logits = logits;
     prm.labels = labels;
@@ -2051,6 +2054,10 @@ int backward(const char *who, const void *logits, const int64_t *labels, const v
         set_error("%s: null pointer", who);
         return B200_ERR_ARG;
     }
+    if (dtype == B200_F64)
+        return stats ? (set_error("%s: no per-pixel statistics in float64", who), B200_ERR_UNSUPPORTED)
+                     : f64_softmax_backward(KIND, logits, labels, grad_out, grad_mode, denom, grad_logits, N, C, M,
+                                            ignore_index, hp, stream);
     SoftmaxParams prm{};
     prm.logits = logits;
     prm.labels = labels;

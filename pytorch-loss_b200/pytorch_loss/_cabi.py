@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200loss.so")
 
 ABI_VERSION = 2
-F32, F16, BF16 = 0, 1, 2
+F32, F16, BF16, F64 = 0, 1, 2, 3
 
 _c = ctypes
 _vp, _i64, _int, _f32, _f64, _sz = _c.c_void_p, _c.c_int64, _c.c_int, _c.c_float, _c.c_double, _c.c_size_t
@@ -112,9 +112,13 @@ def check(code):
         raise B200LossError(code, msg.decode("utf-8", "replace") if msg else "")
 
 
-def dtype_code(t):
+def dtype_code(t, allow_f64=False):
+    """The library's code of a tensor's dtype.  float64 only where the caller has a double path
+    (per-pixel label-smooth / large-margin / focal kernels)."""
     if t.dtype == torch.float32:
         return F32
+    if t.dtype == torch.float64 and allow_f64:
+        return F64
     if t.dtype == torch.float16:
         return F16
     if t.dtype == torch.bfloat16:

@@ -39,7 +39,7 @@ def _prep(logits, labels):
     dev = _cabi.require_cuda(logits, labels)
     _cabi.split_shape(logits, labels)                       # shape and dtype checks
     logits, n, c, m = kernel_layout(logits)
-    return dev, logits, labels.contiguous(), n, c, m, _cabi.dtype_code(logits)
+    return dev, logits, labels.contiguous(), n, c, m, _cabi.dtype_code(logits, allow_f64=True)
 
 
 def forward_per_pixel(kind, logits, labels, ignore_index, hyper):
@@ -103,11 +103,11 @@ def backward(kind, logits, labels, grad_output, denom, ignore_index, hyper, stat
         if stats is not None:
             _cabi.check(getattr(lib, _ENTRY_EX[kind][1])(
                 _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(stats), _cabi.ptr(g), mode, dptr, _cabi.ptr(grads),
-                n, c, m, _cabi.dtype_code(logits), int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+                n, c, m, _cabi.dtype_code(logits, allow_f64=True), int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
         else:
             _cabi.check(getattr(lib, _ENTRY[kind][1])(
                 _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(g), mode, dptr, _cabi.ptr(grads),
-                n, c, m, _cabi.dtype_code(logits), int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+                n, c, m, _cabi.dtype_code(logits, allow_f64=True), int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
     return grads
 
 
@@ -203,6 +203,8 @@ class ReducedLossFunc(torch.autograd.Function):
             loss = _sharding.combine_mean(sum_count) if mean else sum_count[0].to(torch.float32)
         else:
             loss = rec[4] if mean else rec[5]
+        if logits.dtype == torch.float64:        # the record's float fields would round a double loss
+            loss = sum_count[0] / sum_count[1] if mean else sum_count[0].clone()
         ctx.variables = logits, labels, kind, hyper, ignore_index, (sum_count[1:] if mean else None), stats
         return loss
 

@@ -31,7 +31,7 @@ def _prep(logits, labels):
     dense = logits.is_contiguous() or (logits.dim() >= 3 and logits.movedim(1, -1).is_contiguous())
     if not (dense and labels.stride() == logits.stride()):
         logits, labels = logits.contiguous(), labels.contiguous()
-    return dev, logits, labels, _cabi.dtype_code(logits)
+    return dev, logits, labels, _cabi.dtype_code(logits, allow_f64=True)
 
 
 def _focal_backward(logits, labels, grad_output, denom, alpha, gamma):
@@ -51,7 +51,7 @@ def _focal_backward(logits, labels, grad_output, denom, alpha, gamma):
         _cabi.check(lib.b200_focal_backward(
             _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(g), mode,
             None if denom is None else _cabi._vp(denom.data_ptr()),
-            _cabi.ptr(grads), logits.numel(), _cabi.dtype_code(logits),
+            _cabi.ptr(grads), logits.numel(), _cabi.dtype_code(logits, allow_f64=True),
             float(gamma), float(alpha), _cabi.stream_ptr(dev)))
     return grads
 
@@ -179,7 +179,7 @@ class _FocalReducedFunc(torch.autograd.Function):
         ctx.deferred = None
         nccl_group = _sharding.group_is_active(group) and _p2p.get_exchange(group, dev) is None
         if ctx.needs_input_grad[0] and logits.numel() > 0 and not nccl_group and \
-                os.environ.get("B200_FOCAL_FUSED", "1") != "0":
+                logits.dtype != torch.float64 and os.environ.get("B200_FOCAL_FUSED", "1") != "0":
             return _FocalReducedFunc._fused_forward(ctx, logits, labels, alpha, gamma, mean, group, dev, dt, state)
         rec = _cabi.new_record(dev)
         exchange = _p2p.get_exchange(group, dev)      # sums over the ranks inside the kernel, if possible
@@ -194,6 +194,8 @@ class _FocalReducedFunc(torch.autograd.Function):
             loss = _sharding.combine_mean(sum_count) if mean else sum_count[0].to(torch.float32)
         else:
             loss = rec[4] if mean else rec[5]
+        if logits.dtype == torch.float64:        # the record's float fields would round a double loss
+            loss = sum_count[0] / sum_count[1] if mean else sum_count[0].clone()
         ctx.variables = logits, labels, alpha, gamma, (sum_count[1:] if mean else None)
         return loss
 

@@ -23,9 +23,9 @@ def lovasz_forward(logits, labels, ignore_index, per_image=False):
     shaped [C, N*M] ([N, C, M] per image); both float32."""
     dev = _cabi.require_cuda(logits, labels)
     n, c, m = _cabi.split_shape(logits, labels)
-    if logits.dtype not in (torch.float32, torch.float16, torch.bfloat16):
-        raise RuntimeError("lovasz softmax supports float32, float16 and bfloat16 logits, got %s" % logits.dtype)
-    x = logits.contiguous().float()          # half inputs are computed in fp32, as under autocast
+    if logits.dtype not in (torch.float32, torch.float16, torch.bfloat16, torch.float64):
+        raise RuntimeError("lovasz softmax supports floating-point logits, got %s" % logits.dtype)
+    x = logits.contiguous().float()          # every input dtype is computed in fp32 (half: as under autocast)
     labels = labels.contiguous()
     lib = _cabi.load_library()
     loss = torch.empty((n, c) if per_image else (c,), dtype=torch.float32, device=dev)

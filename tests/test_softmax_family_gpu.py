@@ -202,7 +202,7 @@ def test_bad_arguments_raise():
     with pytest.raises(RuntimeError):
         crit(torch.randn(2, 5, 4, 4).cuda(), torch.zeros(2, 4, 4, dtype=torch.int32).cuda())  # dtype
     with pytest.raises(RuntimeError):
-        crit(torch.randn(2, 5, 4, 4).double().cuda(), torch.zeros(2, 4, 4, dtype=torch.int64).cuda())
+        crit(torch.randint(0, 5, (2, 5, 4, 4)).cuda(), torch.zeros(2, 4, 4, dtype=torch.int64).cuda())   # integer logits
 
 
 def test_deterministic_and_status_clean():
