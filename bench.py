@@ -80,6 +80,43 @@ def measured_traffic(wl):
         return None, None
 
 
+def traffic_from_ncu(args):
+    """`--traffic-from CSV --workload W --items I --launches L`: turns the ncu CSV of a
+    `bench.py --workload W --items I --kernels-only` run (metrics dram__bytes_read.sum,
+    dram__bytes_write.sum; L = warm-up + timed launches of each entry point) into the workload's
+    entry of profiles/dram_traffic.json: DRAM bytes per logit element of the forward and of the
+    backward entry point.  Kernels of the backward entry: the gradient rescale and the Lovasz
+    backward; everything else of this library belongs to the forward entry (other kernels are skipped)."""
+    import csv
+    import re
+    wl = BW.WORKLOADS[args.workload].with_items(args.items) if args.items else BW.WORKLOADS[args.workload]
+    rows = list(csv.reader(ln for ln in open(args.traffic_from) if ln.startswith('"')))
+    col = {h: i for i, h in enumerate(rows[0])}
+    scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    sums = [0.0, 0.0]
+    for r in rows[1:]:
+        if not r[col["Metric Name"]].startswith("dram__bytes_"):
+            continue
+        name = r[col["Kernel Name"]]
+        if "b200::" not in name:                      # torch's own kernels (input generation, fills)
+            continue
+        bwd = re.search(r"rescale_kernel|lovasz_pair_kernel<\(?(bool\))?1|lovasz_tile_kernel<\(?(bool\))?1", name) is not None
+        sums[1 if bwd else 0] += float(r[col["Metric Value"]].replace(",", "")) * scale[r[col["Metric Unit"]]]
+    per_elem = [round(v / args.launches / wl.elems, 3) for v in sums]
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    with open(path) as fh:
+        doc = json.load(fh)
+    key = "fused" if (wl.fused_softmax() or wl.kind not in ("lsr", "lsr_rows", "lmargin")) else "separate"
+    entry = doc["workloads"].setdefault(args.workload, {})
+    entry[key] = per_elem
+    entry["capture"] = "bench.py --workload %s --items %d --kernels-only, %d launches per entry point" % (
+        args.workload, wl.shape[0], args.launches)
+    with open(path, "w") as fh:
+        json.dump(doc, fh, indent=1)
+        fh.write("\n")
+    print(args.workload, key, per_elem)
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -598,7 +635,12 @@ def main():
     ap.add_argument("--kernels-only", action="store_true",
                     help="only launch the forward and backward entry points back to back (profiler captures)")
     ap.add_argument("--no-reference-v3", action="store_true", help="skip the reference's CUDA build")
+    ap.add_argument("--traffic-from", default=None, help="ncu CSV to turn into an entry of profiles/dram_traffic.json")
+    ap.add_argument("--launches", type=int, default=0, help="with --traffic-from: launches of each entry point in the CSV")
     args = ap.parse_args()
+    if args.traffic_from:
+        traffic_from_ncu(args)
+        return
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference_arm(args)

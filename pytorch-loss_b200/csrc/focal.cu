@@ -332,13 +332,12 @@ template <typename T, int MODE, bool REDUCE>
 int launch_focal(const FocalParams &prm, cudaStream_t stream) {
     const int vn = Vec16<T>::N;
     int64_t want = (prm.E / vn + kThreads - 1) / kThreads;
-    const char *eb = getenv("B200_FOCAL_BLOCKS"), *eu = getenv("B200_FOCAL_UNROLL");
     // the fused step (loss sum + gradient) runs best with all eight blocks of an SM resident and
     // one vector per array in flight per thread: 38.8 us against 43.2 us at 16.7 M elements
     constexpr bool kFusedStep = MODE == kFwdBwd && REDUCE;
-    const int bps = eb && atoi(eb) > 0 ? atoi(eb) : (kFusedStep ? 8 : kBlocksPerSM);
-    const int unroll = eu ? atoi(eu) : (kFusedStep ? 1 : 2);
-    const int64_t cap = int64_t(sm_count()) * bps;
+    constexpr int bps = kFusedStep ? 8 : kBlocksPerSM;
+    int64_t cap = int64_t(sm_count()) * bps;
+    if (REDUCE && cap > kMaxPartials) cap = kMaxPartials;      // one partial slot per block
     if (want > cap) want = cap;
     if (want < 1) want = 1;
     const dim3 grid(static_cast<unsigned>(want));
@@ -346,14 +345,15 @@ int launch_focal(const FocalParams &prm, cudaStream_t stream) {
                     (!prm.losses || aligned16(prm.losses)) && (!prm.grads || aligned16(prm.grads)) &&
                     (prm.grad_mode != 2 || aligned16(prm.grad_out));
     // the ring wins for the read-only forward (8% at the 16.7 M-element size); with a gradient
-    // stream to write, plain loads + stores are as fast and simpler (fused step, measured with
-    // B200_FOCAL_RING_STEP=1: ring 40.1 us at its best geometry, plain 39.1 us)
-    if (al && (MODE == kFwd || (kFusedStep && getenv("B200_FOCAL_RING_STEP"))) && !getenv("B200_FOCAL_NO_RING")) {
+    // stream to write, plain loads + stores are as fast and simpler (fused step: ring 40.1 us at
+    // its best geometry, plain 39.1 us)
+    if (al && MODE == kFwd) {
         constexpr size_t smem = 128 + size_t(kRingStages) * 2 * kRingChunkBytes;
-        const int per_sm = eb && atoi(eb) > 0 ? atoi(eb) : int((220 * 1024) / (smem + 1024));
+        const int per_sm = int((220 * 1024) / (smem + 1024));
         const int64_t chunk_elems = kRingChunkBytes / sizeof(T);
         int64_t g = (prm.E + chunk_elems - 1) / chunk_elems;
         if (g > int64_t(sm_count()) * per_sm) g = int64_t(sm_count()) * per_sm;
+        if (REDUCE && g > kMaxPartials) g = kMaxPartials;
         if (g < 1) g = 1;
         auto go = [&](auto kern) {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -365,9 +365,7 @@ int launch_focal(const FocalParams &prm, cudaStream_t stream) {
     }
     if (!al) {
         focal_kernel_unaligned<T, MODE, REDUCE><<<grid, kThreads, 0, stream>>>(prm);
-    } else if (prm.gamma == 2.f && unroll == 4) {
-        focal_kernel<T, MODE, true, REDUCE, 4><<<grid, kThreads, 0, stream>>>(prm);
-    } else if (prm.gamma == 2.f && unroll == 1) {
+    } else if (prm.gamma == 2.f && kFusedStep) {
         focal_kernel<T, MODE, true, REDUCE, 1><<<grid, kThreads, 0, stream>>>(prm);
     } else if (prm.gamma == 2.f) {
         focal_kernel<T, MODE, true, REDUCE><<<grid, kThreads, 0, stream>>>(prm);

@@ -1737,12 +1737,6 @@ rows_warp_fwd_kernel(const SoftmaxParams prm) {
 
 // Integer tuning override from the environment (tile size, ring depth, blocks per SM);
 // unset or unparsable -> the default.
-inline int tune_int(const char *name, int dflt) {
-    const char *v = getenv(name);
-    if (!v || !*v) return dflt;
-    const int x = atoi(v);
-    return x > 0 ? x : dflt;
-}
 
 template <typename K> int set_smem(K kernel, size_t bytes) {
     if (bytes > 40 * 1024) {   // static shared memory shares the default 48 KiB
@@ -1761,7 +1755,7 @@ inline bool chunk_eligible(size_t es, const void *logits, const void *io, const 
     if (M <= 1 || size_t(C) * 32 * es + 8192 > kSmemLimit) return false;
     const bool tma_ok = (M * es) % 16 == 0 && aligned16(logits) && aligned16(io) && M < (int64_t(1) << 31) &&
                         N < (int64_t(1) << 31) && aligned16(labels);
-    if (!tma_ok || M < kChunkTile || getenv("B200_NO_CHUNK")) return false;
+    if (!tma_ok || M < kChunkTile) return false;
     const int64_t nbox = (C + 255) / 256, rows = nbox * ((C + nbox - 1) / nbox);
     return 2 * size_t(rows) * 256 * es > size_t(40) * 1024;
 }
@@ -1788,7 +1782,6 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             target = size_t(80) * 1024;
             default_stages = 1;
         }
-        if (tma_ok && getenv("B200_TILE_KB")) target = size_t(tune_int("B200_TILE_KB", 40)) * 1024;
         int TP = 256;
         while (TP > 32 && size_t(prm.C) * TP * es > target) TP >>= 1;
         while (TP > 32 && TP / 2 >= prm.M) TP >>= 1;   // tiny images: do not waste lanes
@@ -1804,12 +1797,12 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             if (chunk_eligible(es, prm.logits, prm.logits, prm.labels, prm.N, prm.C, prm.M)) {
                 const ChunkLayout lay = chunk_layout<T>();
                 // measured on config 3 (C = 150): 2 stages x 3 blocks per SM 206 us, 3 stages x 2 blocks 222 us
-                int stages = tune_int("B200_CHUNK_STAGES", 2);
+                int stages = (2);
                 if (stages > kMaxStages) stages = kMaxStages;
                 prm.stages = stages;
                 const size_t smem = 128 + size_t(stages) * lay.stage_bytes;
                 int per_sm = int((224 * 1024) / (smem + 1024));
-                const int cap_sm = tune_int("B200_CHUNK_CTAS", 3);
+                const int cap_sm = (3);
                 if (per_sm > cap_sm) per_sm = cap_sm;
                 if (per_sm < 1) per_sm = 1;
                 const int64_t tiles = prm.N * ((prm.M + kChunkTile - 1) / kChunkTile);
@@ -1835,12 +1828,12 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
                 const ChunkBwdLayout lay = chunk_bwd_layout<T>();
                 // a stage is busy from its load to the end of its store: backward wants a deeper ring
                 // than forward (config 3: 3 stages in one block per SM 396 us, 2 stages x 2 blocks 430 us)
-                int stages = tune_int("B200_CHUNK_BWD_STAGES", 3);
+                int stages = (3);
                 if (stages > kMaxStages) stages = kMaxStages;
                 prm.stages = stages;
                 const size_t smem = 128 + size_t(stages) * lay.stage_bytes;
                 int per_sm = int((224 * 1024) / (smem + 1024));
-                const int cap_sm = tune_int("B200_CHUNK_CTAS", 3);
+                const int cap_sm = (3);
                 if (per_sm > cap_sm) per_sm = cap_sm;
                 if (per_sm < 1) per_sm = 1;
                 const int64_t tiles = prm.N * ((prm.M + kChunkTile - 1) / kChunkTile);
@@ -1870,13 +1863,13 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             const size_t xchg_bytes = size_t(5) * kTileCompute * 2 * sizeof(float);
             // a stage holds the logits tile, the tile's labels and its coordinates
             const size_t stage_bytes = tile_bytes + size_t(TPT) * sizeof(int64_t) + 128;
-            int stages = tune_int("B200_STAGES", default_stages);
+            int stages = (default_stages);
             while (stages > 1 && 128 + stages * stage_bytes + xchg_bytes > kSmemLimit) --stages;
             if (stages > kMaxStages) stages = kMaxStages;
             prm.stages = stages;
             const size_t smem = 128 + stages * stage_bytes + xchg_bytes;
             int per_sm = int((224 * 1024) / (smem + 1024));
-            const int cap_sm = tune_int("B200_CTAS", 3);
+            const int cap_sm = (3);
             if (per_sm > cap_sm) per_sm = cap_sm;
             if (per_sm < 1) per_sm = 1;
             int64_t grid = int64_t(sms) * per_sm;
@@ -1909,11 +1902,11 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
     if constexpr (!BWD) {
         // ---- rows regime, forward, long rows: one warp per row, streamed (any row length)
         if (prm.M == 1 && (size_t(prm.C) * es) % 16 == 0 && size_t(prm.C) * es >= 2 * size_t(kWarpRowChunk) &&
-            aligned_io && !getenv("B200_NO_ROWWARP")) {
+            aligned_io) {
             const size_t smem = 128 + size_t(kWarpRowWarps) * kWarpRowStages * kWarpRowChunk;
             // measured on config 5: 2 stages x 3 blocks per SM 223 us, 3 stages x 2 blocks 237 us,
             // 2 KB chunks x 5 blocks 246 us (whole-row kernel below: 251 us)
-            const int per_sm = tune_int("B200_ROWWARP_CTAS", 3);
+            const int per_sm = (3);
             int64_t grid = int64_t(sms) * per_sm;
             const int64_t need = (prm.N + kWarpRowWarps - 1) / kWarpRowWarps;
             if (grid > need) grid = need;
@@ -1935,13 +1928,13 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             // the phases of a row (max sweep, block reduction, sum sweep, ...) cannot overlap inside
             // a block, they can across blocks (config 5: forward 0.60 of peak with 2 blocks x 1 stage
             // against 0.52 with 1 block x 3 stages; backward 0.85 with 3 blocks).
-            int stages = tune_int("B200_STAGES", row_al > 32 * 1024 ? 1 : 2);
+            int stages = (row_al > 32 * 1024 ? 1 : 2);
             while (stages > 1 && 128 + stages * row_al > kSmemLimit) --stages;
             if (stages > kMaxStages) stages = kMaxStages;
             prm.stages = stages;
             const size_t smem = 128 + stages * row_al;
             int per_sm = int((224 * 1024) / (smem + 2048));
-            const int rows_cap = tune_int("B200_ROWS_CTAS", BWD ? 3 : 2);
+            const int rows_cap = (BWD ? 3 : 2);
             if (per_sm > rows_cap) per_sm = rows_cap;
             if (per_sm < 1) per_sm = 1;
             int64_t grid = int64_t(sms) * per_sm;
