@@ -1994,6 +1994,11 @@ int check_shape(const char *who, int64_t N, int64_t C, int64_t M) {
     return B200_OK;
 }
 
+__global__ void empty_record_kernel(void *workspace, ReduceRecord *out) {
+    __shared__ double sh[64];
+    grid_reduce_finish(0.0, 0.0, workspace, out, sh);
+}
+
 template <int KIND>
 int forward(const char *who, const void *logits, const int64_t *labels, void *losses, void *out,
             void *workspace, size_t workspace_bytes, int64_t N, int64_t C, int64_t M, int dtype,
@@ -2013,6 +2018,11 @@ int forward(const char *who, const void *logits, const int64_t *labels, void *lo
     if (P > 0 && (!logits || !labels)) {
         set_error("%s: null input pointer", who);
         return B200_ERR_ARG;
+    }
+    if (P == 0) {
+        // no pixels: the record of an empty sum (count 0, mean 0/0), still added over attached ranks
+        empty_record_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(workspace, static_cast<ReduceRecord *>(out));
+        return launch_status("empty reduction launch");
     }
     if (dtype == B200_F64)
         return stats ? (set_error("%s: no per-pixel statistics in float64", who), B200_ERR_UNSUPPORTED)

@@ -9,7 +9,9 @@
 // sizes, C = size(dim), M = product of the trailing sizes).
 //
 // How: the op streams x (and g) once from HBM and writes once; there is no exponential.
-//   M > 1   a thread owns 4 adjacent positions along M (16-byte accesses when the layout
+//   M > 1   few channels (<= 32 forward, <= 20 backward, float32): a thread owns 2 adjacent
+//           positions and keeps all their channels in registers -- one read, one write;
+//           otherwise a thread owns 4 adjacent positions along M (16-byte accesses when the layout
 //           allows, else one position) and walks the C channels twice: sums first, outputs
 //           second; the second walk finds its lines in L1/L2 (a block's working set is C x 4 KB).
 //   M == 1  a warp owns a row: lanes stride over the channels, warp-shuffle sums.
@@ -124,6 +126,74 @@ taylor_spatial_kernel(const TaylorParams p) {
     }
 }
 
+// M > 1, few channels (C <= CMAX), float32: a thread owns 2 adjacent positions and keeps all their
+// channels in registers, so x (and g) are read once: 8-byte accesses, 256 B per warp and channel.
+template <bool BWD, bool LOG, int ORDER, int CMAX>
+__global__ void __launch_bounds__(kTaylorThreads, 2)
+taylor_resident_kernel(const TaylorParams p) {
+    const float *x = static_cast<const float *>(p.x);
+    const float *g = static_cast<const float *>(p.g);
+    float *out = static_cast<float *>(p.out);
+    const int C = int(p.C);
+    const int64_t groups_per_row = p.M / 2;
+    const int64_t groups = p.N * groups_per_row;
+    const int64_t stride = int64_t(gridDim.x) * kTaylorThreads;
+    for (int64_t gi = int64_t(blockIdx.x) * kTaylorThreads + threadIdx.x; gi < groups; gi += stride) {
+        const int64_t n = gi / groups_per_row, m0 = (gi % groups_per_row) * 2;
+        const int64_t base = n * p.C * p.M + m0;
+        float2 xv[CMAX], gv[BWD ? CMAX : 1];
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j) {
+            if (j < C) {
+                xv[j] = __ldcs(reinterpret_cast<const float2 *>(x + base + j * p.M));
+                if (BWD) gv[j] = __ldcs(reinterpret_cast<const float2 *>(g + base + j * p.M));
+            }
+        }
+        float2 S = make_float2(0.f, 0.f), A = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j) {
+            if (j < C) {
+                float d;
+                float2 f;
+                taylor_poly<ORDER, false>(xv[j].x, p, f.x, d);
+                taylor_poly<ORDER, false>(xv[j].y, p, f.y, d);
+                S.x += f.x;
+                S.y += f.y;
+                if (BWD) {
+                    A.x += LOG ? gv[j].x : gv[j].x * f.x;
+                    A.y += LOG ? gv[j].y : gv[j].y * f.y;
+                } else {
+                    xv[j] = f;            // forward: f(x) takes x's place; backward recomputes it with f'
+                }
+            }
+        }
+        const float2 invS = make_float2(1.f / S.x, 1.f / S.y);
+        const float2 logS = LOG && !BWD ? make_float2(logf(S.x), logf(S.y)) : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j) {
+            if (j < C) {
+                float2 o;
+                if constexpr (!BWD) {
+                    o.x = LOG ? logf(xv[j].x) - logS.x : xv[j].x * invS.x;
+                    o.y = LOG ? logf(xv[j].y) - logS.y : xv[j].y * invS.y;
+                } else {
+                    float fx, fy, dx, dy;
+                    taylor_poly<ORDER, true>(xv[j].x, p, fx, dx);
+                    taylor_poly<ORDER, true>(xv[j].y, p, fy, dy);
+                    if (LOG) {
+                        o.x = dx * (gv[j].x / fx - A.x * invS.x);
+                        o.y = dy * (gv[j].y / fy - A.y * invS.y);
+                    } else {
+                        o.x = dx * invS.x * (gv[j].x - A.x * invS.x);
+                        o.y = dy * invS.y * (gv[j].y - A.y * invS.y);
+                    }
+                }
+                __stcs(reinterpret_cast<float2 *>(out + base + j * p.M), o);
+            }
+        }
+    }
+}
+
 // M == 1: one warp per row.
 template <typename T, bool BWD, bool LOG, int ORDER>
 __global__ void __launch_bounds__(kTaylorThreads)
@@ -173,6 +243,21 @@ int launch_taylor(const TaylorParams &p, cudaStream_t stream) {
         if (grid > cap) grid = cap;
         taylor_rows_kernel<T, BWD, LOG, ORDER><<<unsigned(grid), kTaylorThreads, 0, stream>>>(p);
         return launch_status("taylor softmax rows kernel launch");
+    }
+    if constexpr (sizeof(T) == 4) {
+        // few channels: everything a thread needs stays in its registers, one read of x (and g)
+        const bool al8 = ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out) |
+                           (BWD ? reinterpret_cast<uintptr_t>(p.g) : 0)) & 7u) == 0;
+        constexpr int kSmall = BWD ? 20 : 32;
+        if (p.M % 2 == 0 && al8 && p.C <= kSmall) {
+            const int64_t groups2 = p.N * (p.M / 2);
+            int64_t grid2 = (groups2 + kTaylorThreads - 1) / kTaylorThreads;
+            const int64_t cap2 = int64_t(sm_count()) * 2 * 8;
+            if (grid2 > cap2) grid2 = cap2;
+            if (p.C <= 8) taylor_resident_kernel<BWD, LOG, ORDER, 8><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
+            else taylor_resident_kernel<BWD, LOG, ORDER, kSmall><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
+            return launch_status("taylor softmax resident kernel launch");
+        }
     }
     const bool vec4 = sizeof(T) == 4 && p.M % 4 == 0 && aligned16(p.x) && aligned16(p.out) && (!BWD || aligned16(p.g));
     const int64_t groups = p.N * (vec4 ? p.M / 4 : p.M);

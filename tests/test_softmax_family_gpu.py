@@ -294,3 +294,15 @@ def test_fused_step(kind, shape, reduction, monkeypatch):
     plain_loss, plain_grad = run_module(crit, xg, yg)
     assert_loss_close(fused_loss, plain_loss.cpu(), rtol=2e-6)
     assert_grad_close(fused_grad, plain_grad.cpu())
+
+
+@pytest.mark.parametrize("kind", ["lsr", "lmargin"])
+def test_empty_batch_reduced(kind):
+    """No pixels at all: 'sum' is 0, 'mean' is 0/0 = NaN as in the reference, the gradient is empty."""
+    for reduction in ("sum", "mean"):
+        crit, _ = _crit(kind, reduction, 255)
+        x = torch.randn(0, 5, 4, 4).cuda().requires_grad_(True)
+        loss = crit(x, torch.zeros(0, 4, 4, dtype=torch.int64).cuda())
+        loss.backward()
+        assert x.grad.shape == x.shape
+        assert torch.isnan(loss.detach()) if reduction == "mean" else float(loss.detach()) == 0.0
