@@ -37,6 +37,7 @@ PY_MODULES = {
     "large_margin_softmax.py": "large_margin_softmax.py",
     "lovasz_softmax.py": "lovasz_softmax.py",
     "taylor_softmax.py": "taylor_softmax.py",
+    "pc_softmax.py": "pc_softmax.py",
     "label_smooth.py": os.path.join("pytorch_loss", "label_smooth.py"),
     "ohem_loss.py": os.path.join("pytorch_loss", "ohem_loss.py"),
 }

@@ -66,7 +66,7 @@ def run(args):
     kind = wl.kind
     if kind in ("lsr", "lsr_rows"):
         from reference_py import label_smooth as M
-        crit = M.LabelSmoothSoftmaxCEV3(0.1, 'mean', 255 if kind == "lsr" else -100)
+        crit = M.LabelSmoothSoftmaxCEV3(0.1, wl.reduction, 255 if kind == "lsr" else -100)
         step = lambda x, y: crit(x, y)
     elif kind == "focal":
         from reference_py import focal_loss as M
@@ -74,7 +74,7 @@ def run(args):
         step = lambda x, y: crit(x, y)
     elif kind == "lmargin":
         from reference_py import large_margin_softmax as M
-        crit = M.LargeMarginSoftmaxV3(0.3, 'mean', 255)
+        crit = M.LargeMarginSoftmaxV3(0.3, wl.reduction, 255)
         step = lambda x, y: crit(x, y)
     elif kind == "lovasz":
         from reference_py import lovasz_softmax as M
@@ -83,6 +83,15 @@ def run(args):
     elif kind == "ohem":
         from reference_py import ohem_loss as M
         crit = M.OhemCELoss(0.7, None, 255)
+        step = lambda x, y: crit(x, y)
+    elif kind == "taylor":
+        from reference_py import taylor_softmax as M
+        crit = M.LogTaylorSoftmaxV3(dim=1, n=2)
+        step = lambda x, g: crit(x)               # the set's second tensor is the upstream gradient
+    elif kind == "pc_softmax":
+        # (no CUDA extension in the reference for this one: its V2 Function is made of torch ops)
+        from reference_py import pc_softmax as M
+        crit = M.PCSoftmaxCrossEntropyV2(wl.proportions(), 'mean', 255)
         step = lambda x, y: crit(x, y)
     else:
         raise RuntimeError("no reference V3 module for workload kind %s" % kind)
@@ -93,13 +102,13 @@ def run(args):
     for r in range(1, N_SETS):
         x, y = wl.make(seed_offset=100 * r, device=dev)
         sets.append((x.requires_grad_(True), y))
-    up = torch.tensor(float(wl.upstream), device=dev)
+    up = wl.upstream_tensor(dev)
 
     def one(k):
         x, y = sets[k % N_SETS]
         x.grad = None
         loss = step(x, y)
-        loss.backward(up if wl.upstream != 1.0 else None)
+        loss.backward(y if kind == "taylor" else up)
         return loss
 
     loss0 = one(0)
@@ -116,7 +125,7 @@ def run(args):
     b.record()
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / args.steps
-    return {"ms_per_step": ms, "elems_per_s": wl.elems / (ms / 1e3), "steps": args.steps, "loss": float(loss0),
+    return {"ms_per_step": ms, "elems_per_s": wl.elems / (ms / 1e3), "steps": args.steps, "loss": float(loss0.detach().float().sum()),
             "shape": list(wl.shape), "mode": "eager module forward+backward, %d rotating input sets" % N_SETS}
 
 

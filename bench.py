@@ -54,7 +54,8 @@ MIN_TIMED_MS = 60.0
 L2_BYTES = 126 << 20
 # workloads the reference's own V3 CUDA build is timed on (N=1): every one of them ran to the end
 # on a B200 when first tried; a workload whose reference kernels fault or hang is taken off here
-REFERENCE_V3_WORKLOADS = ("lmargin", "lsr", "focal", "lsr_rows", "lovasz", "lovasz_full", "ohem", "focal_up2")
+REFERENCE_V3_WORKLOADS = ("lmargin", "lsr", "focal", "lsr_rows", "lovasz", "lovasz_full", "ohem", "focal_up2",
+                          "lmargin_none", "lsr_none", "taylor", "pc_softmax")
 
 
 def measured_peak():
@@ -278,10 +279,15 @@ def make_sets(wl, device, rank):
 
 
 def step_eager(crit, x, y, up=None):
+    """One forward+backward.  `up is DENSE`: the module is an activation, not a loss -- the set's
+    second tensor is the upstream gradient."""
     x.grad = None
-    loss = crit(x, y)
-    loss.backward(up)
+    loss = crit(x) if up is DENSE else crit(x, y)
+    loss.backward(y if up is DENSE else up)
     return loss
+
+
+DENSE = object()
 
 
 def try_capture(crit, sets, up):
@@ -300,8 +306,7 @@ def try_capture(crit, sets, up):
             x.grad = None
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                loss = crit(x, y)
-                loss.backward(up)
+                loss = step_eager(crit, x, y, up)
             graphs.append((g, loss))
         torch.cuda.synchronize()
         return graphs
@@ -388,7 +393,40 @@ def direct_calls(wl, sets, device):
                 P(xs[i]), P(new_labels[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(),
                 _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255, 0.0, 0, st))
         return fwd, rescale
+    if wl.kind == "taylor":
+        outs = [torch.empty_like(x) for x in xs]
+        fwd = lambda i: _cabi.check(lib.b200_taylor_softmax_forward(P(xs[i]), P(outs[i]), n, c, m, dt, 2, 1, st))
+        bwd = lambda i: _cabi.check(lib.b200_taylor_softmax_backward(P(ys[i]), P(xs[i]), P(grads[i]), n, c, m, dt, 2, 1, st))
+        return fwd, bwd
+    if wl.kind == "pc_softmax":
+        w = torch.tensor(wl.proportions(), dtype=torch.float32, device=device)
+        losses = [torch.empty_like(y, dtype=xs[0].dtype) for y in ys]
+        cnts = [_cabi.new_record(device) for _ in sets]
+
+        def fwd(i):
+            _cabi.check(lib.b200_count_valid(P(ys[i]), n * m, 255, P(cnts[i]), P(ws), ws.numel(), st))
+            _cabi.check(lib.b200_pc_softmax_ce_scaled(P(xs[i]), P(ys[i]), P(w), P(losses[i]), P(grads[i]),
+                                                      _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255, st))
+        return fwd, rescale
     stem, hyper, ign = {"lsr": ("lsr", 0.1, 255), "lsr_rows": ("lsr", 0.1, -100), "lmargin": ("lmargin", 0.3, 255)}[wl.kind]
+    if wl.reduction == 'none':
+        # per-pixel losses out, a per-pixel upstream gradient in: the separate kernels
+        px = [torch.empty_like(y, dtype=xs[0].dtype) for y in ys]
+        upx = wl.upstream_tensor(device).to(xs[0].dtype)
+        if lib.b200_softmax_stats_path(P(xs[0]), P(ys[0]), P(grads[0]), n, c, m, dt):
+            f_fwd, f_bwd = getattr(lib, "b200_%s_forward_ex" % stem), getattr(lib, "b200_%s_backward_ex" % stem)
+            stats = [torch.empty((n * m, 4), dtype=torch.float32, device=device) for _ in sets]
+            fwd = lambda i: _cabi.check(f_fwd(P(xs[i]), P(ys[i]), P(px[i]), None, None, 0, P(stats[i]),
+                                              n, c, m, dt, ign, hyper, st))
+            bwd = lambda i: _cabi.check(f_bwd(P(xs[i]), P(ys[i]), P(stats[i]), P(upx), 2, None, P(grads[i]),
+                                              n, c, m, dt, ign, hyper, st))
+            for i in range(len(sets)):
+                fwd(i)
+            return fwd, bwd
+        f_fwd, f_bwd = getattr(lib, "b200_%s_forward" % stem), getattr(lib, "b200_%s_backward" % stem)
+        fwd = lambda i: _cabi.check(f_fwd(P(xs[i]), P(ys[i]), P(px[i]), None, None, 0, n, c, m, dt, ign, hyper, st))
+        bwd = lambda i: _cabi.check(f_bwd(P(xs[i]), P(ys[i]), P(upx), 2, None, P(grads[i]), n, c, m, dt, ign, hyper, st))
+        return fwd, bwd
     if wl.fused_softmax():
         # the module's training step: count of valid labels, then ONE pass over the logits that sums
         # the loss and writes the final gradient; backward is the rescale kernel (upstream gradient 1)
@@ -484,7 +522,8 @@ def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e, with_ent
         kernels = time_entries(wl, sets, device, args, peak)
         check_all_status(device)
         return {"workload": wl.desc, "shape": list(wl.shape), "kernels_only": True, "kernels": kernels}
-    up = None if wl.upstream == 1.0 else torch.tensor(float(wl.upstream), device=device)
+    up = DENSE if wl.kind == "taylor" else wl.upstream_tensor(device)
+    scalar_loss = wl.kind != "taylor" and wl.reduction != 'none'
 
     def barrier():
         if world > 1:
@@ -576,7 +615,7 @@ def measure_workload(wl, args, device, world, rank, with_cpu, with_e2e, with_ent
 
     # ---- end to end from pinned host memory (eager, public module API)
     e2e = None
-    if with_e2e:
+    if with_e2e and scalar_loss:
         hx, hy = host0[0].pin_memory(), host0[1].pin_memory()
         dx = torch.empty_like(sets[0][0]).detach().requires_grad_(True)
         dy = torch.empty_like(sets[0][1])

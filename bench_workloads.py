@@ -13,18 +13,19 @@ import torch
 
 
 class Workload:
-    def __init__(self, name, cfg, shape, dtype, desc, cpu_sample_items, kind=None, upstream=1.0):
+    def __init__(self, name, cfg, shape, dtype, desc, cpu_sample_items, kind=None, upstream=1.0, reduction='mean'):
         self.name, self.cfg, self.shape, self.dtype, self.desc = name, cfg, shape, dtype, desc
         self.cpu_sample_items = cpu_sample_items     # batch items timed on the CPU baseline
         self.kind = kind or name                     # which loss / kernel family (variants share one)
         self.upstream = upstream                     # d(objective)/d(loss) handed to backward
+        self.reduction = reduction                   # 'none': per-pixel losses out, a per-pixel upstream tensor in
 
     def with_items(self, items, note=None):
         """The same workload with another batch size (reduced cases for profiler captures, and a
         rank's shard of the global batch in multi-GPU runs)."""
         return Workload(self.name, self.cfg, (items,) + tuple(self.shape[1:]), self.dtype,
                         self.desc + (note or " [batch %d]" % items), min(self.cpu_sample_items, items),
-                        self.kind, self.upstream)
+                        self.kind, self.upstream, self.reduction)
 
     @property
     def elems(self):
@@ -54,10 +55,16 @@ class Workload:
             # on this workload's random logits: two 16-byte scatter passes, three histogram reads,
             # the 12-byte Jaccard pass) is data dependent and not counted.
             return 20 * e + 8 * p
+        if self.kind == "taylor":
+            return 2 * s * e                 # input read, output written
+        if self.kind == "pc_softmax":
+            # label count (8P), then one launch: logits and labels read, per-pixel loss and FINAL
+            # gradient written; the sum of the per-pixel losses (4P read) is torch's
+            return 2 * s * e + 16 * p + 2 * s * p
         if self.fused_softmax():
             # label count (8P), then the fused step: logits read, gradient written, labels read
             return 2 * s * e + 16 * p
-        return s * e + 8 * p
+        return s * e + 8 * p + (s * p if self.reduction == 'none' else 0)
 
     def bytes_backward(self):
         # (with many classes backward also reads 16 bytes of saved statistics per pixel: 0.1 byte per
@@ -69,13 +76,16 @@ class Workload:
             return 0 if self.upstream == 1.0 else 2 * s * e
         if self.kind == "lovasz":
             return 12 * e + 8 * p
-        if self.kind == "ohem" or self.fused_softmax():
+        if self.kind == "taylor":
+            return 3 * s * e                 # upstream gradient and input read, gradient written
+        if self.kind in ("ohem", "pc_softmax") or self.fused_softmax():
             return 0                         # upstream gradient 1: the rescale kernel has nothing to do
-        return 2 * s * e + 8 * p
+        return 2 * s * e + 8 * p + (s * p if self.reduction == 'none' else 0)
 
     def fused_softmax(self):
         """The softmax workloads run the fused training step unless B200_SOFTMAX_FUSED=0."""
-        return self.kind in ("lsr", "lsr_rows", "lmargin") and os.environ.get("B200_SOFTMAX_FUSED", "1") != "0"
+        return self.kind in ("lsr", "lsr_rows", "lmargin") and self.reduction != 'none' and \
+            os.environ.get("B200_SOFTMAX_FUSED", "1") != "0"
 
     def bytes_step(self):
         return self.bytes_forward() + self.bytes_backward()
@@ -85,6 +95,10 @@ class Workload:
             return "b200_focal_forward_backward_reduced", "b200_rescale_gradient"
         if self.kind == "ohem":
             return "b200_ohem_label+b200_count_valid+b200_lsr_forward_backward_reduced", "b200_rescale_gradient"
+        if self.kind == "taylor":
+            return "b200_taylor_softmax_forward", "b200_taylor_softmax_backward"
+        if self.kind == "pc_softmax":
+            return "b200_count_valid+b200_pc_softmax_ce_scaled", "b200_rescale_gradient"
         if self.fused_softmax():
             stem = "lmargin" if self.kind == "lmargin" else "lsr"
             return "b200_count_valid+b200_%s_forward_backward_reduced" % stem, "b200_rescale_gradient"
@@ -105,7 +119,9 @@ class Workload:
             logits = torch.randn(shape, **kw) * math.sqrt(3.0)
             labels = (torch.rand(shape, **kw) < 0.1).float()
             return logits, labels
-        if self.kind == "lsr":
+        if self.kind == "taylor":
+            return torch.randn(shape, **kw) * math.sqrt(2.0), torch.randn(shape, **kw)     # input, upstream gradient
+        if self.kind in ("lsr", "pc_softmax"):
             logits = torch.randn(shape, **kw) * math.sqrt(2.0)
             labels = torch.randint(0, shape[1], [n] + shape[2:], **kw)
             labels[torch.rand([n] + shape[2:], **kw) < 0.05] = 255
@@ -152,14 +168,30 @@ class Workload:
         if self.kind == "focal":
             return package.FocalLossV3(0.25, 2, 'mean', process_group=process_group)
         if self.kind == "lsr":
-            return package.LabelSmoothSoftmaxCEV3(0.1, 'mean', 255, process_group=process_group)
+            return package.LabelSmoothSoftmaxCEV3(0.1, self.reduction, 255, process_group=process_group)
         if self.kind == "lmargin":
-            return package.LargeMarginSoftmaxV3(0.3, 'mean', 255, process_group=process_group)
+            return package.LargeMarginSoftmaxV3(0.3, self.reduction, 255, process_group=process_group)
+        if self.kind == "taylor":
+            return package.LogTaylorSoftmaxV3(dim=1, n=2)
+        if self.kind == "pc_softmax":
+            return package.PCSoftmaxCrossEntropyV2(self.proportions(), 'mean', 255)
         if self.kind == "lovasz":
             return package.LovaszSoftmaxV3('mean', 255, per_image=True, process_group=process_group)
         if self.kind == "ohem":
             return package.OhemCELoss(0.7, None, 255)
         return package.LabelSmoothSoftmaxCEV3(0.1, 'mean', -100, process_group=process_group)
+
+    def upstream_tensor(self, device):
+        """What backward() is given: None (autograd's 1), a scalar, or with reduction 'none' a tensor
+        over the pixels."""
+        if self.reduction == 'none':
+            return torch.full((self.shape[0],) + tuple(self.shape[2:]), self.upstream / self.pixels, device=device)
+        return None if self.upstream == 1.0 else torch.tensor(float(self.upstream), device=device)
+
+    def proportions(self):
+        """Class proportions of the PC-softmax workload: a long-tailed training set."""
+        w = torch.arange(1, self.shape[1] + 1, dtype=torch.float64).reciprocal()
+        return (w / w.sum()).tolist()
 
     def oracle(self, oracle_module):
         """The CPU port's function for this workload: f(logits, labels) -> (loss, grad)."""
@@ -167,9 +199,15 @@ class Workload:
         if self.kind == "focal":
             return lambda x, y: O.focal_loss(x, y, 0.25, 2.0, 'mean')
         if self.kind == "lsr":
-            return lambda x, y: O.label_smooth_ce(x, y, 0.1, 255, 'mean')
+            return lambda x, y: O.label_smooth_ce(x, y, 0.1, 255, self.reduction)
         if self.kind == "lmargin":
-            return lambda x, y: O.large_margin_softmax(x, y, 0.3, 255, 'mean')
+            return lambda x, y: O.large_margin_softmax(x, y, 0.3, 255, self.reduction)
+        if self.kind == "taylor":
+            from oracle import taylor as OT
+            return lambda x, g: OT.taylor_softmax(x, 1, 2, True, upstream=g)
+        if self.kind == "pc_softmax":
+            from oracle import pc_softmax as OP
+            return lambda x, y: OP.pc_softmax_ce(x, y, self.proportions(), 255, 'mean')
         if self.kind == "lovasz":
             return lambda x, y: O.lovasz_softmax(x, y, 255, 'mean', per_image=True)
         if self.kind == "ohem":
@@ -197,9 +235,22 @@ WORKLOADS = {
     "focal_up2": Workload("focal_up2", 2, (16, 1, 1024, 1024), torch.float32,
                           "FocalLossV3 fp32 [16,1,1024,1024], alpha 0.25 gamma 2, mean, upstream gradient 2.0 "
                           "(the gradient rescale pass runs in full)", 16, kind="focal", upstream=2.0),
-    # not one of the five baseline configurations: the relabelling step in front of the loss
+    "lmargin_none": Workload("lmargin_none", 3, (8, 150, 512, 512), torch.float32,
+                             "LargeMarginSoftmaxV3 fp32 [8,150,512,512], 10% ignored, reduction 'none', per-pixel "
+                             "upstream gradient (the separate forward and backward kernels)", 1, kind="lmargin",
+                             reduction='none'),
+    "lsr_none": Workload("lsr_none", 1, (16, 19, 512, 512), torch.float32,
+                         "LabelSmoothSoftmaxCEV3 fp32 [16,19,512,512], 5% ignored, reduction 'none', per-pixel "
+                         "upstream gradient (the separate forward and backward kernels)", 16, kind="lsr",
+                         reduction='none'),
+    # not baseline configurations: the relabelling step in front of the loss, and the two other
+    # softmax variants of the reference on the shape of configuration 1
     "ohem": Workload("ohem", 6, (16, 19, 512, 512), torch.float32,
                      "OhemCELoss fp32 [16,19,512,512], thresh 0.7, n_min P/16, 97% easy pixels, 5% ignored", 4),
+    "taylor": Workload("taylor", 7, (16, 19, 512, 512), torch.float32,
+                       "LogTaylorSoftmaxV3 fp32 [16,19,512,512], dim 1, n 2, dense upstream gradient", 2),
+    "pc_softmax": Workload("pc_softmax", 8, (16, 19, 512, 512), torch.float32,
+                           "PCSoftmaxCrossEntropyV2 fp32 [16,19,512,512], 1/k class proportions, 5% ignored, mean", 2),
 }
 HEADLINE = "lmargin"        # the largest configuration that the baseline file shards over GPUs
 # multi-GPU runs: these split their one global batch over the ranks (strong scaling) ...

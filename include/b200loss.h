@@ -374,6 +374,13 @@ int b200_taylor_softmax_backward(const void *grad, const void *feat, void *grad_
 int b200_pc_softmax_ce(const void *logits, const int64_t *labels, const float *weight, void *losses,
                        void *grad_logits, int64_t N, int64_t C, int64_t M, int dtype,
                        int64_t ignore_index, void *stream);
+/* The same with the gradient divided by *denom (a device double, e.g. the count written by
+ * b200_count_valid; NULL: not divided): what 'mean' needs, so that the caller's backward has
+ * nothing left to do for an upstream gradient of 1 (the division the reference's backward
+ * makes with a tensor op, pc_softmax.py:108-110). */
+int b200_pc_softmax_ce_scaled(const void *logits, const int64_t *labels, const float *weight,
+                              void *losses, void *grad_logits, const void *denom, int64_t N,
+                              int64_t C, int64_t M, int dtype, int64_t ignore_index, void *stream);
 
 #ifdef __cplusplus
 }

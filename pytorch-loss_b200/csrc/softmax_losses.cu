@@ -2091,6 +2091,115 @@ inline bool fused_step_eligible(size_t es, const void *logits, const void *grads
            M < (int64_t(1) << 31) && N < (int64_t(1) << 31);
 }
 
+// Label-smooth training step for few channels (C <= CMAX, float32, M even, 8-byte aligned
+// pointers): a thread owns 2 adjacent pixels and keeps all their channels in registers, so the
+// logits are read once with 8-byte accesses and the gradient is written once -- no shared
+// memory, no barrier before the final reduction.  The label channel's gradient is a second
+// 4-byte store over the first one instead of a compare per channel.
+constexpr int kResidentThreads = 256;
+// EXACT: C == CMAX, the channel loops carry no predicate.
+template <int CMAX, bool EXACT>
+__global__ void __launch_bounds__(kResidentThreads, 2)
+lsr_resident_step_kernel(const SoftmaxParams prm) {
+    __shared__ double sh_red[64];
+    const float *x = static_cast<const float *>(prm.logits);
+    float *grads = static_cast<float *>(prm.grads);
+    const int C = EXACT ? CMAX : prm.k.C;
+    const int M = int(prm.M);                      // C * M < 2^31 (host check): 32-bit channel offsets
+    const int64_t groups_per_row = prm.M / 2;
+    const int64_t groups = prm.N * groups_per_row;
+    const int64_t stride = int64_t(gridDim.x) * kResidentThreads;
+    const float gs = uniform_grad_scale(nullptr, 0, prm.denom);
+    const float sumy_gs = prm.k.sumy * gs, neg_gs = prm.k.lb_neg * gs;
+    const float dpn = prm.k.lb_pos - prm.k.lb_neg;
+    constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+    float acc = 0.f, cnt = 0.f;
+    for (int64_t gi = int64_t(blockIdx.x) * kResidentThreads + threadIdx.x; gi < groups; gi += stride) {
+        const int64_t n = gi / groups_per_row, m0 = (gi % groups_per_row) * 2;
+        const int64_t base = n * prm.C * prm.M + m0;
+        const float *xb = x + base;
+        float2 xv[CMAX];
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j)
+            if (EXACT || j < C) xv[j] = __ldcs(reinterpret_cast<const float2 *>(xb + j * M));
+        const longlong2 lb2 = __ldcs(reinterpret_cast<const longlong2 *>(prm.labels + n * prm.M + m0));
+        const bool v0 = lb2.x != prm.ignore, v1 = lb2.y != prm.ignore;
+        // (labels outside [0, C) that are not the ignore value are undefined in the reference;
+        // here no channel takes the target term)
+        const int l0 = v0 ? int(lb2.x) : -1, l1 = v1 ? int(lb2.y) : -1;
+        float2 mx = make_float2(kNegInf, kNegInf), sx = make_float2(0.f, 0.f);
+        float xl0 = 0.f, xl1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j)
+            if (EXACT || j < C) {
+                mx = max2(mx, xv[j]);
+                sx = add2(sx, xv[j]);
+                if (j == l0) xl0 = xv[j].x;
+                if (j == l1) xl1 = xv[j].y;
+            }
+        const float2 nm2 = make_float2(-mx.x * kLog2e, -mx.y * kLog2e);
+        float2 s = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j)
+            if (EXACT || j < C) {
+                xv[j] = ex2_2(fma2(xv[j], splat2(kLog2e), nm2));      // e^{x - m} takes x's place
+                s = add2(s, xv[j]);
+            }
+        if (v0) {
+            acc += prm.k.sumy * fmaf(__log2f(s.x), kLn2, mx.x) - prm.k.lb_neg * sx.x - dpn * xl0;
+            cnt += 1.f;
+        }
+        if (v1) {
+            acc += prm.k.sumy * fmaf(__log2f(s.y), kLn2, mx.y) - prm.k.lb_neg * sx.y - dpn * xl1;
+            cnt += 1.f;
+        }
+        // g_j = (sumy e_j / s - y_j) gs with y_j = lb_neg, lb_pos at the label; zero at ignored pixels
+        const float2 a = make_float2(v0 ? __fdividef(sumy_gs, s.x) : 0.f, v1 ? __fdividef(sumy_gs, s.y) : 0.f);
+        const float2 b = make_float2(v0 ? -neg_gs : 0.f, v1 ? -neg_gs : 0.f);
+        const float dl = -dpn * gs;
+        float *gb = grads + base;
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j)
+            if (EXACT || j < C) {
+                float2 g = fma2(xv[j], a, b);
+                if (j == l0) g.x += dl;
+                if (j == l1) g.y += dl;
+                __stcs(reinterpret_cast<float2 *>(gb + j * M), g);
+            }
+    }
+    grid_reduce_finish(double(acc), double(cnt), prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
+}
+
+inline bool aligned8(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
+
+// The layouts lsr_resident_step_kernel takes, and the sizes it wins at: up to ~40 M elements its
+// short ramp (no tensor maps, no barrier set-up, no pipeline fill) beats the tile pipeline (label
+// count + step: 29.6 against 35.4 us at 10 M elements, 42.3 against 49.5 us at 20 M, level at
+// 80 M); larger inputs keep the pipeline.  Layouts
+// the pipeline cannot take (M even but not a multiple of 4, 8-byte alignment) come here at any size.
+inline bool resident_step_eligible(int kind, int dtype, const void *logits, const void *grads, const void *labels,
+                                   int64_t N, int64_t C, int64_t M, bool pipeline_ok) {
+    if (!(kind == kLSR && dtype == B200_F32 && N >= 1 && M >= 2 && M % 2 == 0 && C <= 32 &&
+          C * M < (int64_t(1) << 31) && aligned8(logits) && aligned8(grads) && aligned16(labels)))
+        return false;
+    return !pipeline_ok || N * C * M <= (int64_t(40) << 20);
+}
+
+int launch_resident_step(const SoftmaxParams &prm, cudaStream_t stream) {
+    const int64_t groups = prm.N * (prm.M / 2);
+    int64_t grid = (groups + kResidentThreads - 1) / kResidentThreads;
+    const int64_t cap = int64_t(sm_count()) * 2;        // all blocks resident: one reduction barrier per block
+    if (grid > cap) grid = cap;
+    const unsigned g = unsigned(grid);
+    cudaStream_t st = stream;
+    if (prm.C == 19) lsr_resident_step_kernel<19, true><<<g, kResidentThreads, 0, st>>>(prm);
+    else if (prm.C == 21) lsr_resident_step_kernel<21, true><<<g, kResidentThreads, 0, st>>>(prm);
+    else if (prm.C <= 8) lsr_resident_step_kernel<8, false><<<g, kResidentThreads, 0, st>>>(prm);
+    else if (prm.C <= 20) lsr_resident_step_kernel<20, false><<<g, kResidentThreads, 0, st>>>(prm);
+    else lsr_resident_step_kernel<32, false><<<g, kResidentThreads, 0, st>>>(prm);
+    return launch_status("label-smooth resident step launch");
+}
+
 template <int KIND>
 int fused_step(const char *who, const void *logits, const int64_t *labels, void *grad_logits, void *out,
                void *workspace, size_t workspace_bytes, const void *denom, int64_t N, int64_t C, int64_t M,
@@ -2106,7 +2215,9 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
         return B200_ERR_ARG;
     }
     const size_t es = dtype_size(dtype);
-    if (!fused_step_eligible(es, logits, grad_logits, labels, N, C, M)) {
+    const bool pipeline_ok = fused_step_eligible(es, logits, grad_logits, labels, N, C, M);
+    const bool resident = resident_step_eligible(KIND, dtype, logits, grad_logits, labels, N, C, M, pipeline_ok);
+    if (!resident && !pipeline_ok) {
         set_error("%s: this layout has no fused step (ask b200_softmax_fused_step_path first)", who);
         return B200_ERR_UNSUPPORTED;
     }
@@ -2123,6 +2234,7 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
     prm.ignore = ignore_index;
     prm.k = make_consts(KIND, C, hp);
     prm.defer = defer;
+    if (resident) return launch_resident_step(prm, static_cast<cudaStream_t>(stream));
     return dispatch<KIND, true>(prm, dtype, true, static_cast<cudaStream_t>(stream));
 }
 

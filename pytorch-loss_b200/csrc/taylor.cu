@@ -8,7 +8,9 @@
 // over the dimension `dim` of a tensor viewed as [N, C, M] (N = product of the leading
 // sizes, C = size(dim), M = product of the trailing sizes).
 //
-// How: the op streams x (and g) once from HBM and writes once; there is no exponential.
+// How: the op streams x (and g) once from HBM and writes once; there is no exponential.  The
+// log form takes the hardware logarithm (lg2.approx, a few ulp) per element and the library
+// one per position for log S.
 //   M > 1   few channels (<= 32 forward, <= 20 backward, float32): a thread owns 2 adjacent
 //           positions and keeps all their channels in registers -- one read, one write;
 //           otherwise a thread owns 4 adjacent positions along M (16-byte accesses when the layout
@@ -117,7 +119,7 @@ taylor_spatial_kernel(const TaylorParams p) {
             for (int v = 0; v < VEC; ++v) {
                 float f, d;
                 taylor_poly<ORDER, BWD>(xv[v], p, f, d);
-                if (!BWD) ov[v] = LOG ? logf(f) - logS[v] : f * invS[v];
+                if (!BWD) ov[v] = LOG ? __logf(f) - logS[v] : f * invS[v];
                 else if (LOG) ov[v] = d * (gv[v] / f - A[v] * invS[v]);
                 else ov[v] = d * invS[v] * (gv[v] - A[v] * invS[v]);
             }
@@ -129,7 +131,7 @@ taylor_spatial_kernel(const TaylorParams p) {
 // M > 1, few channels (C <= CMAX), float32: a thread owns 2 adjacent positions and keeps all their
 // channels in registers, so x (and g) are read once: 8-byte accesses, 256 B per warp and channel.
 template <bool BWD, bool LOG, int ORDER, int CMAX>
-__global__ void __launch_bounds__(kTaylorThreads, 2)
+__global__ void __launch_bounds__(kTaylorThreads, (!BWD && CMAX <= 20) ? 3 : 2)
 taylor_resident_kernel(const TaylorParams p) {
     const float *x = static_cast<const float *>(p.x);
     const float *g = static_cast<const float *>(p.g);
@@ -174,8 +176,8 @@ taylor_resident_kernel(const TaylorParams p) {
             if (j < C) {
                 float2 o;
                 if constexpr (!BWD) {
-                    o.x = LOG ? logf(xv[j].x) - logS.x : xv[j].x * invS.x;
-                    o.y = LOG ? logf(xv[j].y) - logS.y : xv[j].y * invS.y;
+                    o.x = LOG ? __logf(xv[j].x) - logS.x : xv[j].x * invS.x;
+                    o.y = LOG ? __logf(xv[j].y) - logS.y : xv[j].y * invS.y;
                 } else {
                     float fx, fy, dx, dy;
                     taylor_poly<ORDER, true>(xv[j].x, p, fx, dx);
@@ -225,7 +227,7 @@ taylor_rows_kernel(const TaylorParams p) {
             float f, d;
             taylor_poly<ORDER, BWD>(to_f32(xr[j]), p, f, d);
             float o;
-            if (!BWD) o = LOG ? logf(f) - logS : f * invS;
+            if (!BWD) o = LOG ? __logf(f) - logS : f * invS;
             else if (LOG) o = d * (to_f32(gr[j]) / f - A * invS);
             else o = d * invS * (to_f32(gr[j]) - A * invS);
             out[r * p.C + j] = from_f32<T>(o);
@@ -255,6 +257,7 @@ int launch_taylor(const TaylorParams &p, cudaStream_t stream) {
             const int64_t cap2 = int64_t(sm_count()) * 2 * 8;
             if (grid2 > cap2) grid2 = cap2;
             if (p.C <= 8) taylor_resident_kernel<BWD, LOG, ORDER, 8><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
+            else if (!BWD && p.C <= 20) taylor_resident_kernel<false, LOG, ORDER, 20><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
             else taylor_resident_kernel<BWD, LOG, ORDER, kSmall><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
             return launch_status("taylor softmax resident kernel launch");
         }

@@ -42,16 +42,27 @@ def _prep(logits, labels):
     return dev, logits, labels.contiguous(), n, c, m, _cabi.dtype_code(logits, allow_f64=True)
 
 
-def forward_per_pixel(kind, logits, labels, ignore_index, hyper):
-    """Per-pixel losses [N, *spatial] in the logits' dtype, zeros at ignored pixels."""
+def forward_per_pixel(kind, logits, labels, ignore_index, hyper, want_stats=False):
+    """Per-pixel losses [N, *spatial] in the logits' dtype, zeros at ignored pixels.  Returns
+    (losses, logits, labels, statistics): the statistics (16 bytes per pixel; only when asked for
+    and only for layouts with many classes, else None) let backward skip its own softmax pass."""
     dev, logits, labels, n, c, m, dt = _prep(logits, labels)
     lib = _cabi.load_library()
     losses = torch.empty(labels.shape, dtype=logits.dtype, device=dev)
+    stats = None
+    if want_stats and n * m > 0 and lib.b200_softmax_stats_path(_cabi.ptr(logits), _cabi.ptr(labels), None,
+                                                                n, c, m, dt):
+        stats = torch.empty((n * m, 4), dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        _cabi.check(getattr(lib, _ENTRY[kind][0])(
-            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), None, None, 0,
-            n, c, m, dt, int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
-    return losses, logits, labels
+        if stats is not None:
+            _cabi.check(getattr(lib, _ENTRY_EX[kind][0])(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), None, None, 0, _cabi.ptr(stats),
+                n, c, m, dt, int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+        else:
+            _cabi.check(getattr(lib, _ENTRY[kind][0])(
+                _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(losses), None, None, 0,
+                n, c, m, dt, int(ignore_index), float(hyper), _cabi.stream_ptr(dev)))
+    return losses, logits, labels, stats
 
 
 def forward_reduced(kind, logits, labels, ignore_index, hyper, want_losses=False, exchange=None,

@@ -21,15 +21,16 @@ class LSRCrossEntropyFunctionV3(torch.autograd.Function):
     @staticmethod
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
     def forward(ctx, logits, labels, lb_smooth, lb_ignore):
-        losses, logits, labels = _sf.forward_per_pixel("lsr", logits, labels, lb_ignore, lb_smooth)
-        ctx.variables = logits, labels, lb_ignore, lb_smooth
+        losses, logits, labels, stats = _sf.forward_per_pixel("lsr", logits, labels, lb_ignore, lb_smooth,
+                                                              want_stats=ctx.needs_input_grad[0])
+        ctx.variables = logits, labels, lb_ignore, lb_smooth, stats
         return losses
 
     @staticmethod
     @amp.custom_bwd(device_type='cuda')
     def backward(ctx, grad_output):
-        logits, labels, lb_ignore, lb_smooth = ctx.variables
-        grad = _sf.backward("lsr", logits, labels, grad_output, None, lb_ignore, lb_smooth)
+        logits, labels, lb_ignore, lb_smooth, stats = ctx.variables
+        grad = _sf.backward("lsr", logits, labels, grad_output, None, lb_ignore, lb_smooth, stats)
         return grad, None, None, None
 
 

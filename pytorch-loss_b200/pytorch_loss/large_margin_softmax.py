@@ -12,20 +12,22 @@ from . import _softmax_family as _sf
 
 
 class LargeMarginSoftmaxFuncV3(torch.autograd.Function):
-    """Per-pixel losses; backward recomputes (reference large_margin_softmax.py:146-169)."""
+    """Per-pixel losses; backward recomputes, from 16 bytes of saved statistics per pixel where
+    the layout has many classes (reference large_margin_softmax.py:146-169)."""
 
     @staticmethod
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
     def forward(ctx, logits, labels, lam=0.3, ignore_index=255):
-        losses, logits, labels = _sf.forward_per_pixel("lmargin", logits, labels, ignore_index, lam)
-        ctx.variables = logits, labels, lam, ignore_index
+        losses, logits, labels, stats = _sf.forward_per_pixel("lmargin", logits, labels, ignore_index, lam,
+                                                              want_stats=ctx.needs_input_grad[0])
+        ctx.variables = logits, labels, lam, ignore_index, stats
         return losses
 
     @staticmethod
     @amp.custom_bwd(device_type='cuda')
     def backward(ctx, grad_output):
-        logits, labels, lam, ignore_index = ctx.variables
-        grads = _sf.backward("lmargin", logits, labels, grad_output, None, ignore_index, lam)
+        logits, labels, lam, ignore_index, stats = ctx.variables
+        grads = _sf.backward("lmargin", logits, labels, grad_output, None, ignore_index, lam, stats)
         return grads, None, None, None
 
 
@@ -38,18 +40,18 @@ class LargeMarginSoftmaxFuncV3FB(torch.autograd.Function):
     @staticmethod
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
     def forward(ctx, logits, labels, lam=0.3, ignore_index=255):
-        rec, losses, logits, labels = _sf.forward_reduced("lmargin", logits, labels, ignore_index, lam,
-                                                          want_losses=True)
+        rec, losses, logits, labels, stats = _sf.forward_reduced("lmargin", logits, labels, ignore_index, lam,
+                                                                 want_losses=True, want_stats=True)
         valid_cnt = rec[:4].view(torch.float64)[1:2].to(torch.int64)
-        ctx.variables = logits, labels, lam, ignore_index
+        ctx.variables = logits, labels, lam, ignore_index, stats
         ctx.mark_non_differentiable(valid_cnt)
         return losses, valid_cnt
 
     @staticmethod
     @amp.custom_bwd(device_type='cuda')
     def backward(ctx, grad_output, grad_cnt):
-        logits, labels, lam, ignore_index = ctx.variables
-        grads = _sf.backward("lmargin", logits, labels, grad_output, None, ignore_index, lam)
+        logits, labels, lam, ignore_index, stats = ctx.variables
+        grads = _sf.backward("lmargin", logits, labels, grad_output, None, ignore_index, lam, stats)
         return grads, None, None, None
 
 

@@ -13,18 +13,22 @@ import torch
 import torch.nn as nn
 import torch.amp as amp
 
-from . import _cabi
+from . import _cabi, _softmax_family
 
 
 def _weights(lb_proportion, num_classes, device):
+    if isinstance(lb_proportion, torch.Tensor) and lb_proportion.device == device and \
+            lb_proportion.dtype == torch.float32 and lb_proportion.numel() == num_classes:
+        return lb_proportion.reshape(-1).contiguous()         # (the module's cached copy: no transfer)
     w = torch.as_tensor(lb_proportion, dtype=torch.float32).reshape(-1)
     if w.numel() != num_classes:
         raise RuntimeError("lb_proportion has %d entries for %d classes" % (w.numel(), num_classes))
     return w.to(device)
 
 
-def pc_softmax_ce(logits, labels, lb_proportion, ignore_index, want_grad=True):
-    """(per-pixel losses [N, *spatial], unscaled gradient like logits or None), logits' dtype."""
+def pc_softmax_ce(logits, labels, lb_proportion, ignore_index, want_grad=True, denom=None):
+    """(per-pixel losses [N, *spatial], gradient like logits or None), logits' dtype.  `denom`: a
+    device double the gradient is divided by inside the kernel (the valid-pixel count for 'mean')."""
     dev = _cabi.require_cuda(logits, labels)
     n, c, m = _cabi.split_shape(logits, labels)
     logits, labels = logits.contiguous(), labels.contiguous()
@@ -32,10 +36,21 @@ def pc_softmax_ce(logits, labels, lb_proportion, ignore_index, want_grad=True):
     losses = torch.empty(labels.shape, dtype=logits.dtype, device=dev)
     grads = torch.empty_like(logits) if want_grad else None
     with torch.cuda.device(dev):
-        _cabi.check(_cabi.load_library().b200_pc_softmax_ce(
+        _cabi.check(_cabi.load_library().b200_pc_softmax_ce_scaled(
             _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(w), _cabi.ptr(losses), _cabi.ptr(grads),
+            None if denom is None else _cabi._vp(denom.data_ptr()),
             n, c, m, _cabi.dtype_code(logits), int(ignore_index), _cabi.stream_ptr(dev)))
     return losses, grads
+
+
+def _rescale(grads, grad_output):
+    """grads *= grad_output (a scalar) in place; the kernel leaves at once when it is 1."""
+    g = grad_output.to(torch.float32).reshape(-1)[:1].contiguous()
+    with torch.cuda.device(grads.device):
+        _cabi.check(_cabi.load_library().b200_rescale_gradient(
+            _cabi.ptr(grads), _cabi.ptr(g), None, grads.numel(), _cabi.dtype_code(grads),
+            _cabi.stream_ptr(grads.device)))
+    return grads
 
 
 class PCSoftmaxCrossEntropyFunction(torch.autograd.Function):
@@ -45,11 +60,17 @@ class PCSoftmaxCrossEntropyFunction(torch.autograd.Function):
     @staticmethod
     @amp.custom_fwd(cast_inputs=torch.float32, device_type='cuda')
     def forward(ctx, logits, label, lb_proportion, reduction, ignore_index):
-        losses, grads = pc_softmax_ce(logits, label, lb_proportion, ignore_index, ctx.needs_input_grad[0])
-        n_valid = (label != ignore_index).sum()
-        ctx.vars = grads, reduction, n_valid
+        # 'mean': the valid pixels are counted first (labels only), so that the gradient leaves the
+        # kernel already divided and backward has nothing to do for an upstream gradient of 1
+        n_valid = None
+        if reduction == 'mean':
+            _cabi.require_cuda(logits, label)
+            n_valid = _softmax_family.count_valid(label, ignore_index)
+        losses, grads = pc_softmax_ce(logits, label, lb_proportion, ignore_index, ctx.needs_input_grad[0], n_valid)
+        ctx.vars = logits, label, lb_proportion, ignore_index, reduction, n_valid
+        ctx.grads = grads
         if reduction == 'mean':               # (half inputs: the sum is taken in fp32)
-            return losses.sum(dtype=torch.float32) / n_valid
+            return losses.sum(dtype=torch.float32) / n_valid[0].to(torch.float32)
         if reduction == 'sum':
             return losses.sum(dtype=torch.float32)
         return losses
@@ -57,14 +78,13 @@ class PCSoftmaxCrossEntropyFunction(torch.autograd.Function):
     @staticmethod
     @amp.custom_bwd(device_type='cuda')
     def backward(ctx, grad_output):
-        grads, reduction, n_valid = ctx.vars
-        if reduction == 'mean':
-            grad = grads * (grad_output / n_valid)
-        elif reduction == 'sum':
-            grad = grads * grad_output
-        else:
-            grad = grads * grad_output.unsqueeze(1)
-        return grad, None, None, None, None
+        logits, label, lb_proportion, ignore_index, reduction, n_valid = ctx.vars
+        grads, ctx.grads = ctx.grads, None
+        if grads is None:                     # a second trip through the graph: the first scaled them in place
+            _, grads = pc_softmax_ce(logits, label, lb_proportion, ignore_index, True, n_valid)
+        if reduction in ('mean', 'sum'):
+            return _rescale(grads, grad_output), None, None, None, None
+        return grads * grad_output.unsqueeze(1), None, None, None, None
 
 
 class PCSoftmaxCrossEntropyV2(nn.Module):
@@ -79,7 +99,12 @@ class PCSoftmaxCrossEntropyV2(nn.Module):
         self.lb_proportion = lb_proportion
         self.reduction = reduction
         self.ignore_index = ignore_index
+        self._on_device = {}          # device -> float32 tensor of the proportions (sent once)
 
     def forward(self, logits, label):
+        w = self._on_device.get(logits.device)
+        if w is None and logits.is_cuda:
+            w = torch.as_tensor(self.lb_proportion, dtype=torch.float32).reshape(-1).to(logits.device)
+            self._on_device[logits.device] = w
         return PCSoftmaxCrossEntropyFunction.apply(
-            logits, label, self.lb_proportion, self.reduction, self.ignore_index)
+            logits, label, self.lb_proportion if w is None else w, self.reduction, self.ignore_index)

@@ -65,3 +65,26 @@ def test_fp16_per_pixel_upstream_gradient_and_errors():
         P.PCSoftmaxCrossEntropyV2([0.5, 0.5])(torch.randn(2, 3, 4, 4).cuda(), torch.zeros(2, 4, 4, dtype=torch.int64).cuda())
     with pytest.raises(RuntimeError):
         P.PCSoftmaxCrossEntropyV2([0.5, 0.5])(torch.randn(2, 2, 4, 4), torch.zeros(2, 4, 4, dtype=torch.int64))
+
+
+@pytest.mark.parametrize("c", [8, 20, 32, 33])
+def test_scalar_upstream_gradient_and_second_backward(c):
+    """'mean' leaves the kernel divided by the valid count; backward rescales in place once, and a
+    second trip through the graph recomputes instead of scaling twice."""
+    import pytorch_loss as P
+    from oracle import pc_softmax as PC
+    g = torch.Generator().manual_seed(720 + c)
+    logits = torch.randn(2, c, 10, 12, generator=g) * 2.0
+    labels = labels_with_ignores(g, (2, 10, 12), c, 255, 0.2)
+    prop = torch.rand(c, generator=g) + 0.05
+    prop = (prop / prop.sum()).tolist()
+    for reduction in ("mean", "sum"):
+        want_loss, want_grad = PC.pc_softmax_ce(logits, labels, prop, 255, reduction)
+        x = logits.cuda().requires_grad_(True)
+        loss = P.PCSoftmaxCrossEntropyV2(prop, reduction, 255)(x, labels.cuda())
+        (loss * 3.0).backward(retain_graph=True)
+        assert_loss_close(loss.detach(), want_loss, atol=1e-7)
+        assert_grad_close(x.grad, want_grad * 3.0)
+        x.grad = None
+        (loss * -0.5).backward()
+        assert_grad_close(x.grad, want_grad * -0.5)
