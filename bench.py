@@ -73,7 +73,8 @@ def measured_traffic(wl):
     proportion to the batch), or (None, None) for a workload without a capture."""
     try:
         with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as fh:
-            rec = json.load(fh)["workloads"][wl.name]
+            recs = json.load(fh)["workloads"]
+        rec = recs.get(wl.name) or recs[wl.kind]       # (reduction 'none' variants: the separate kernels of their kind)
         key = "fused" if (wl.fused_softmax() or wl.kind not in ("lsr", "lsr_rows", "lmargin")) else "separate"
         f, b = rec[key]
         return f * wl.elems, b * wl.elems
@@ -86,8 +87,8 @@ def traffic_from_ncu(args):
     `bench.py --workload W --items I --kernels-only` run (metrics dram__bytes_read.sum,
     dram__bytes_write.sum; L = warm-up + timed launches of each entry point) into the workload's
     entry of profiles/dram_traffic.json: DRAM bytes per logit element of the forward and of the
-    backward entry point.  Kernels of the backward entry: the gradient rescale and the Lovasz
-    backward; everything else of this library belongs to the forward entry (other kernels are skipped)."""
+    backward entry point.  Kernels of the backward entry: the gradient rescale, the Lovasz
+    and the Taylor backward; everything else of this library belongs to the forward entry (other kernels are skipped)."""
     import csv
     import re
     wl = BW.WORKLOADS[args.workload].with_items(args.items) if args.items else BW.WORKLOADS[args.workload]
@@ -101,7 +102,9 @@ def traffic_from_ncu(args):
         name = r[col["Kernel Name"]]
         if "b200::" not in name:                      # torch's own kernels (input generation, fills)
             continue
-        bwd = re.search(r"rescale_kernel|lovasz_pair_kernel<\(?(bool\))?1|lovasz_tile_kernel<\(?(bool\))?1", name) is not None
+        bwd = re.search(r"rescale_kernel|lovasz_pair_kernel<\(?(bool\))?1|lovasz_tile_kernel<\(?(bool\))?1|"
+                        r"taylor_resident_kernel<\(?(bool\))?1|taylor_spatial_kernel<[^,]+, [^,]+, \(?(bool\))?1|"
+                        r"taylor_rows_kernel<[^,]+, \(?(bool\))?1", name) is not None
         sums[1 if bwd else 0] += float(r[col["Metric Value"]].replace(",", "")) * scale[r[col["Metric Unit"]]]
     per_elem = [round(v / args.launches / wl.elems, 3) for v in sums]
     path = os.path.join(ROOT, "profiles", "dram_traffic.json")
