@@ -394,7 +394,7 @@ def direct_calls(wl, sets, device):
             _cabi.check(lib.b200_count_valid(P(new_labels[i]), n * m, 255, P(cnts[i]), P(ws), ws.numel(), st))
             _cabi.check(lib.b200_lsr_forward_backward_reduced(
                 P(xs[i]), P(new_labels[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(),
-                _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255, 0.0, 0, st))
+                _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255, 0.0, _cabi.STEP_AFTER_COUNT, st))
         return fwd, rescale
     if wl.kind == "taylor":
         outs = [torch.empty_like(x) for x in xs]
@@ -441,7 +441,7 @@ def direct_calls(wl, sets, device):
         def fwd(i):
             _cabi.check(lib.b200_count_valid(P(ys[i]), n * m, ign, P(cnts[i]), P(ws), ws.numel(), st))
             _cabi.check(f_step(P(xs[i]), P(ys[i]), P(grads[i]), P(recs[i]), P(ws), ws.numel(),
-                               _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, ign, hyper, 0, st))
+                               _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, ign, hyper, _cabi.STEP_AFTER_COUNT, st))
         return fwd, rescale
     one = torch.ones(1, dtype=torch.float32, device=device)
     if lib.b200_softmax_stats_path(P(xs[0]), P(ys[0]), P(grads[0]), n, c, m, dt):

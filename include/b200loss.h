@@ -102,7 +102,15 @@ int b200_focal_forward_backward_predicted(const void *logits, const void *labels
                                           float gamma, float alpha, int defer, void *stream);
 int b200_rescale_gradient(void *grad, const float *grad_out, const float *correction, int64_t E, int dtype,
                           void *stream);
-/* `defer` (fused steps; only acts on a workspace with ranks attached, see "cross-GPU sum"): the
+/* Bits of the `defer` argument of the fused steps. */
+#define B200_STEP_DEFER 1        /* post the sums to the peers, collect later (below) */
+#define B200_STEP_AFTER_COUNT 2  /* softmax steps with a `denom`: b200_count_valid wrote it and is the
+                                  * operation directly in front of this call on the stream, so the step's
+                                  * kernel may start under the count's tail (programmatic dependent launch:
+                                  * it fills its pipeline from the logits, which the count does not write,
+                                  * and waits for the count before it reads *denom).  Do not set it when
+                                  * anything else was enqueued in between. */
+/* `defer` bit B200_STEP_DEFER (fused steps; only acts on a workspace with ranks attached, see "cross-GPU sum"): the
  * kernel posts this rank's [sum, count] to the peers and returns without waiting for theirs; the
  * record's float fields stay NaN (and *correction unwritten) until a later call on the same
  * stream completes it:

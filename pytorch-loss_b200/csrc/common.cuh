@@ -3,6 +3,7 @@
 // reducing forward kernel, and thin wrappers over the sm_100a bulk-async (TMA)
 // and mbarrier PTX used to stage tiles in shared memory.
 #pragma once
+#include <utility>
 
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -172,6 +173,32 @@ __device__ __forceinline__ void block_sum2(double &a, double &b, double *sh) {
         a = warp_sum(a);
         b = warp_sum(b);
     }
+}
+
+// ---- programmatic dependent launch (a kernel that starts under the tail of the one in front)
+// The dependent may only touch what the kernel in front produces after pdl_wait(): it returns
+// when that grid has completed and its writes are visible (at once in a plain launch).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The kernel in front: its dependents may be scheduled from now on (once every block has said so
+// or exited); a no-op when nothing depends on it this way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// kernel<<<grid, block, smem, stream>>>(args...), optionally as a programmatic dependent of the
+// operation in front of it on the stream.
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          bool dependent, Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 // ---- cross-GPU messages (see ExchangeSlot).  All three functions are called by ONE full warp.

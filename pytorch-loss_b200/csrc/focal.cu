@@ -507,7 +507,7 @@ extern "C" int b200_focal_forward_backward_reduced(const void *logits, const voi
     prm.gamma = gamma;
     prm.alpha = alpha;
     prm.host_scale = grad_scale;
-    prm.defer = defer;
+    prm.defer = defer & B200_STEP_DEFER;
     return dispatch_focal<kFwdBwd, true>(prm, dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -544,7 +544,7 @@ extern "C" int b200_focal_forward_backward_predicted(const void *logits, const v
     prm.E = E;
     prm.gamma = gamma;
     prm.alpha = alpha;
-    prm.defer = defer;
+    prm.defer = defer & B200_STEP_DEFER;
     return dispatch_focal<kFwdBwd, true>(prm, dtype, static_cast<cudaStream_t>(stream));
 }
 

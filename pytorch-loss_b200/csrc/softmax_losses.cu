@@ -51,6 +51,7 @@ struct SoftmaxParams {
     int stages;              // ring depth of the pipelined kernels
     int64_t tiles_per_image, total_tiles;
     int defer;               // cross-GPU sum of the fused step: post only (see grid_reduce_finish)
+    int after_count;         // fused step launched as a programmatic dependent of the label count
 };
 
 // ------------------------------------------------------------------ tile regime
@@ -546,6 +547,9 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
         T *losses = static_cast<T *>(prm.losses);
         const LossConsts kc = prm.k;
         float gscale = 1.f;
+        // fused step: the divisor comes from the label count, which may still be running (the
+        // loader warp above is already filling the ring)
+        if (BWD && REDUCE) pdl_wait();
         if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
         float acc32 = 0.f;
         int cnt32 = 0;
@@ -1350,6 +1354,7 @@ rows_pipe_kernel(const SoftmaxParams prm) {
         T *losses = static_cast<T *>(prm.losses);
         const LossConsts kc = prm.k;
         float gscale = 1.f;
+        if (BWD && REDUCE) pdl_wait();          // (see tile_pair_kernel)
         if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
         int k = 0;
         for (int64_t r = first; r < prm.N; r += stride, ++k) {
@@ -1883,7 +1888,8 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             if (BWD && !encode_tensor_map(&map_out, dtype, prm.grads, 3, dims, strides, box)) return B200_ERR_LAUNCH;
             auto kern = tile_pair_kernel<T, KIND, BWD, REDUCE>;
             if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
-            kern<<<dim3(unsigned(grid)), kTileBlock, smem, stream>>>(prm, map_in, map_out);
+            launch_kernel(kern, dim3(unsigned(grid)), dim3(kTileBlock), smem, stream, BWD && REDUCE && prm.after_count,
+                          prm, map_in, map_out);
         } else {
             const size_t smem = 128 + tile_bytes + red_bytes;
             int per_sm = int((220 * 1024) / (smem + 1024));
@@ -1942,7 +1948,7 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             if (grid > kMaxPartials) grid = kMaxPartials;
             auto kern = rows_pipe_kernel<T, KIND, BWD, REDUCE>;
             if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
-            kern<<<dim3(unsigned(grid)), kRowsBlock, smem, stream>>>(prm);
+            launch_kernel(kern, dim3(unsigned(grid)), dim3(kRowsBlock), smem, stream, BWD && REDUCE && prm.after_count, prm);
         } else {
             const size_t smem = 128 + row_al;
             int per_sm = int((220 * 1024) / (smem + 2048));
@@ -2109,6 +2115,7 @@ lsr_resident_step_kernel(const SoftmaxParams prm) {
     const int64_t groups_per_row = prm.M / 2;
     const int64_t groups = prm.N * groups_per_row;
     const int64_t stride = int64_t(gridDim.x) * kResidentThreads;
+    pdl_wait();                                    // the divisor comes from the label count in front
     const float gs = uniform_grad_scale(nullptr, 0, prm.denom);
     const float sumy_gs = prm.k.sumy * gs, neg_gs = prm.k.lb_neg * gs;
     const float dpn = prm.k.lb_pos - prm.k.lb_neg;
@@ -2192,11 +2199,13 @@ int launch_resident_step(const SoftmaxParams &prm, cudaStream_t stream) {
     if (grid > cap) grid = cap;
     const unsigned g = unsigned(grid);
     cudaStream_t st = stream;
-    if (prm.C == 19) lsr_resident_step_kernel<19, true><<<g, kResidentThreads, 0, st>>>(prm);
-    else if (prm.C == 21) lsr_resident_step_kernel<21, true><<<g, kResidentThreads, 0, st>>>(prm);
-    else if (prm.C <= 8) lsr_resident_step_kernel<8, false><<<g, kResidentThreads, 0, st>>>(prm);
-    else if (prm.C <= 20) lsr_resident_step_kernel<20, false><<<g, kResidentThreads, 0, st>>>(prm);
-    else lsr_resident_step_kernel<32, false><<<g, kResidentThreads, 0, st>>>(prm);
+    const bool dep = prm.after_count != 0;
+    const dim3 gd(g), bd(kResidentThreads);
+    if (prm.C == 19) launch_kernel(lsr_resident_step_kernel<19, true>, gd, bd, 0, st, dep, prm);
+    else if (prm.C == 21) launch_kernel(lsr_resident_step_kernel<21, true>, gd, bd, 0, st, dep, prm);
+    else if (prm.C <= 8) launch_kernel(lsr_resident_step_kernel<8, false>, gd, bd, 0, st, dep, prm);
+    else if (prm.C <= 20) launch_kernel(lsr_resident_step_kernel<20, false>, gd, bd, 0, st, dep, prm);
+    else launch_kernel(lsr_resident_step_kernel<32, false>, gd, bd, 0, st, dep, prm);
     return launch_status("label-smooth resident step launch");
 }
 
@@ -2233,7 +2242,8 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
     prm.M = M;
     prm.ignore = ignore_index;
     prm.k = make_consts(KIND, C, hp);
-    prm.defer = defer;
+    prm.defer = defer & B200_STEP_DEFER;
+    prm.after_count = (denom != nullptr && (defer & B200_STEP_AFTER_COUNT)) ? 1 : 0;
     if (resident) return launch_resident_step(prm, static_cast<cudaStream_t>(stream));
     return dispatch<KIND, true>(prm, dtype, true, static_cast<cudaStream_t>(stream));
 }
@@ -2242,6 +2252,7 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
 __global__ void __launch_bounds__(256) count_valid_kernel(const int64_t *labels, int64_t P, int64_t ignore,
                                                           void *workspace, ReduceRecord *out) {
     __shared__ double sh[64];
+    pdl_launch_dependents();      // a fused step behind this kernel may start filling its pipeline
     const bool al = (reinterpret_cast<uintptr_t>(labels) & 15u) == 0;
     const int64_t nvec = al ? P / 2 : 0;
     const longlong2 *v = reinterpret_cast<const longlong2 *>(labels);

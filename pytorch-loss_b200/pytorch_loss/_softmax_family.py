@@ -158,16 +158,20 @@ def fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange, denom=
     rec = _cabi.new_record(dev)
     ws = exchange.workspace() if exchange is not None else _cabi.reduce_workspace(dev)
     st = _cabi.stream_ptr(dev)
-    if mean and denom is None:
-        denom = count_valid(labels, ignore_index, exchange)
     # across GPUs the kernel only posts its sums; backward's rescale kernel collects the peers'
     # (or whatever reads the loss first, see _p2p.DeferredLoss)
-    defer = 1 if (exchange is not None and _p2p.defer_enabled()) else 0
+    flags = _cabi.STEP_DEFER if (exchange is not None and _p2p.defer_enabled()) else 0
+    if mean and denom is None:
+        # everything the step needs is allocated by now: the label count is the operation directly
+        # in front of the step's kernel, which may then start under the count's tail
+        denom = count_valid(labels, ignore_index, exchange)
+        flags |= _cabi.STEP_AFTER_COUNT
     with torch.cuda.device(dev):
         _cabi.check(getattr(lib, _ENTRY_FUSED[kind])(
             _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws), ws.numel(),
             None if not mean else _cabi._vp(denom.data_ptr()), n, c, m, dt, int(ignore_index), float(hyper),
-            defer, st))
+            flags, st))
+    defer = flags & _cabi.STEP_DEFER
     if defer:
         exchange.defer(rec, ws)
     return rec, grads, logits, labels
@@ -188,17 +192,13 @@ class ReducedLossFunc(torch.autograd.Function):
         ctx.fused = None
         ctx.deferred = None
         nccl_group = exchange is None and _sharding.group_is_active(group)
-        denom = None
-        if exchange is not None and mean:
-            # Ranks must make the same sequence of exchanges whichever kernels each of them runs
-            # below (a rank may hold an empty or unaligned shard, or need no gradient): with
-            # 'mean' every rank posts its label count first, then its loss sum.
-            _cabi.require_cuda(logits, labels)
-            denom = count_valid(labels, ignore_index, exchange)
+        # Ranks must make the same sequence of exchanges whichever kernels each of them runs (a
+        # rank may hold an empty or unaligned shard, or need no gradient): with 'mean' every rank
+        # posts its label count first, then its loss sum -- inside fused_step, or right below.
         if ctx.needs_input_grad[0] and logits.is_cuda and not nccl_group and \
                 os.environ.get("B200_SOFTMAX_FUSED", "1") != "0":
             # the fused step: loss sum and final gradient from one read of the logits
-            step = fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange, denom)
+            step = fused_step(kind, logits, labels, ignore_index, hyper, mean, exchange)
             if step is not None:
                 rec, grads, logits, labels = step
                 ctx.fused = grads
@@ -206,6 +206,9 @@ class ReducedLossFunc(torch.autograd.Function):
                 ctx.variables = (logits, labels, kind, hyper, ignore_index,
                                  (rec[:4].view(torch.float64)[1:] if mean else None), None)
                 return rec[4] if mean else rec[5]
+        if exchange is not None and mean:
+            _cabi.require_cuda(logits, labels)
+            count_valid(labels, ignore_index, exchange)        # (the exchange every rank makes first)
         rec, _, logits, labels, stats = forward_reduced(kind, logits, labels, ignore_index, hyper,
                                                         exchange=exchange, want_stats=True)
         sum_count = rec[:4].view(torch.float64)
