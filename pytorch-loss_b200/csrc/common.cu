@@ -112,7 +112,7 @@ __global__ void set_exchange_kernel(void *workspace, const void *ctx) {
 
 extern "C" {
 
-int b200_abi_version(void) { return 2; }
+int b200_abi_version(void) { return 3; }
 
 uint64_t b200_kernel_launch_count(void) { return b200::g_launches.load(std::memory_order_relaxed); }
 

@@ -14,7 +14,7 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200loss.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 STEP_DEFER, STEP_AFTER_COUNT = 1, 2      # bits of the fused steps' `defer` argument (b200loss.h)
 F32, F16, BF16, F64 = 0, 1, 2, 3
 
