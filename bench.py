@@ -403,13 +403,15 @@ def direct_calls(wl, sets, device):
         return fwd, bwd
     if wl.kind == "pc_softmax":
         w = torch.tensor(wl.proportions(), dtype=torch.float32, device=device)
-        losses = [torch.empty_like(y, dtype=xs[0].dtype) for y in ys]
         cnts = [_cabi.new_record(device) for _ in sets]
+        if not lib.b200_pc_softmax_step_path(P(xs[0]), P(ys[0]), P(grads[0]), n, c, m, dt):
+            raise SystemExit("bench: workload %s has no fused step on this build" % wl.name)
 
         def fwd(i):
             _cabi.check(lib.b200_count_valid(P(ys[i]), n * m, 255, P(cnts[i]), P(ws), ws.numel(), st))
-            _cabi.check(lib.b200_pc_softmax_ce_scaled(P(xs[i]), P(ys[i]), P(w), P(losses[i]), P(grads[i]),
-                                                      _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255, st))
+            _cabi.check(lib.b200_pc_softmax_step(P(xs[i]), P(ys[i]), P(w), P(grads[i]), P(recs[i]), P(ws), ws.numel(),
+                                                 _cabi._vp(cnts[i].data_ptr() + 8), n, c, m, dt, 255,
+                                                 _cabi.STEP_AFTER_COUNT, st))
         return fwd, rescale
     stem, hyper, ign = {"lsr": ("lsr", 0.1, 255), "lsr_rows": ("lsr", 0.1, -100), "lmargin": ("lmargin", 0.3, 255)}[wl.kind]
     if wl.reduction == 'none':

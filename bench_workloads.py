@@ -58,9 +58,8 @@ class Workload:
         if self.kind == "taylor":
             return 2 * s * e                 # input read, output written
         if self.kind == "pc_softmax":
-            # label count (8P), then one launch: logits and labels read, per-pixel loss and FINAL
-            # gradient written; the sum of the per-pixel losses (4P read) is torch's
-            return 2 * s * e + 16 * p + 2 * s * p
+            # label count (8P), then the fused step: logits read, gradient written, labels read
+            return 2 * s * e + 16 * p
         if self.fused_softmax():
             # label count (8P), then the fused step: logits read, gradient written, labels read
             return 2 * s * e + 16 * p
@@ -98,7 +97,7 @@ class Workload:
         if self.kind == "taylor":
             return "b200_taylor_softmax_forward", "b200_taylor_softmax_backward"
         if self.kind == "pc_softmax":
-            return "b200_count_valid+b200_pc_softmax_ce_scaled", "b200_rescale_gradient"
+            return "b200_count_valid+b200_pc_softmax_step", "b200_rescale_gradient"
         if self.fused_softmax():
             stem = "lmargin" if self.kind == "lmargin" else "lsr"
             return "b200_count_valid+b200_%s_forward_backward_reduced" % stem, "b200_rescale_gradient"

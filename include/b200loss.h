@@ -382,6 +382,19 @@ int b200_taylor_softmax_backward(const void *grad, const void *feat, void *grad_
 int b200_pc_softmax_ce(const void *logits, const int64_t *labels, const float *weight, void *losses,
                        void *grad_logits, int64_t N, int64_t C, int64_t M, int dtype,
                        int64_t ignore_index, void *stream);
+/* The 'mean' / 'sum' TRAINING STEP of the same loss on the tile pipeline of the label-smooth step
+ * (b200_lsr_forward_backward_reduced with smoothing 0 and the class weights inside the
+ * exponentials): out = reduction record of the loss over the valid pixels, grad_logits =
+ * d(loss sum)/d(logits) / *denom (denom: optional device double, e.g. the count of
+ * b200_count_valid), ONE read of the logits.  b200_pc_softmax_step_path: 1 when the layout has
+ * this step (M > 1, 16-byte aligned rows, at most 256 classes), else 0 -> use b200_pc_softmax_ce.
+ * `flags`: B200_STEP_AFTER_COUNT as for the label-smooth step.  Backward: b200_rescale_gradient. */
+int b200_pc_softmax_step_path(const void *logits, const int64_t *labels, const void *grad_logits,
+                              int64_t N, int64_t C, int64_t M, int dtype);
+int b200_pc_softmax_step(const void *logits, const int64_t *labels, const float *weight,
+                         void *grad_logits, void *out, void *workspace, size_t workspace_bytes,
+                         const void *denom, int64_t N, int64_t C, int64_t M, int dtype,
+                         int64_t ignore_index, int flags, void *stream);
 /* The same with the gradient divided by *denom (a device double, e.g. the count written by
  * b200_count_valid; NULL: not divided): what 'mean' needs, so that the caller's backward has
  * nothing left to do for an upstream gradient of 1 (the division the reference's backward

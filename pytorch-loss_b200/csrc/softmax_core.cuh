@@ -25,7 +25,9 @@
 
 namespace b200 {
 
-enum LossKind { kLSR = 0, kLMargin = 1 };
+// kPC: proportion-corrected softmax cross entropy = label smooth with smoothing 0 and a class
+// weight inside every exponential; only the resident-tile fused step is instantiated for it.
+enum LossKind { kLSR = 0, kLMargin = 1, kPC = 2 };
 
 struct LossConsts {
     // LSR

@@ -30,6 +30,8 @@ constexpr int kThreads = 256;
 constexpr size_t kTileTargetBytes = 48 * 1024;
 constexpr size_t kSmemLimit = 200 * 1024;
 
+constexpr int kPcMaxC = 256;     // classes the kPC fused step holds weights for
+
 struct SoftmaxParams {
     const void *logits;
     const int64_t *labels;
@@ -52,6 +54,7 @@ struct SoftmaxParams {
     int64_t tiles_per_image, total_tiles;
     int defer;               // cross-GPU sum of the fused step: post only (see grid_reduce_finish)
     int after_count;         // fused step launched as a programmatic dependent of the label count
+    const float *chan_w;     // kPC: class weights [C] (device)
 };
 
 // ------------------------------------------------------------------ tile regime
@@ -475,8 +478,13 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
     extern __shared__ unsigned char smem_raw[];
     __shared__ PipeBarriers bars;
     __shared__ double sh_red[64];
+    __shared__ float s_lw2[KIND == kPC ? kPcMaxC : 1];    // kPC: log2 of the class weights
 
     const int TP = prm.TP, C = static_cast<int>(prm.C), NS = prm.stages;
+    if constexpr (KIND == kPC) {
+        // (a weight of 0 gives -inf: that class's exponential is 0, as w * e^x would be)
+        for (int j = threadIdx.x; j < C; j += kTileBlock) s_lw2[j] = __log2f(__ldg(prm.chan_w + j));
+    }
     const int NBX = prm.nbx, TPT = TP * NBX;        // a tile is NBX boxes of TP pixels side by side
     const int box_elems = prm.rows * TP;            // elements of one box in shared memory
     unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
@@ -589,7 +597,7 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
             T *tile = reinterpret_cast<T *>(base + s * stage_bytes);
             T *mine = tile + bxo + ks * TP;           // my first channel, my pixel pair
 
-            if constexpr (KIND == kLSR) {
+            if constexpr (KIND != kLMargin) {
                 // ---- phase 1: max
                 float2 m = splat2(kNegInf);
                 {
@@ -622,9 +630,11 @@ tile_pair_kernel(const SoftmaxParams prm, const __grid_constant__ CUtensorMap ma
 #pragma unroll 4
                     for (int j = ks; j < C; j += KS, q += step) {
                         const pk_t x = ld_pk(q);
-                        const pk_t e = pex2(pfma(x, l2e, nml));
+                        pk_t e;
+                        if constexpr (KIND == kPC) e = pex2(pfma(x, l2e, padd(nml, psplat(s_lw2[j]))));   // w_j e^{x - m}
+                        else e = pex2(pfma(x, l2e, nml));
                         psum = padd(psum, e);
-                        if (!BWD || REDUCE) psx = padd(psx, x);
+                        if (KIND != kPC && (!BWD || REDUCE)) psx = padd(psx, x);    // (kPC: lb_neg = 0, the sum of logits is not used)
                         if (BWD) st_pk(q, e);
                     }
                     sum = upk2(psum);
@@ -1826,7 +1836,7 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
                 return launch_status("softmax chunked forward kernel launch");
             }
         }
-        if constexpr (BWD) {
+        if constexpr (BWD && KIND != kPC) {
             // many channels, backward from the statistics the chunked forward saved
             if (prm.stats && aligned16(prm.stats) &&
                 chunk_eligible(es, prm.logits, prm.grads, prm.labels, prm.N, prm.C, prm.M)) {
@@ -1890,7 +1900,7 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
             launch_kernel(kern, dim3(unsigned(grid)), dim3(kTileBlock), smem, stream, BWD && REDUCE && prm.after_count,
                           prm, map_in, map_out);
-        } else {
+        } else if constexpr (KIND != kPC) {
             const size_t smem = 128 + tile_bytes + red_bytes;
             int per_sm = int((220 * 1024) / (smem + 1024));
             if (per_sm > 8) per_sm = 8;
@@ -1902,9 +1912,17 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             auto kern = tile_kernel<T, KIND, BWD, REDUCE, false>;
             if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
             kern<<<dim3(unsigned(grid)), kThreads, smem, stream>>>(prm, unused, unused);
+        } else {
+            (void)red_bytes;
+            set_error("pc softmax step: this layout has no fused step");
+            return B200_ERR_UNSUPPORTED;
         }
         return launch_status("softmax tile kernel launch");
     }
+    if constexpr (KIND == kPC) {
+        set_error("pc softmax step: this layout has no fused step");
+        return B200_ERR_UNSUPPORTED;
+    } else {
     if constexpr (!BWD) {
         // ---- rows regime, forward, long rows: one warp per row, streamed (any row length)
         if (prm.M == 1 && (size_t(prm.C) * es) % 16 == 0 && size_t(prm.C) * es >= 2 * size_t(kWarpRowChunk) &&
@@ -1971,6 +1989,7 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
     if (grid < 1) grid = 1;
     sweep_kernel<T, KIND, BWD, REDUCE><<<dim3(unsigned(grid)), kThreads, 0, stream>>>(prm);
     return launch_status("softmax sweep kernel launch");
+    }
 }
 
 template <int KIND, bool BWD>
@@ -2248,6 +2267,15 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
     return dispatch<KIND, true>(prm, dtype, true, static_cast<cudaStream_t>(stream));
 }
 
+// Proportion-corrected softmax cross entropy as a training step on the resident-tile pipeline
+// (tile_pair_kernel<T, kPC, true, true>): loss sum record and final gradient from one read of the
+// logits.  Layouts: those of the tile pipeline (M > 1, 16-byte aligned rows), up to kPcMaxC classes.
+inline bool pc_step_eligible(int dtype, const void *logits, const void *grads, const void *labels, int64_t N,
+                             int64_t C, int64_t M) {
+    return dtype_known(dtype) && dtype != B200_F64 && M > 1 && C >= 1 && C <= kPcMaxC &&
+           fused_step_eligible(dtype_size(dtype), logits, grads, labels, N, C, M);
+}
+
 // Number of labels != ignore, 16-byte loads, four in flight per thread.
 __global__ void __launch_bounds__(256) count_valid_kernel(const int64_t *labels, int64_t P, int64_t ignore,
                                                           void *workspace, ReduceRecord *out) {
@@ -2308,6 +2336,53 @@ extern "C" int b200_softmax_fused_step_path(const void *logits, const int64_t *l
     if (!dtype_known(dtype)) return 0;
     if (C < 1 || C >= (int64_t(1) << 31)) return 0;
     return fused_step_eligible(dtype_size(dtype), logits, grad_logits, labels, N, C, M) ? 1 : 0;
+}
+
+extern "C" int b200_pc_softmax_step_path(const void *logits, const int64_t *labels, const void *grad_logits,
+                                         int64_t N, int64_t C, int64_t M, int dtype) {
+    return pc_step_eligible(dtype, logits, grad_logits, labels, N, C, M) ? 1 : 0;
+}
+
+// PC-softmax cross entropy (see pc_softmax.cu for the formulas): out = reduction record of the loss
+// over the valid pixels, grad_logits = d(loss sum)/d(logits) / *denom (denom optional), one pass.
+extern "C" int b200_pc_softmax_step(const void *logits, const int64_t *labels, const float *weight, void *grad_logits,
+                                    void *out, void *workspace, size_t workspace_bytes, const void *denom,
+                                    int64_t N, int64_t C, int64_t M, int dtype, int64_t ignore_index, int flags,
+                                    void *stream) {
+    const char *who = "b200_pc_softmax_step";
+    int rc = check_shape(who, N, C, M);
+    if (rc != B200_OK) return rc;
+    if (!out || !workspace || workspace_bytes < kReduceWorkspaceBytes) {
+        set_error("%s: out and a workspace of %zu bytes are required", who, kReduceWorkspaceBytes);
+        return B200_ERR_WORKSPACE;
+    }
+    if (!logits || !labels || !grad_logits || !weight) {
+        set_error("%s: null pointer", who);
+        return B200_ERR_ARG;
+    }
+    if (!pc_step_eligible(dtype, logits, grad_logits, labels, N, C, M)) {
+        set_error("%s: this layout has no fused step (ask b200_pc_softmax_step_path first)", who);
+        return B200_ERR_UNSUPPORTED;
+    }
+    SoftmaxParams prm{};
+    prm.logits = logits;
+    prm.labels = labels;
+    prm.grads = grad_logits;
+    prm.denom = static_cast<const double *>(denom);
+    prm.workspace = workspace;
+    prm.out = static_cast<ReduceRecord *>(out);
+    prm.N = N;
+    prm.C = C;
+    prm.M = M;
+    prm.ignore = ignore_index;
+    prm.k = make_consts(kLSR, C, 0.f);          // cross entropy: smoothing 0
+    prm.chan_w = weight;
+    prm.defer = 0;
+    prm.after_count = (denom != nullptr && (flags & B200_STEP_AFTER_COUNT)) ? 1 : 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == B200_F32) return launch_regime<float, kPC, true, true>(prm, dtype, st);
+    if (dtype == B200_F16) return launch_regime<__half, kPC, true, true>(prm, dtype, st);
+    return launch_regime<__nv_bfloat16, kPC, true, true>(prm, dtype, st);
 }
 
 // Loss sum (record in `out`) and FINAL gradient (divided by *denom when given: a device double,

@@ -64,6 +64,8 @@ SIGNATURES = {
     "b200_taylor_softmax_forward": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp]),
     "b200_taylor_softmax_backward": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _int, _vp]),
     "b200_pc_softmax_ce": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _i64, _vp]),
+    "b200_pc_softmax_step_path": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int]),
+    "b200_pc_softmax_step": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _i64, _i64, _i64, _int, _i64, _int, _vp]),
     "b200_pc_softmax_ce_scaled": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _i64, _vp]),
     "b200_ohem_workspace_bytes": (_sz, [_i64, _i64]),
     "b200_ohem_label": (_int, [_vp, _vp, _vp, _vp, _sz, _i64, _i64, _i64, _int, _i64, _f32, _i64, _vp]),

@@ -53,6 +53,35 @@ def _rescale(grads, grad_output):
     return grads
 
 
+def pc_softmax_step(logits, labels, lb_proportion, ignore_index, mean):
+    """The 'mean' / 'sum' training step in one pass over the logits (the label-smooth step's tile
+    pipeline with the class weights inside the exponentials), or None when the layout has none.
+    Returns (record, final gradient, valid-pixel count or None)."""
+    dev = _cabi.require_cuda(logits, labels)
+    n, c, m = _cabi.split_shape(logits, labels)
+    if labels.dtype != torch.int64 or logits.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        return None
+    logits, labels = logits.contiguous(), labels.contiguous()
+    lib = _cabi.load_library()
+    grads = torch.empty_like(logits)
+    dt = _cabi.dtype_code(logits)
+    if n * m == 0 or not lib.b200_pc_softmax_step_path(_cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(grads), n, c, m, dt):
+        return None
+    w = _weights(lb_proportion, c, dev)
+    rec = _cabi.new_record(dev)
+    ws = _cabi.reduce_workspace(dev)
+    denom, flags = None, 0
+    if mean:       # (directly in front of the step's launch: it starts under the count's tail)
+        denom = _softmax_family.count_valid(labels, ignore_index)
+        flags = _cabi.STEP_AFTER_COUNT
+    with torch.cuda.device(dev):
+        _cabi.check(lib.b200_pc_softmax_step(
+            _cabi.ptr(logits), _cabi.ptr(labels), _cabi.ptr(w), _cabi.ptr(grads), _cabi.ptr(rec), _cabi.ptr(ws),
+            ws.numel(), None if denom is None else _cabi._vp(denom.data_ptr()), n, c, m, dt, int(ignore_index),
+            flags, _cabi.stream_ptr(dev)))
+    return rec, grads, denom
+
+
 class PCSoftmaxCrossEntropyFunction(torch.autograd.Function):
     """forward(logits, label, lb_proportion, reduction, ignore_index)
     (reference pc_softmax.py:52-114)."""
@@ -62,6 +91,13 @@ class PCSoftmaxCrossEntropyFunction(torch.autograd.Function):
     def forward(ctx, logits, label, lb_proportion, reduction, ignore_index):
         # 'mean': the valid pixels are counted first (labels only), so that the gradient leaves the
         # kernel already divided and backward has nothing to do for an upstream gradient of 1
+        if reduction in ('mean', 'sum') and ctx.needs_input_grad[0] and logits.is_cuda:
+            step = pc_softmax_step(logits, label, lb_proportion, ignore_index, reduction == 'mean')
+            if step is not None:
+                rec, grads, n_valid = step
+                ctx.vars = logits, label, lb_proportion, ignore_index, reduction, n_valid
+                ctx.grads = grads
+                return rec[4] if reduction == 'mean' else rec[5]
         n_valid = None
         if reduction == 'mean':
             _cabi.require_cuda(logits, label)

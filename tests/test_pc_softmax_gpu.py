@@ -88,3 +88,44 @@ def test_scalar_upstream_gradient_and_second_backward(c):
         x.grad = None
         (loss * -0.5).backward()
         assert_grad_close(x.grad, want_grad * -0.5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(2, 19, (32, 40)), (1, 150, (16, 32)), (2, 256, (8, 16)), (2, 257, (8, 16))],
+                         ids=lambda s: "x".join(map(str, (s[0], s[1]) + s[2])))
+def test_half_logits_reduced_step(shape, dtype):
+    """'mean' / 'sum' with a gradient: the fused step on the tile pipeline (up to 256 classes; 257
+    takes the per-pixel kernel), half storage, fp32 arithmetic."""
+    import pytorch_loss as P
+    from oracle import pc_softmax as PC
+    n, c, sp = shape
+    g = torch.Generator().manual_seed(730 + c)
+    logits = (torch.randn((n, c) + sp, generator=g) * 2.0).to(dtype)
+    labels = labels_with_ignores(g, (n,) + sp, c, 255, 0.15)
+    prop = torch.rand(c, generator=g) + 0.05
+    prop = (prop / prop.sum()).tolist()
+    tol = TOL_F16 if dtype == torch.float16 else 2.0 ** -7
+    for reduction in ("mean", "sum"):
+        want_loss, want_grad = PC.pc_softmax_ce(logits.float(), labels, prop, 255, reduction)
+        loss, grad = run_module(P.PCSoftmaxCrossEntropyV2(prop, reduction, 255), logits.cuda(), labels.cuda())
+        assert grad.dtype == dtype
+        assert_loss_close(loss.float(), want_loss, rtol=tol, atol=tol)
+        assert_grad_close(grad.float(), want_grad, atol=tol, rtol=tol)
+        ign = labels == 255
+        assert bool((grad.cpu().transpose(0, 1)[:, ign] == 0).all())
+
+
+def test_zero_proportion_class():
+    """A class with proportion 0 drops out of the sum (its exponential is weighted by 0)."""
+    import pytorch_loss as P
+    from oracle import pc_softmax as PC
+    g = torch.Generator().manual_seed(740)
+    logits = torch.randn(2, 6, 8, 12, generator=g) * 2.0
+    labels = torch.randint(1, 6, (2, 8, 12), generator=g)          # class 0 never is the label
+    prop = [0.0, 0.3, 0.2, 0.2, 0.1, 0.2]
+    for reduction in ("mean", "none"):
+        want_loss, want_grad = PC.pc_softmax_ce(logits, labels, prop, 255, reduction)
+        loss, grad = run_module(P.PCSoftmaxCrossEntropyV2(prop, reduction, 255), logits.cuda(), labels.cuda())
+        assert_loss_close(loss, want_loss, atol=2e-6)
+        assert_grad_close(grad, want_grad)
+        assert bool((grad[:, 0] == 0).all())
