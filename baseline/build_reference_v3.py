@@ -11,7 +11,8 @@ lovasz_softmax_cpp, ohem_cpp, taylor_softmax_cpp), compiled straight from `csrc/
 lie, and the package `reference_py/`: the reference's Python modules that call those extensions (the same files a
 `pip install --target` of the reference would place there), in the copies that match the
 current extension signatures:
-    focal_loss.py, large_margin_softmax.py, lovasz_softmax.py, taylor_softmax.py (repository root)
+    focal_loss.py, large_margin_softmax.py, lovasz_softmax.py, taylor_softmax.py, pc_softmax.py
+    (repository root; the last one has no extension behind it: tensor ops)
     label_smooth.py, ohem_loss.py (pytorch_loss/; the root label_smooth.py does not import on
     torch >= 2.4 because it calls torch.amp.custom_fwd without device_type).
 Compilation needs nvcc only (no GPU); each extension takes 2-3 minutes.
@@ -45,11 +46,12 @@ PY_MODULES = {
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("PYTORCH_LOSS_REFERENCE", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("PYTORCH_LOSS_REFERENCE"),
+                    help="checkout of CoinCheung/pytorch-loss (or set PYTORCH_LOSS_REFERENCE)")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
-    if not os.path.isdir(os.path.join(args.ref, "csrc")):
-        sys.exit("no reference checkout at %s" % args.ref)
+    if not args.ref or not os.path.isdir(os.path.join(args.ref, "csrc")):
+        sys.exit("no reference checkout at %s (pass --ref or set PYTORCH_LOSS_REFERENCE)" % args.ref)
     os.environ["TORCH_CUDA_ARCH_LIST"] = "10.0a"
     os.environ.setdefault("MAX_JOBS", str(os.cpu_count() or 4))
     from torch.utils import cpp_extension
