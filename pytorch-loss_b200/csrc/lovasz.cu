@@ -772,10 +772,29 @@ sort_scan_kernel(uint32_t *__restrict__ hist, uint32_t *__restrict__ fghist,
 #pragma unroll
     for (int which = 0; which < (LAST ? 2 : 1); ++which) {
         uint32_t *h = (which ? fghist : hist) + seg * T * kBins;
+        // (a thread walks its digit's column tile by tile: eight independent loads in flight)
         uint32_t total = 0;
-        for (int64_t t = 0; t < Tk; ++t) total += h[t * kBins + b];
+        int64_t t = 0;
+        for (; t + 8 <= Tk; t += 8) {
+            uint32_t c[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) c[u] = h[(t + u) * kBins + b];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) total += c[u];
+        }
+        for (; t < Tk; ++t) total += h[t * kBins + b];
         uint32_t run = block_excl_scan_1024(total, warp_tot, &grand);
-        for (int64_t t = 0; t < Tk; ++t) {
+        for (t = 0; t + 8 <= Tk; t += 8) {
+            uint32_t c[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) c[u] = h[(t + u) * kBins + b];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                h[(t + u) * kBins + b] = run;
+                run += c[u];
+            }
+        }
+        for (; t < Tk; ++t) {
             const uint32_t c = h[t * kBins + b];
             h[t * kBins + b] = run;
             run += c;

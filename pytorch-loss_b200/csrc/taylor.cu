@@ -13,6 +13,8 @@
 // one per position for log S.
 //   M > 1   few channels (<= 32 forward, <= 20 backward, float32): a thread owns 2 adjacent
 //           positions and keeps all their channels in registers -- one read, one write;
+//           33..320 channels (float32): channel slices over the threads of a block, each thread's
+//           share in registers, partial sums through shared memory -- again one read, one write;
 //           otherwise a thread owns 4 adjacent positions along M (16-byte accesses when the layout
 //           allows, else one position) and walks the C channels twice: sums first, outputs
 //           second; the second walk finds its lines in L1/L2 (a block's working set is C x 4 KB).
@@ -196,6 +198,105 @@ taylor_resident_kernel(const TaylorParams p) {
     }
 }
 
+// M > 1, more channels than one thread can hold (float32, M even, 8-byte aligned): the 256
+// threads of a block are KS channel slices x (256 / KS) adjacent position PAIRS; a thread keeps
+// its slice's channels (every KS-th, at most CPT of them) of one pair in registers -- a warp
+// reads 256 contiguous bytes per channel -- and the slices add their partial sums through shared
+// memory (two buffers, one block barrier per group of positions).  x and g are read once.
+template <bool BWD, bool LOG, int ORDER, int KS, int CPT>
+__global__ void __launch_bounds__(kTaylorThreads, 2)
+taylor_sliced_kernel(const TaylorParams p) {
+    constexpr int PX = kTaylorThreads / KS;            // position pairs per block and round
+    __shared__ float2 part[2][2][KS][PX];              // [round parity][S, A][slice][pair]
+    const float *x = static_cast<const float *>(p.x);
+    const float *g = static_cast<const float *>(p.g);
+    float *out = static_cast<float *>(p.out);
+    const int C = int(p.C);
+    const int M = int(p.M);                            // C * M < 2^31 (host check): 32-bit channel offsets
+    const int px = threadIdx.x % PX, ks = threadIdx.x / PX;
+    const int64_t groups_per_row = (p.M / 2 + PX - 1) / PX;
+    const int64_t groups = p.N * groups_per_row;
+    int par = 0;
+    for (int64_t gi = blockIdx.x; gi < groups; gi += gridDim.x, par ^= 1) {
+        const int64_t n = gi / groups_per_row;
+        const int m = (int(gi % groups_per_row) * PX + px) * 2;
+        const bool live = m < M;
+        const int64_t base = n * p.C * p.M + (live ? m : 0);
+        const float *xb = x + base;
+        const float *gb = BWD ? g + base : nullptr;
+        float2 xv[CPT], gv[BWD ? CPT : 1];
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int j = ks + i * KS;
+            if (live && j < C) {
+                xv[i] = __ldcs(reinterpret_cast<const float2 *>(xb + j * M));
+                if (BWD) gv[i] = __ldcs(reinterpret_cast<const float2 *>(gb + j * M));
+            }
+        }
+        float2 S = make_float2(0.f, 0.f), A = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            if (ks + i * KS < C) {
+                float d;
+                float2 f;
+                taylor_poly<ORDER, false>(xv[i].x, p, f.x, d);
+                taylor_poly<ORDER, false>(xv[i].y, p, f.y, d);
+                S.x += f.x;
+                S.y += f.y;
+                if (BWD) {
+                    A.x += LOG ? gv[i].x : gv[i].x * f.x;
+                    A.y += LOG ? gv[i].y : gv[i].y * f.y;
+                } else {
+                    xv[i] = f;                        // forward: f(x) takes x's place
+                }
+            }
+        }
+        part[par][0][ks][px] = S;
+        if (BWD) part[par][1][ks][px] = A;
+        __syncthreads();
+        S = make_float2(0.f, 0.f);
+        A = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < KS; ++q) {
+            const float2 s = part[par][0][q][px];
+            S.x += s.x;
+            S.y += s.y;
+            if (BWD) {
+                const float2 a = part[par][1][q][px];
+                A.x += a.x;
+                A.y += a.y;
+            }
+        }
+        if (!live) continue;
+        const float2 invS = make_float2(1.f / S.x, 1.f / S.y);
+        const float2 logS = LOG && !BWD ? make_float2(logf(S.x), logf(S.y)) : make_float2(0.f, 0.f);
+        float *ob = out + base;
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int j = ks + i * KS;
+            if (j < C) {
+                float2 o;
+                if constexpr (!BWD) {
+                    o.x = LOG ? __logf(xv[i].x) - logS.x : xv[i].x * invS.x;
+                    o.y = LOG ? __logf(xv[i].y) - logS.y : xv[i].y * invS.y;
+                } else {
+                    float fx, fy, dx, dy;
+                    taylor_poly<ORDER, true>(xv[i].x, p, fx, dx);
+                    taylor_poly<ORDER, true>(xv[i].y, p, fy, dy);
+                    if (LOG) {
+                        o.x = dx * (gv[i].x / fx - A.x * invS.x);
+                        o.y = dy * (gv[i].y / fy - A.y * invS.y);
+                    } else {
+                        o.x = dx * invS.x * (gv[i].x - A.x * invS.x);
+                        o.y = dy * invS.y * (gv[i].y - A.y * invS.y);
+                    }
+                }
+                __stcs(reinterpret_cast<float2 *>(ob + j * M), o);
+            }
+        }
+    }
+}
+
 // M == 1: one warp per row.
 template <typename T, bool BWD, bool LOG, int ORDER>
 __global__ void __launch_bounds__(kTaylorThreads)
@@ -260,6 +361,31 @@ int launch_taylor(const TaylorParams &p, cudaStream_t stream) {
             else if (!BWD && p.C <= 20) taylor_resident_kernel<false, LOG, ORDER, 20><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
             else taylor_resident_kernel<BWD, LOG, ORDER, kSmall><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
             return launch_status("taylor softmax resident kernel launch");
+        }
+    }
+    if constexpr (sizeof(T) == 4 && ORDER > 0) {
+        // 33..320 channels: sliced register-resident kernel (forward: 40 channels per thread in 4
+        // or 8 slices; backward holds x and g: 20 channels per thread in 8 or 16 slices)
+        const bool al8s = ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out) |
+                            (BWD ? reinterpret_cast<uintptr_t>(p.g) : 0)) & 7u) == 0;
+        // (measured at [16,64,512,512] / [16,40,512,512]: the forward ties with or loses to the two
+        // walks below up to ~96 channels, 0.58 / 0.59 against 0.61 / 0.68 of peak; the backward wins from
+        // 33 on, 0.90 / 0.69 against 0.62 / 0.63; at 150 channels 0.83 / 1.00 against 0.60 / 0.61)
+        if (p.C > (BWD ? 32 : 96) && p.C <= 320 && p.C * p.M < (int64_t(1) << 31) && p.M >= 64 && p.M % 2 == 0 && al8s) {
+            // slices so that a thread holds 20..48 channels: few channels per thread leave too few
+            // bytes in flight between two block barriers (C = 40 in 4 slices: 0.46 of peak)
+            constexpr int KS0 = BWD ? 4 : 2, KS1 = BWD ? 8 : 4, KS2 = BWD ? 16 : 8;
+            constexpr int CPT0 = BWD ? 24 : 48, CPT = BWD ? 20 : 40;
+            const int ks = p.C <= 96 ? KS0 : (p.C <= 160 ? KS1 : KS2);
+            const int px = kTaylorThreads / ks;
+            const int64_t rounds = p.N * ((p.M / 2 + px - 1) / px);
+            int64_t grid3 = int64_t(sm_count()) * 2;
+            if (grid3 > rounds) grid3 = rounds;
+            const unsigned g3 = unsigned(grid3);
+            if (ks == KS0) taylor_sliced_kernel<BWD, LOG, ORDER, KS0, CPT0><<<g3, kTaylorThreads, 0, stream>>>(p);
+            else if (ks == KS1) taylor_sliced_kernel<BWD, LOG, ORDER, KS1, CPT><<<g3, kTaylorThreads, 0, stream>>>(p);
+            else taylor_sliced_kernel<BWD, LOG, ORDER, KS2, CPT><<<g3, kTaylorThreads, 0, stream>>>(p);
+            return launch_status("taylor softmax sliced kernel launch");
         }
     }
     const bool vec4 = sizeof(T) == 4 && p.M % 4 == 0 && aligned16(p.x) && aligned16(p.out) && (!BWD || aligned16(p.g));
