@@ -55,7 +55,7 @@ L2_BYTES = 126 << 20
 # workloads the reference's own V3 CUDA build is timed on (N=1): every one of them ran to the end
 # on a B200 when first tried; a workload whose reference kernels fault or hang is taken off here
 REFERENCE_V3_WORKLOADS = ("lmargin", "lsr", "focal", "lsr_rows", "lovasz", "lovasz_full", "ohem", "focal_up2",
-                          "lmargin_none", "lsr_none", "taylor", "pc_softmax")
+                          "lmargin_none", "lsr_none", "taylor", "taylor_c150", "pc_softmax")
 
 
 def measured_peak():
@@ -103,7 +103,8 @@ def traffic_from_ncu(args):
         if "b200::" not in name:                      # torch's own kernels (input generation, fills)
             continue
         bwd = re.search(r"rescale_kernel|lovasz_pair_kernel<\(?(bool\))?1|lovasz_tile_kernel<\(?(bool\))?1|"
-                        r"taylor_resident_kernel<\(?(bool\))?1|taylor_spatial_kernel<[^,]+, [^,]+, \(?(bool\))?1|"
+                        r"taylor_resident_kernel<\(?(bool\))?1|taylor_sliced_kernel<\(?(bool\))?1|"
+                        r"taylor_spatial_kernel<[^,]+, [^,]+, \(?(bool\))?1|"
                         r"taylor_rows_kernel<[^,]+, \(?(bool\))?1", name) is not None
         sums[1 if bwd else 0] += float(r[col["Metric Value"]].replace(",", "")) * scale[r[col["Metric Unit"]]]
     per_elem = [round(v / args.launches / wl.elems, 3) for v in sums]

@@ -248,6 +248,9 @@ WORKLOADS = {
                      "OhemCELoss fp32 [16,19,512,512], thresh 0.7, n_min P/16, 97% easy pixels, 5% ignored", 4),
     "taylor": Workload("taylor", 7, (16, 19, 512, 512), torch.float32,
                        "LogTaylorSoftmaxV3 fp32 [16,19,512,512], dim 1, n 2, dense upstream gradient", 2),
+    "taylor_c150": Workload("taylor_c150", 9, (8, 150, 512, 512), torch.float32,
+                            "LogTaylorSoftmaxV3 fp32 [8,150,512,512], dim 1, n 2, dense upstream gradient", 1,
+                            kind="taylor"),
     "pc_softmax": Workload("pc_softmax", 8, (16, 19, 512, 512), torch.float32,
                            "PCSoftmaxCrossEntropyV2 fp32 [16,19,512,512], 1/k class proportions, 5% ignored, mean", 2),
 }
