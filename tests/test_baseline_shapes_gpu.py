@@ -37,9 +37,11 @@ def _check_scaled(grad, want, what, units=1e-5):
 LOVASZ_RANK_UNITS = 2e-4
 
 
-@pytest.mark.parametrize("items", [2, 5])
+@pytest.mark.parametrize("items", [2, 5, 9])
 def test_config1_label_smooth(items):
-    """[items,19,512,512], 5 % ignored: two-box TMA tiles, 512 tiles per image."""
+    """[items,19,512,512], 5 % ignored.  Up to 40 M elements (2 and 5 images) the fused step is the
+    register-resident kernel; 9 images (44.8 M) take the tile pipeline of the full configuration:
+    two-box TMA tiles, 512 tiles per image."""
     import pytorch_loss as P
     O = _oracle()
     x, y = BW.WORKLOADS["lsr"].make(items=items)
@@ -150,3 +152,37 @@ def test_config5_label_smooth_rows_fp16():
     want_px, _ = O.label_smooth_ce(x.float(), y, 0.1, -100, "none")
     px, _ = run_module(P.LabelSmoothSoftmaxCEV3(0.1, "none", -100), x.cuda(), y.cuda())
     assert_loss_close(px.float(), want_px, rtol=TOL_F16, what="config 5 per-row loss")
+
+
+def test_pc_softmax_at_config1_shape():
+    """PCSoftmaxCrossEntropyV2 at [2,19,512,512] with the benchmark's inputs and class proportions:
+    the fused step on the tile pipeline ('mean', 'sum') and the per-pixel kernel ('none')."""
+    import pytorch_loss as P
+    from oracle import pc_softmax as PC
+    wl = BW.WORKLOADS["pc_softmax"]
+    x, y = wl.make(items=2)
+    prop = wl.proportions()
+    for red in ("sum", "mean", "none"):
+        want_loss, want_grad = PC.pc_softmax_ce(x, y, prop, 255, red, dtype=torch.float64)
+        loss, grad = run_module(P.PCSoftmaxCrossEntropyV2(prop, red, 255), x.cuda(), y.cuda())
+        assert_loss_close(loss, want_loss, atol=2e-6 if red == "none" else 1e-7, what="pc softmax %s loss" % red)
+        (_check_scaled if red == "mean" else assert_grad_close)(grad, want_grad, what="pc softmax %s grad" % red)
+        assert bool((grad.cpu().transpose(0, 1)[:, y == 255] == 0).all())
+
+
+@pytest.mark.parametrize("shape", [(2, 19, 512, 512), (1, 150, 512, 512)], ids=["19ch", "150ch"])
+@pytest.mark.parametrize("use_log", [False, True])
+def test_taylor_softmax_at_bench_shapes(shape, use_log):
+    """The two Taylor workloads of the benchmark at full per-item size: all channels of a pixel pair
+    in one thread's registers (19), channel slices over the threads of a block (150)."""
+    import pytorch_loss as P
+    from oracle import taylor as OT
+    g = torch.Generator().manual_seed(77 + shape[1])
+    x = torch.randn(shape, generator=g) * 1.4
+    up = torch.randn(shape, generator=g)
+    want, want_grad = OT.taylor_softmax(x, 1, 2, use_log, upstream=up, dtype=torch.float64)
+    xg = x.cuda().requires_grad_(True)
+    out = (P.LogTaylorSoftmaxV3 if use_log else P.TaylorSoftmaxV3)(dim=1, n=2)(xg)
+    out.backward(up.cuda())
+    assert_loss_close(out.detach(), want, atol=2e-6, what="taylor output")
+    assert_grad_close(xg.grad, want_grad, what="taylor gradient")
