@@ -55,7 +55,7 @@ L2_BYTES = 126 << 20
 # workloads the reference's own V3 CUDA build is timed on (N=1): every one of them ran to the end
 # on a B200 when first tried; a workload whose reference kernels fault or hang is taken off here
 REFERENCE_V3_WORKLOADS = ("lmargin", "lsr", "focal", "lsr_rows", "lovasz", "lovasz_full", "ohem", "focal_up2",
-                          "lmargin_none", "lsr_none", "taylor", "taylor_c150", "pc_softmax")
+                          "lmargin_none", "lsr_none", "taylor", "taylor_c150", "pc_softmax", "lsr_nhwc", "lmargin_nhwc")
 
 
 def measured_peak():
@@ -74,7 +74,8 @@ def measured_traffic(wl):
     try:
         with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as fh:
             recs = json.load(fh)["workloads"]
-        rec = recs.get(wl.name) or recs[wl.kind]       # (reduction 'none' variants: the separate kernels of their kind)
+        # (reduction 'none' variants: the separate kernels of their kind; other layouts: own captures only)
+        rec = recs.get(wl.name) or (recs[wl.kind] if wl.layout == 'nchw' else None)
         key = "fused" if (wl.fused_softmax() or wl.kind not in ("lsr", "lsr_rows", "lmargin")) else "separate"
         f, b = rec[key]
         return f * wl.elems, b * wl.elems
@@ -361,6 +362,8 @@ def direct_calls(wl, sets, device):
     ys = [y for _, y in sets]
     n, c = wl.shape[0], wl.shape[1]
     m = wl.elems // (n * c)
+    if wl.layout == 'nhwc':                 # every pixel is a row of C contiguous logits
+        n, m = n * m, 1
     dt = _cabi.dtype_code(xs[0])
     denoms = [_cabi._vp(r.data_ptr() + 8) for r in recs]
     rescale = lambda i: _cabi.check(lib.b200_rescale_gradient(P(grads[i]), P(up), None, wl.elems, dt, st))

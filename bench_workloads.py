@@ -13,19 +13,21 @@ import torch
 
 
 class Workload:
-    def __init__(self, name, cfg, shape, dtype, desc, cpu_sample_items, kind=None, upstream=1.0, reduction='mean'):
+    def __init__(self, name, cfg, shape, dtype, desc, cpu_sample_items, kind=None, upstream=1.0, reduction='mean',
+                 layout='nchw'):
         self.name, self.cfg, self.shape, self.dtype, self.desc = name, cfg, shape, dtype, desc
         self.cpu_sample_items = cpu_sample_items     # batch items timed on the CPU baseline
         self.kind = kind or name                     # which loss / kernel family (variants share one)
         self.upstream = upstream                     # d(objective)/d(loss) handed to backward
         self.reduction = reduction                   # 'none': per-pixel losses out, a per-pixel upstream tensor in
+        self.layout = layout                         # 'nhwc': channels-last logits (torch.channels_last), consumed in place
 
     def with_items(self, items, note=None):
         """The same workload with another batch size (reduced cases for profiler captures, and a
         rank's shard of the global batch in multi-GPU runs)."""
         return Workload(self.name, self.cfg, (items,) + tuple(self.shape[1:]), self.dtype,
                         self.desc + (note or " [batch %d]" % items), min(self.cpu_sample_items, items),
-                        self.kind, self.upstream, self.reduction)
+                        self.kind, self.upstream, self.reduction, self.layout)
 
     @property
     def elems(self):
@@ -108,6 +110,12 @@ class Workload:
     def make(self, seed_offset=0, device="cpu", items=None):
         """(logits, labels) for `items` batch items (default: all).  device='cpu' gives the
         canonical seeded tensors; a CUDA device draws the same distributions there."""
+        logits, labels = self._make(seed_offset, device, items)
+        if self.layout == 'nhwc':
+            logits = logits.contiguous(memory_format=torch.channels_last)
+        return logits, labels
+
+    def _make(self, seed_offset, device, items):
         shape = list(self.shape)
         if items is not None:
             shape[0] = items
@@ -242,6 +250,13 @@ WORKLOADS = {
                          "LabelSmoothSoftmaxCEV3 fp32 [16,19,512,512], 5% ignored, reduction 'none', per-pixel "
                          "upstream gradient (the separate forward and backward kernels)", 16, kind="lsr",
                          reduction='none'),
+    # configurations 1 and 3 with channels-last logits (what a network in torch.channels_last hands over)
+    "lsr_nhwc": Workload("lsr_nhwc", 1, (16, 19, 512, 512), torch.float32,
+                         "LabelSmoothSoftmaxCEV3 fp32 [16,19,512,512] channels-last, 5% ignored, mean", 16,
+                         kind="lsr", layout='nhwc'),
+    "lmargin_nhwc": Workload("lmargin_nhwc", 3, (8, 150, 512, 512), torch.float32,
+                             "LargeMarginSoftmaxV3 fp32 [8,150,512,512] channels-last, 10% ignored, mean", 1,
+                             kind="lmargin", layout='nhwc'),
     # not baseline configurations: the relabelling step in front of the loss, and the two other
     # softmax variants of the reference on the shape of configuration 1
     "ohem": Workload("ohem", 6, (16, 19, 512, 512), torch.float32,

@@ -1750,6 +1750,208 @@ rows_warp_fwd_kernel(const SoftmaxParams prm) {
     if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
+// ------------------------------------------------------------- short-rows regime
+// M == 1 with few channels: [N, C] inputs and channels-last images, where every pixel is a row of
+// C contiguous logits (C x element size need not be a multiple of 16).  A stage holds R = 256 / TPR
+// consecutive rows -- ONE contiguous run of R * C elements, moved by one bulk copy in and, in
+// backward, one bulk copy out (R is a multiple of 16, so every run starts and ends on 16 bytes) --
+// together with the R labels.  TPR adjacent lanes (1, 2, 4, 8 or 16: at most 32 channels per
+// lane) share a row and combine their statistics with shuffles: no block barrier, no shared-memory
+// exchange.  A lane walks its channels starting at an offset that depends on the row (row mod C,
+// wrapping around), so that the lanes of a warp, whose rows lie C words apart, do not all hit one
+// bank when C is even.  The last rows of the input (fewer than R) have no 16-byte guarantee: the
+// compute threads move them with plain loads and stores.
+constexpr int kShortCompute = 256;
+constexpr int kShortBlock = kShortCompute + 64;
+
+// Statistics of a row combined over its TPR adjacent lanes.  `mask` names exactly those lanes: the
+// lanes of a row take the same branches (a row is valid or ignored as a whole), other rows of
+// the warp may be elsewhere.
+template <int KIND> struct LaneMerge;
+template <> struct LaneMerge<kLSR> {
+    static __device__ __forceinline__ void s1(Stat1<kLSR> &a, int tpr, unsigned mask) {
+        for (int o = tpr >> 1; o > 0; o >>= 1) a.m = fmaxf(a.m, __shfl_xor_sync(mask, a.m, o));
+    }
+    static __device__ __forceinline__ void s2(Stat2<kLSR> &b, int tpr, unsigned mask) {
+        for (int o = tpr >> 1; o > 0; o >>= 1) {
+            b.s += __shfl_xor_sync(mask, b.s, o);
+            b.sx += __shfl_xor_sync(mask, b.sx, o);
+            b.xl += __shfl_xor_sync(mask, b.xl, o);
+        }
+    }
+};
+template <> struct LaneMerge<kLMargin> {
+    static __device__ __forceinline__ void s1(Stat1<kLMargin> &a, int tpr, unsigned mask) {
+        for (int o = tpr >> 1; o > 0; o >>= 1) {
+            a.m_no = fmaxf(a.m_no, __shfl_xor_sync(mask, a.m_no, o));
+            a.xl = fmaxf(a.xl, __shfl_xor_sync(mask, a.xl, o));
+        }
+    }
+    static __device__ __forceinline__ void s2(Stat2<kLMargin> &b, int tpr, unsigned mask) {
+        for (int o = tpr >> 1; o > 0; o >>= 1) {
+            b.s_no += __shfl_xor_sync(mask, b.s_no, o);
+            b.sde += __shfl_xor_sync(mask, b.sde, o);
+            b.sd += __shfl_xor_sync(mask, b.sd, o);
+        }
+    }
+};
+
+template <typename T, int KIND, bool BWD, bool REDUCE>
+__global__ void __launch_bounds__(kShortBlock)
+rows_multi_kernel(const SoftmaxParams prm) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ PipeBarriers bars;
+    __shared__ double sh_red[64];
+
+    const int C = static_cast<int>(prm.C), NS = prm.stages, TPR = prm.KS;
+    const int R = kShortCompute / TPR;                       // rows per stage
+    unsigned char *base = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    const size_t label_off = (size_t(R) * C * sizeof(T) + 127) & ~size_t(127);
+    const size_t stage_bytes = label_off + size_t(R) * sizeof(int64_t);
+    const int tid = threadIdx.x;
+    unsigned *status = prm.workspace ? reinterpret_cast<unsigned *>(prm.workspace) + 1 : nullptr;
+    const int64_t n_stages = (prm.N + R - 1) / R;
+    const uint32_t full_bytes = uint32_t(R) * C * sizeof(T);
+
+    pipe_init<kShortCompute, BWD>(bars, NS);
+    const int64_t first = blockIdx.x, stride = gridDim.x;
+    double acc_loss = 0.0, acc_cnt = 0.0;
+
+    if (tid == kShortCompute) {
+        int k = 0;
+        for (int64_t st = first; st < n_stages; st += stride, ++k) {
+            const int s = k % NS;
+            if (k >= NS && !mbar_wait_bounded(&bars.empty[s], ((k / NS) - 1) & 1, status)) break;
+            const int64_t row0 = st * R;
+            if (prm.N - row0 >= R) {
+                unsigned char *stage = base + s * stage_bytes;
+                const unsigned char *src = static_cast<const unsigned char *>(prm.logits) + row0 * C * sizeof(T);
+                mbar_expect_tx(&bars.full[s], full_bytes + uint32_t(R) * sizeof(int64_t));
+                for (uint32_t off = 0; off < full_bytes; off += 32768u) {
+                    const uint32_t nb = full_bytes - off < 32768u ? full_bytes - off : 32768u;
+                    bulk_load_1d(stage + off, src + off, nb, &bars.full[s]);
+                }
+                bulk_load_1d(stage + label_off, prm.labels + row0, uint32_t(R) * sizeof(int64_t), &bars.full[s]);
+            } else {
+                mbar_expect_tx(&bars.full[s], 0);            // ragged end: the compute threads fetch it themselves
+            }
+        }
+    } else if (BWD && tid == kShortCompute + 32) {
+        int k = 0;
+        for (int64_t st = first; st < n_stages; st += stride, ++k) {
+            const int s = k % NS;
+            if (!mbar_wait_bounded(&bars.ready[s], (k / NS) & 1, status)) break;
+            const int64_t row0 = st * R;
+            if (prm.N - row0 >= R) {
+                const unsigned char *stage = base + s * stage_bytes;
+                unsigned char *dst = static_cast<unsigned char *>(prm.grads) + row0 * C * sizeof(T);
+                for (uint32_t off = 0; off < full_bytes; off += 32768u) {
+                    const uint32_t nb = full_bytes - off < 32768u ? full_bytes - off : 32768u;
+                    bulk_store_1d(dst + off, stage + off, nb);
+                }
+                bulk_commit();
+                bulk_wait_read_all();
+            }
+            mbar_arrive(&bars.empty[s]);
+        }
+        bulk_wait_all();
+    } else if (tid < kShortCompute) {
+        const int lane = tid & 31;
+        const int rowl = tid / TPR, t = tid % TPR;           // my row inside a stage, my lane inside the row
+        const int rot = rowl % C;                            // where my walk over the channels starts
+        const unsigned row_mask = (TPR == 32 ? 0xffffffffu : ((1u << TPR) - 1u)) << (lane & ~(TPR - 1));
+        const T *gout = static_cast<const T *>(prm.grad_out);
+        T *losses = static_cast<T *>(prm.losses);
+        const LossConsts kc = prm.k;
+        float gscale = 1.f;
+        if (BWD && REDUCE) pdl_wait();                       // (see tile_pair_kernel)
+        if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
+        int k = 0;
+        for (int64_t st = first; st < n_stages; st += stride, ++k) {
+            const int s = k % NS;
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(&bars.full[s], (k / NS) & 1, status);
+            // (the ragged last stage needs all compute threads at a named barrier, which has no
+            // time limit: every stage's decision to go on is taken by all of them together)
+            if (!compute_all(ok, kShortCompute)) break;
+            const int64_t row0 = st * R;
+            const int nrows = prm.N - row0 >= R ? R : int(prm.N - row0);
+            const bool ragged = nrows < R;
+            T *tile = reinterpret_cast<T *>(base + s * stage_bytes);
+            int64_t *tile_labels = reinterpret_cast<int64_t *>(base + s * stage_bytes + label_off);
+            if (ragged) {
+                const T *src = static_cast<const T *>(prm.logits) + row0 * C;
+                for (int e = tid; e < nrows * C; e += kShortCompute) tile[e] = src[e];
+                for (int e = tid; e < nrows; e += kShortCompute) tile_labels[e] = prm.labels[row0 + e];
+                compute_sync(kShortCompute);
+            }
+            const bool live = rowl < nrows;
+            const int64_t row = row0 + rowl;
+            const int64_t lb = live ? tile_labels[rowl] : prm.ignore;
+            const bool valid = live && lb != prm.ignore;
+            const int lbi = valid ? ((lb >= 0 && lb < C) ? int(lb) : -2) : -1;
+            T *rp = tile + size_t(rowl) * C;
+            if (valid) {
+                Stat1<KIND> s1;
+                s1.init();
+                for (int p = t, j = t + rot; p < C; p += TPR, j += TPR) {
+                    if (j >= C) j -= C;
+                    s1.add(to_f32(rp[j]), j == lbi);
+                }
+                LaneMerge<KIND>::s1(s1, TPR, row_mask);
+                Stat2<KIND> s2;
+                s2.init();
+                for (int p = t, j = t + rot; p < C; p += TPR, j += TPR) {
+                    if (j >= C) j -= C;
+                    s2.add(to_f32(rp[j]), j == lbi, s1);
+                }
+                LaneMerge<KIND>::s2(s2, TPR, row_mask);
+                PixelFinal<KIND> fin;
+                fin.finish(s1, s2, kc);
+                if (t == 0) {
+                    if (!BWD && losses) losses[row] = from_f32<T>(fin.loss);
+                    if (REDUCE) {
+                        acc_loss += double(fin.loss);
+                        acc_cnt += 1.0;
+                    }
+                }
+                if (BWD) {
+                    float psc = gscale;
+                    if (prm.grad_mode == 2) psc *= to_f32(gout[row]);
+                    for (int p = t, j = t + rot; p < C; p += TPR, j += TPR) {
+                        if (j >= C) j -= C;
+                        rp[j] = from_f32<T>(fin.grad(to_f32(rp[j]), j == lbi, kc) * psc);
+                    }
+                }
+            } else if (live) {
+                if (!BWD && losses && t == 0) losses[row] = from_f32<T>(0.f);
+                if (BWD)
+                    for (int p = t; p < C; p += TPR) rp[p] = from_f32<T>(0.f);
+            }
+            if (!BWD) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.empty[s]);
+            } else {
+                if (ragged) {
+                    compute_sync(kShortCompute);
+                    T *dst = static_cast<T *>(prm.grads) + row0 * C;
+                    for (int e = tid; e < nrows * C; e += kShortCompute) dst[e] = tile[e];
+                } else {
+                    fence_proxy_async_smem();
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars.ready[s]);
+            }
+        }
+    }
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
+}
+
+// The layouts rows_multi_kernel takes.
+inline bool short_rows_eligible(const void *logits, const void *io, const void *labels, int64_t N, int64_t C, int64_t M) {
+    return M == 1 && N >= 1 && C >= 1 && C < 256 && aligned16(logits) && aligned16(io) && aligned16(labels);
+}
+
 // Integer tuning override from the environment (tile size, ring depth, blocks per SM);
 // unset or unparsable -> the default.
 
@@ -1981,6 +2183,29 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
         }
         return launch_status("softmax rows kernel launch");
     }
+    if (short_rows_eligible(prm.logits, io, prm.labels, prm.N, prm.C, prm.M)) {
+        // ---- short-rows regime
+        int tpr = 1;
+        while (tpr < 8 && (prm.C + tpr - 1) / tpr > 32) tpr <<= 1;
+        prm.KS = tpr;
+        const int R = kShortCompute / tpr;
+        const size_t label_off = (size_t(R) * prm.C * es + 127) & ~size_t(127);
+        const size_t stage_bytes = label_off + size_t(R) * sizeof(int64_t);
+        prm.stages = BWD ? 3 : 2;
+        const size_t smem = 128 + size_t(prm.stages) * stage_bytes;
+        int per_sm = int((224 * 1024) / (smem + 2048));
+        if (per_sm > 4) per_sm = 4;
+        if (per_sm < 1) per_sm = 1;
+        const int64_t n_stages = (prm.N + R - 1) / R;
+        int64_t grid = int64_t(sms) * per_sm;
+        if (grid > n_stages) grid = n_stages;
+        if (grid > kMaxPartials) grid = kMaxPartials;
+        auto kern = rows_multi_kernel<T, KIND, BWD, REDUCE>;
+        int rc;
+        if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
+        launch_kernel(kern, dim3(unsigned(grid)), dim3(kShortBlock), smem, stream, BWD && REDUCE && prm.after_count, prm);
+        return launch_status("softmax short-rows kernel launch");
+    }
     // ---- sweep regime
     const int64_t P = prm.N * prm.M;
     int64_t grid = (P + kThreads - 1) / kThreads;
@@ -2108,9 +2333,10 @@ int backward(const char *who, const void *logits, const int64_t *labels, const v
 inline bool fused_step_eligible(size_t es, const void *logits, const void *grads, const void *labels, int64_t N,
                                 int64_t C, int64_t M) {
     if (N < 1 || M < 1) return false;
-    if (M == 1)
-        return C >= 256 && size_t(C) * es + 1024 <= kSmemLimit && (size_t(C) * es) % 16 == 0 && aligned16(logits) &&
-               aligned16(grads);
+    if (M == 1) {
+        if (C < 256) return aligned16(logits) && aligned16(grads) && aligned16(labels);      // short rows
+        return size_t(C) * es + 1024 <= kSmemLimit && (size_t(C) * es) % 16 == 0 && aligned16(logits) && aligned16(grads);
+    }
     if (size_t(C) * 32 * es + 8192 > kSmemLimit) return false;
     return (M * es) % 16 == 0 && aligned16(logits) && aligned16(grads) && aligned16(labels) &&
            M < (int64_t(1) << 31) && N < (int64_t(1) << 31);
