@@ -1757,9 +1757,7 @@ rows_warp_fwd_kernel(const SoftmaxParams prm) {
 // backward, one bulk copy out (R is a multiple of 16, so every run starts and ends on 16 bytes) --
 // together with the R labels.  TPR adjacent lanes (1, 2, 4, 8 or 16: at most 32 channels per
 // lane) share a row and combine their statistics with shuffles: no block barrier, no shared-memory
-// exchange.  A lane walks its channels starting at an offset that depends on the row (row mod C,
-// wrapping around), so that the lanes of a warp, whose rows lie C words apart, do not all hit one
-// bank when C is even.  The last rows of the input (fewer than R) have no 16-byte guarantee: the
+// exchange.  The last rows of the input (fewer than R) have no 16-byte guarantee: the
 // compute threads move them with plain loads and stores.
 constexpr int kShortCompute = 256;
 constexpr int kShortBlock = kShortCompute + 64;
@@ -1858,7 +1856,22 @@ rows_multi_kernel(const SoftmaxParams prm) {
     } else if (tid < kShortCompute) {
         const int lane = tid & 31;
         const int rowl = tid / TPR, t = tid % TPR;           // my row inside a stage, my lane inside the row
-        const int rot = rowl % C;                            // where my walk over the channels starts
+        // One lane per row: its walk over the channels starts at an offset that depends on the row
+        // when C is even (the rows of a warp lie C words apart: without it they would share banks).
+        // Several lanes per row walk their channels t, t + TPR, ... in order: the lanes of a row
+        // touch adjacent banks and few rows share a warp.
+        const int rot = (TPR == 1 && (C & 1) == 0) ? rowl % C : 0;
+        auto walk = [&](auto &&body) {
+            if (TPR == 1) {
+#pragma unroll 4
+                for (int j = rot; j < C; ++j) body(j);
+#pragma unroll 4
+                for (int j = 0; j < rot; ++j) body(j);
+            } else {
+#pragma unroll 4
+                for (int j = t; j < C; j += TPR) body(j);
+            }
+        };
         const unsigned row_mask = (TPR == 32 ? 0xffffffffu : ((1u << TPR) - 1u)) << (lane & ~(TPR - 1));
         const T *gout = static_cast<const T *>(prm.grad_out);
         T *losses = static_cast<T *>(prm.losses);
@@ -1894,17 +1907,11 @@ rows_multi_kernel(const SoftmaxParams prm) {
             if (valid) {
                 Stat1<KIND> s1;
                 s1.init();
-                for (int p = t, j = t + rot; p < C; p += TPR, j += TPR) {
-                    if (j >= C) j -= C;
-                    s1.add(to_f32(rp[j]), j == lbi);
-                }
+                walk([&](int j) { s1.add(to_f32(rp[j]), j == lbi); });
                 LaneMerge<KIND>::s1(s1, TPR, row_mask);
                 Stat2<KIND> s2;
                 s2.init();
-                for (int p = t, j = t + rot; p < C; p += TPR, j += TPR) {
-                    if (j >= C) j -= C;
-                    s2.add(to_f32(rp[j]), j == lbi, s1);
-                }
+                walk([&](int j) { s2.add(to_f32(rp[j]), j == lbi, s1); });
                 LaneMerge<KIND>::s2(s2, TPR, row_mask);
                 PixelFinal<KIND> fin;
                 fin.finish(s1, s2, kc);
@@ -1918,10 +1925,7 @@ rows_multi_kernel(const SoftmaxParams prm) {
                 if (BWD) {
                     float psc = gscale;
                     if (prm.grad_mode == 2) psc *= to_f32(gout[row]);
-                    for (int p = t, j = t + rot; p < C; p += TPR, j += TPR) {
-                        if (j >= C) j -= C;
-                        rp[j] = from_f32<T>(fin.grad(to_f32(rp[j]), j == lbi, kc) * psc);
-                    }
+                    walk([&](int j) { rp[j] = from_f32<T>(fin.grad(to_f32(rp[j]), j == lbi, kc) * psc); });
                 }
             } else if (live) {
                 if (!BWD && losses && t == 0) losses[row] = from_f32<T>(0.f);
