@@ -2189,6 +2189,9 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
     }
     if (short_rows_eligible(prm.logits, io, prm.labels, prm.N, prm.C, prm.M)) {
         // ---- short-rows regime
+        // at most 32 channels per lane, 3 stages in backward (measured on the fused steps of configs 1
+        // and 3 in channels-last: 0.148 / 0.797 ms; 2 or 4 stages 0.162 / 0.93-0.95 ms; 16 channels per
+        // lane doubles config 1's time; 40 per lane and 2 stages: 0.163 / 0.760 ms)
         int tpr = 1;
         while (tpr < 8 && (prm.C + tpr - 1) / tpr > 32) tpr <<= 1;
         prm.KS = tpr;
