@@ -257,6 +257,10 @@ WORKLOADS = {
     "lmargin_nhwc": Workload("lmargin_nhwc", 3, (8, 150, 512, 512), torch.float32,
                              "LargeMarginSoftmaxV3 fp32 [8,150,512,512] channels-last, 10% ignored, mean", 1,
                              kind="lmargin", layout='nhwc'),
+    # label smoothing where it is used most: classification logits [batch, classes]
+    "lsr_cls": Workload("lsr_cls", 10, (65536, 1000), torch.float32,
+                        "LabelSmoothSoftmaxCEV3 fp32 [65536,1000] (classification rows), 5% ignored, mean", 8192,
+                        kind="lsr"),
     # not baseline configurations: the relabelling step in front of the loss, and the two other
     # softmax variants of the reference on the shape of configuration 1
     "ohem": Workload("ohem", 6, (16, 19, 512, 512), torch.float32,

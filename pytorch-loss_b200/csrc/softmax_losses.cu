@@ -1751,16 +1751,17 @@ rows_warp_fwd_kernel(const SoftmaxParams prm) {
 }
 
 // ------------------------------------------------------------- short-rows regime
-// M == 1 with few channels: [N, C] inputs and channels-last images, where every pixel is a row of
-// C contiguous logits (C x element size need not be a multiple of 16).  A stage holds R = 256 / TPR
-// consecutive rows -- ONE contiguous run of R * C elements, moved by one bulk copy in and, in
-// backward, one bulk copy out (R is a multiple of 16, so every run starts and ends on 16 bytes) --
-// together with the R labels.  TPR adjacent lanes (1, 2, 4, 8 or 16: at most 32 channels per
-// lane) share a row and combine their statistics with shuffles: no block barrier, no shared-memory
+// M == 1 with up to 2048 channels: [N, C] classification inputs and channels-last images, where
+// every pixel is a row of C contiguous logits (C x element size need not be a multiple of 16).  A
+// stage holds R = 256 / TPR consecutive rows -- ONE contiguous run of R * C elements, moved by one bulk copy in and, in
+// backward, one bulk copy out (R is a multiple of 8 and an element has 2 or 4 bytes, so every run starts and ends on 16 bytes) --
+// together with the R labels.  TPR adjacent lanes (1 to 32: at most 32 channels per lane up to
+// 1024 channels, 64 beyond) share a row and combine their statistics with shuffles: no block barrier, no shared-memory
 // exchange.  The last rows of the input (fewer than R) have no 16-byte guarantee: the
 // compute threads move them with plain loads and stores.
 constexpr int kShortCompute = 256;
 constexpr int kShortBlock = kShortCompute + 64;
+constexpr int kShortRowsMaxC = 2048;          // a warp per row, 64 channels per lane
 
 // Statistics of a row combined over its TPR adjacent lanes.  `mask` names exactly those lanes: the
 // lanes of a row take the same branches (a row is valid or ignored as a whole), other rows of
@@ -1953,7 +1954,7 @@ rows_multi_kernel(const SoftmaxParams prm) {
 
 // The layouts rows_multi_kernel takes.
 inline bool short_rows_eligible(const void *logits, const void *io, const void *labels, int64_t N, int64_t C, int64_t M) {
-    return M == 1 && N >= 1 && C >= 1 && C < 256 && aligned16(logits) && aligned16(io) && aligned16(labels);
+    return M == 1 && N >= 1 && C >= 1 && C <= kShortRowsMaxC && aligned16(logits) && aligned16(io) && aligned16(labels);
 }
 
 // Integer tuning override from the environment (tile size, ring depth, blocks per SM);
@@ -2129,6 +2130,32 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
         set_error("pc softmax step: this layout has no fused step");
         return B200_ERR_UNSUPPORTED;
     } else {
+    if (short_rows_eligible(prm.logits, io, prm.labels, prm.N, prm.C, prm.M)) {
+        // ---- short-rows regime
+        // at most 32 channels per lane, 3 stages in backward (measured on the fused steps of configs 1
+        // and 3 in channels-last: 0.148 / 0.797 ms; 2 or 4 stages 0.162 / 0.93-0.95 ms; 16 channels per
+        // lane doubles config 1's time; 40 per lane and 2 stages: 0.163 / 0.760 ms)
+        int tpr = 1;
+        while (tpr < 32 && (prm.C + tpr - 1) / tpr > 32) tpr <<= 1;
+        prm.KS = tpr;
+        const int R = kShortCompute / tpr;
+        const size_t label_off = (size_t(R) * prm.C * es + 127) & ~size_t(127);
+        const size_t stage_bytes = label_off + size_t(R) * sizeof(int64_t);
+        prm.stages = (BWD && stage_bytes <= size_t(36) * 1024) ? 3 : 2;
+        const size_t smem = 128 + size_t(prm.stages) * stage_bytes;
+        int per_sm = int((224 * 1024) / (smem + 2048));
+        if (per_sm > 4) per_sm = 4;
+        if (per_sm < 1) per_sm = 1;
+        const int64_t n_stages = (prm.N + R - 1) / R;
+        int64_t grid = int64_t(sms) * per_sm;
+        if (grid > n_stages) grid = n_stages;
+        if (grid > kMaxPartials) grid = kMaxPartials;
+        auto kern = rows_multi_kernel<T, KIND, BWD, REDUCE>;
+        int rc;
+        if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
+        launch_kernel(kern, dim3(unsigned(grid)), dim3(kShortBlock), smem, stream, BWD && REDUCE && prm.after_count, prm);
+        return launch_status("softmax short-rows kernel launch");
+    }
     if constexpr (!BWD) {
         // ---- rows regime, forward, long rows: one warp per row, streamed (any row length)
         if (prm.M == 1 && (size_t(prm.C) * es) % 16 == 0 && size_t(prm.C) * es >= 2 * size_t(kWarpRowChunk) &&
@@ -2186,32 +2213,6 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             kern<<<dim3(unsigned(grid)), kThreads, smem, stream>>>(prm);
         }
         return launch_status("softmax rows kernel launch");
-    }
-    if (short_rows_eligible(prm.logits, io, prm.labels, prm.N, prm.C, prm.M)) {
-        // ---- short-rows regime
-        // at most 32 channels per lane, 3 stages in backward (measured on the fused steps of configs 1
-        // and 3 in channels-last: 0.148 / 0.797 ms; 2 or 4 stages 0.162 / 0.93-0.95 ms; 16 channels per
-        // lane doubles config 1's time; 40 per lane and 2 stages: 0.163 / 0.760 ms)
-        int tpr = 1;
-        while (tpr < 8 && (prm.C + tpr - 1) / tpr > 32) tpr <<= 1;
-        prm.KS = tpr;
-        const int R = kShortCompute / tpr;
-        const size_t label_off = (size_t(R) * prm.C * es + 127) & ~size_t(127);
-        const size_t stage_bytes = label_off + size_t(R) * sizeof(int64_t);
-        prm.stages = BWD ? 3 : 2;
-        const size_t smem = 128 + size_t(prm.stages) * stage_bytes;
-        int per_sm = int((224 * 1024) / (smem + 2048));
-        if (per_sm > 4) per_sm = 4;
-        if (per_sm < 1) per_sm = 1;
-        const int64_t n_stages = (prm.N + R - 1) / R;
-        int64_t grid = int64_t(sms) * per_sm;
-        if (grid > n_stages) grid = n_stages;
-        if (grid > kMaxPartials) grid = kMaxPartials;
-        auto kern = rows_multi_kernel<T, KIND, BWD, REDUCE>;
-        int rc;
-        if ((rc = set_smem(kern, smem)) != B200_OK) return rc;
-        launch_kernel(kern, dim3(unsigned(grid)), dim3(kShortBlock), smem, stream, BWD && REDUCE && prm.after_count, prm);
-        return launch_status("softmax short-rows kernel launch");
     }
     // ---- sweep regime
     const int64_t P = prm.N * prm.M;
@@ -2341,7 +2342,7 @@ inline bool fused_step_eligible(size_t es, const void *logits, const void *grads
                                 int64_t C, int64_t M) {
     if (N < 1 || M < 1) return false;
     if (M == 1) {
-        if (C < 256) return aligned16(logits) && aligned16(grads) && aligned16(labels);      // short rows
+        if (C <= kShortRowsMaxC && aligned16(logits) && aligned16(grads) && aligned16(labels)) return true;   // short rows
         return size_t(C) * es + 1024 <= kSmemLimit && (size_t(C) * es) % 16 == 0 && aligned16(logits) && aligned16(grads);
     }
     if (size_t(C) * 32 * es + 8192 > kSmemLimit) return false;
