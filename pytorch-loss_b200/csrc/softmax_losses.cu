@@ -1857,22 +1857,32 @@ rows_multi_kernel(const SoftmaxParams prm) {
     } else if (tid < kShortCompute) {
         const int lane = tid & 31;
         const int rowl = tid / TPR, t = tid % TPR;           // my row inside a stage, my lane inside the row
-        // One lane per row: its walk over the channels starts at an offset that depends on the row
-        // when C is even (the rows of a warp lie C words apart: without it they would share banks).
-        // Several lanes per row walk their channels t, t + TPR, ... in order: the lanes of a row
-        // touch adjacent banks and few rows share a warp.
-        const int rot = (TPR == 1 && (C & 1) == 0) ? rowl % C : 0;
-        auto walk = [&](auto &&body) {
-            if (TPR == 1) {
+        // A lane visits the units (channels, or channel pairs) u = c * TPR + t of its row, chunk c
+        // after chunk c.  Few lanes per row and an even C: the rows of a warp lie an even number of
+        // words apart and would share banks, so the walk starts at a chunk that depends on the row
+        // and wraps around (same trip count in every lane: no divergence).  Otherwise (odd C, or
+        // 8+ lanes per row = few rows per warp) a plain strided loop.
+        const bool rotate = TPR <= 4 && (C & 1) == 0;
+        const int chunks_c = (C + TPR - 1) / TPR, chunks_p = ((C >> 1) + TPR - 1) / TPR;
+        const int rot_c = rotate ? rowl % chunks_c : 0, rot_p = (rotate && chunks_p > 0) ? rowl % chunks_p : 0;
+        auto walk_units = [&](int n, int chunks, int rot, auto &&body) {
+            if (!rotate && TPR == 1) {
 #pragma unroll 4
-                for (int j = rot; j < C; ++j) body(j);
+                for (int u = 0; u < n; ++u) body(u);            // (unit stride: immediate offsets after unrolling)
+            } else if (!rotate) {
 #pragma unroll 4
-                for (int j = 0; j < rot; ++j) body(j);
+                for (int u = t; u < n; u += TPR) body(u);
             } else {
+                int c = rot;
 #pragma unroll 4
-                for (int j = t; j < C; j += TPR) body(j);
+                for (int i = 0; i < chunks; ++i) {
+                    const int u = c * TPR + t;
+                    if (u < n) body(u);
+                    c = (c + 1 == chunks) ? 0 : c + 1;
+                }
             }
         };
+        auto walk = [&](auto &&body) { walk_units(C, chunks_c, rot_c, body); };
         const unsigned row_mask = (TPR == 32 ? 0xffffffffu : ((1u << TPR) - 1u)) << (lane & ~(TPR - 1));
         const T *gout = static_cast<const T *>(prm.grad_out);
         T *losses = static_cast<T *>(prm.losses);
@@ -1905,7 +1915,53 @@ rows_multi_kernel(const SoftmaxParams prm) {
             const bool valid = live && lb != prm.ignore;
             const int lbi = valid ? ((lb >= 0 && lb < C) ? int(lb) : -2) : -1;
             T *rp = tile + size_t(rowl) * C;
-            if (valid) {
+            if (KIND == kLSR && valid && (C & 1) == 0) {
+                // Label smooth, even C: the lane's channels as adjacent PAIRS (one 8-byte -- half
+                // types 4-byte -- access and packed fp32x2 arithmetic per pair), e^{x-m} kept in the
+                // tile between the sum and the gradient (one exponential per element), the target
+                // term added by the lane that owns the label's pair (tile_pair_kernel's scheme).
+                const int npair = C >> 1;
+                const float xl = lbi >= 0 ? to_f32(rp[lbi]) : 0.f;
+                __syncwarp(row_mask);                          // all of the row's lanes hold x_lb before e^{x-m} overwrites it
+                float2 m2 = splat2(kNegInf);
+                walk_units(npair, chunks_p, rot_p, [&](int q) { m2 = max2(m2, ld_pair(rp + 2 * q)); });
+                float m = fmaxf(m2.x, m2.y);
+                for (int o = TPR >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(row_mask, m, o));
+                pk_t psum = psplat(0.f), psx = psplat(0.f);
+                {
+                    const pk_t nml = psplat(-m * kLog2e), l2e = psplat(kLog2e);
+                    walk_units(npair, chunks_p, rot_p, [&](int q) {
+                        const pk_t x = ld_pk(rp + 2 * q);
+                        const pk_t e = pex2(pfma(x, l2e, nml));
+                        psum = padd(psum, e);
+                        psx = padd(psx, x);
+                        if (BWD) st_pk(rp + 2 * q, e);
+                    });
+                }
+                float2 s2v = upk2(psum), sxv = upk2(psx);
+                float sum = s2v.x + s2v.y, sx = sxv.x + sxv.y;
+                for (int o = TPR >> 1; o > 0; o >>= 1) {
+                    sum += __shfl_xor_sync(row_mask, sum, o);
+                    sx += __shfl_xor_sync(row_mask, sx, o);
+                }
+                const float loss = kc.sumy * (m + __logf(sum)) - kc.lb_neg * sx - (kc.lb_pos - kc.lb_neg) * xl;
+                if (t == 0) {
+                    if (!BWD && losses) losses[row] = from_f32<T>(loss);
+                    if (REDUCE) {
+                        acc_loss += double(loss);
+                        acc_cnt += 1.0;
+                    }
+                }
+                if (BWD) {
+                    float psc = gscale;
+                    if (prm.grad_mode == 2) psc *= to_f32(gout[row]);
+                    // g = (sumy e / s - lb_neg) scale, then the target's lb_neg -> lb_pos
+                    const pk_t pa = psplat(kc.sumy * __fdividef(psc, sum)), pb = psplat(-kc.lb_neg * psc);
+                    walk_units(npair, chunks_p, rot_p, [&](int q) { st_pk(rp + 2 * q, pfma(ld_pk(rp + 2 * q), pa, pb)); });
+                    if (lbi >= 0 && (lbi >> 1) % TPR == t)
+                        rp[lbi] = from_f32<T>(to_f32(rp[lbi]) - (kc.lb_pos - kc.lb_neg) * psc);
+                }
+            } else if (valid) {
                 Stat1<KIND> s1;
                 s1.init();
                 walk([&](int j) { s1.add(to_f32(rp[j]), j == lbi); });
