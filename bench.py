@@ -55,7 +55,7 @@ L2_BYTES = 126 << 20
 # workloads the reference's own V3 CUDA build is timed on (N=1): every one of them ran to the end
 # on a B200 when first tried; a workload whose reference kernels fault or hang is taken off here
 REFERENCE_V3_WORKLOADS = ("lmargin", "lsr", "focal", "lsr_rows", "lovasz", "lovasz_full", "ohem", "focal_up2",
-                          "lmargin_none", "lsr_none", "taylor", "taylor_c150", "pc_softmax", "lsr_nhwc", "lmargin_nhwc", "lsr_cls")
+                          "lmargin_none", "lsr_none", "taylor", "taylor_c150", "pc_softmax", "lsr_nhwc", "lmargin_nhwc", "lsr_cls", "lsr_769")
 
 
 def measured_peak():
@@ -75,7 +75,7 @@ def measured_traffic(wl):
         with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as fh:
             recs = json.load(fh)["workloads"]
         # (reduction 'none' variants: the separate kernels of their kind; other layouts: own captures only)
-        rec = recs.get(wl.name) or (recs[wl.kind] if (wl.layout == 'nchw' and len(wl.shape) > 2) else None)
+        rec = recs.get(wl.name) or (recs[wl.kind] if (wl.layout == 'nchw' and len(wl.shape) > 2 and wl.pixels // wl.shape[0] % 4 == 0) else None)
         key = "fused" if (wl.fused_softmax() or wl.kind not in ("lsr", "lsr_rows", "lmargin")) else "separate"
         f, b = rec[key]
         return f * wl.elems, b * wl.elems

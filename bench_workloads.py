@@ -257,6 +257,10 @@ WORKLOADS = {
     "lmargin_nhwc": Workload("lmargin_nhwc", 3, (8, 150, 512, 512), torch.float32,
                              "LargeMarginSoftmaxV3 fp32 [8,150,512,512] channels-last, 10% ignored, mean", 1,
                              kind="lmargin", layout='nhwc'),
+    # a crop size that is not a multiple of 4 pixels (769 x 769): channel rows start on no 16-byte boundary
+    "lsr_769": Workload("lsr_769", 11, (8, 19, 769, 769), torch.float32,
+                        "LabelSmoothSoftmaxCEV3 fp32 [8,19,769,769] (odd image size), 5% ignored, mean", 4,
+                        kind="lsr"),
     # label smoothing where it is used most: classification logits [batch, classes]
     "lsr_cls": Workload("lsr_cls", 10, (65536, 1000), torch.float32,
                         "LabelSmoothSoftmaxCEV3 fp32 [65536,1000] (classification rows), 5% ignored, mean", 8192,

@@ -2013,6 +2013,147 @@ inline bool short_rows_eligible(const void *logits, const void *io, const void *
     return M == 1 && N >= 1 && C >= 1 && C <= kShortRowsMaxC && aligned16(logits) && aligned16(io) && aligned16(labels);
 }
 
+// ------------------------------------------------------------- any-alignment spatial regime
+// M > 1 where the rows of a channel do not start on 16 bytes (M not a multiple of 4 floats: 769 x
+// 769 or 713 x 713 crops) or the pointers are not aligned: no tensor map, no bulk copy.  The 256
+// threads of a block are KS channel slices x (256 / KS) adjacent pixels; a thread keeps its
+// slice's channels (every KS-th, at most CPT) of ONE pixel in registers -- 4-byte accesses, a warp
+// reads 128 contiguous bytes per channel wherever they start, all of a thread's loads in flight
+// together -- and the slices combine their statistics through shared memory (two block barriers
+// per group of pixels; none with a single slice).  The logits are read once.  float32 only.
+constexpr int kAnyThreads = 256;
+template <int KIND, bool BWD, bool REDUCE, int KS, int CPT>
+__global__ void __launch_bounds__(kAnyThreads, KS == 1 ? 3 : 2)
+spatial_any_kernel(const SoftmaxParams prm) {
+    constexpr int PX = kAnyThreads / KS;
+    __shared__ double sh_red[64];
+    __shared__ float ex[2][5][KS][PX];           // [round parity][statistic word][slice][pixel]
+    const float *x = static_cast<const float *>(prm.logits);
+    float *grads = static_cast<float *>(prm.grads);
+    float *losses = static_cast<float *>(prm.losses);
+    const float *gout = static_cast<const float *>(prm.grad_out);
+    const int C = static_cast<int>(prm.C);
+    const int Mi = static_cast<int>(prm.M);      // C * M < 2^31 (host check): 32-bit channel offsets
+    const int px = threadIdx.x % PX, ks = threadIdx.x / PX;
+    const int64_t groups_per_row = (prm.M + PX - 1) / PX;
+    const int64_t groups = prm.N * groups_per_row;
+    const LossConsts kc = prm.k;
+    float gscale = 1.f;
+    bool first = true;
+    double acc_loss = 0.0, acc_cnt = 0.0;
+    int par = 0;
+    for (int64_t gi = blockIdx.x; gi < groups; gi += gridDim.x, par ^= 1) {
+        const int64_t n = gi / groups_per_row;
+        const int64_t m = (gi % groups_per_row) * PX + px;
+        const bool live = m < prm.M;
+        const int64_t base = n * prm.C * prm.M + (live ? m : 0);
+        float xv[CPT];
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int j = ks + i * KS;
+            xv[i] = (live && j < C) ? __ldcs(x + base + j * Mi) : 0.f;
+        }
+        const int64_t lb = live ? prm.labels[n * prm.M + m] : prm.ignore;
+        if (first) {
+            if (BWD && REDUCE) pdl_wait();        // the divisor comes from the label count in front
+            if (BWD) gscale = uniform_grad_scale(prm.grad_out, prm.grad_mode, prm.denom);
+            first = false;
+        }
+        const bool valid = live && lb != prm.ignore;
+        const int lbi = valid ? ((lb >= 0 && lb < C) ? int(lb) : -2) : -1;
+        Stat1<KIND> s1;
+        s1.init();
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int j = ks + i * KS;
+            if (j < C) s1.add(xv[i], j == lbi);
+        }
+        if (KS > 1) {
+            s1.store(&ex[par][0][ks][px], KS * PX);
+            __syncthreads();
+#pragma unroll
+            for (int q = 1; q < KS; ++q) {
+                Stat1<KIND> o;
+                o.load(&ex[par][0][(ks + q) % KS][px], KS * PX);
+                s1.merge(o);
+            }
+        }
+        Stat2<KIND> s2;
+        s2.init();
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+            const int j = ks + i * KS;
+            if (j < C) {
+                if constexpr (KIND == kLSR) {
+                    // e^{x-m} takes x's place: the gradient needs nothing else (one exponential per element)
+                    const float e = exp_fast(xv[i] - s1_max(s1));
+                    s2_add_with_exp(s2, xv[i], e, j == lbi);
+                    xv[i] = e;
+                } else {
+                    s2.add(xv[i], j == lbi, s1);
+                }
+            }
+        }
+        if (KS > 1) {
+            s2.store(&ex[par][2][ks][px], KS * PX);
+            __syncthreads();
+            s2.init();
+#pragma unroll
+            for (int q = 0; q < KS; ++q) {       // (fixed order: every slice gets the same bits)
+                Stat2<KIND> o;
+                o.load(&ex[par][2][q][px], KS * PX);
+                s2.merge(o);
+            }
+        }
+        if (!live) continue;
+        PixelFinal<KIND> fin;
+        fin.finish(s1, s2, kc);
+        if (ks == 0) {
+            if (!BWD && losses) losses[n * prm.M + m] = valid ? fin.loss : 0.f;
+            if (REDUCE && valid) {
+                acc_loss += double(fin.loss);
+                acc_cnt += 1.0;
+            }
+        }
+        if (BWD) {
+            float psc = gscale;
+            if (prm.grad_mode == 2) psc *= gout[n * prm.M + m];
+            float *gb = grads + base;
+#pragma unroll
+            for (int i = 0; i < CPT; ++i) {
+                const int j = ks + i * KS;
+                if (j < C) __stcs(gb + j * Mi, valid ? grad_phase3<KIND>(fin, xv[i], j == lbi, kc) * psc : 0.f);
+            }
+        }
+    }
+    if (first && BWD && REDUCE) pdl_wait();
+    if (REDUCE) grid_reduce_finish(acc_loss, acc_cnt, prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
+}
+
+inline bool spatial_any_eligible(size_t es, int64_t C, int64_t M) {
+    return es == 4 && M > 1 && C <= 320 && C * M < (int64_t(1) << 31);
+}
+
+template <int KIND, bool BWD, bool REDUCE>
+int launch_spatial_any(const SoftmaxParams &prm, cudaStream_t stream) {
+    // slices x channels per thread; the unrolled loops run over all CPT slots, so CPT follows C
+    const int ks = prm.C <= 40 ? 1 : (prm.C <= 160 ? 4 : 8);
+    const int px = kAnyThreads / ks;
+    const int64_t rounds = prm.N * ((prm.M + px - 1) / px);
+    int64_t grid = int64_t(sm_count()) * 2 * (ks == 1 ? 4 : 1);   // a single slice has no barrier: short-lived blocks are fine
+    if (grid > rounds) grid = rounds;
+    if (grid > kMaxPartials) grid = kMaxPartials;
+    const dim3 gd{unsigned(grid)}, bd(kAnyThreads);
+    const bool dep = BWD && REDUCE && prm.after_count;
+    if (prm.C <= 8) launch_kernel(spatial_any_kernel<KIND, BWD, REDUCE, 1, 8>, gd, bd, 0, stream, dep, prm);
+    else if (prm.C <= 20) launch_kernel(spatial_any_kernel<KIND, BWD, REDUCE, 1, 20>, gd, bd, 0, stream, dep, prm);
+    else if (prm.C <= 40) launch_kernel(spatial_any_kernel<KIND, BWD, REDUCE, 1, 40>, gd, bd, 0, stream, dep, prm);
+    else if (prm.C <= 80) launch_kernel(spatial_any_kernel<KIND, BWD, REDUCE, 4, 20>, gd, bd, 0, stream, dep, prm);
+    else if (prm.C <= 160) launch_kernel(spatial_any_kernel<KIND, BWD, REDUCE, 4, 40>, gd, bd, 0, stream, dep, prm);
+    else launch_kernel(spatial_any_kernel<KIND, BWD, REDUCE, 8, 40>, gd, bd, 0, stream, dep, prm);
+    return launch_status("softmax any-alignment kernel launch");
+}
+
 // Integer tuning override from the environment (tile size, ring depth, blocks per SM);
 // unset or unparsable -> the default.
 
@@ -2164,6 +2305,9 @@ int launch_regime(SoftmaxParams prm, int dtype, cudaStream_t stream) {
             launch_kernel(kern, dim3(unsigned(grid)), dim3(kTileBlock), smem, stream, BWD && REDUCE && prm.after_count,
                           prm, map_in, map_out);
         } else if constexpr (KIND != kPC) {
+            if constexpr (sizeof(T) == 4) {
+                if (spatial_any_eligible(es, prm.C, prm.M)) return launch_spatial_any<KIND, BWD, REDUCE>(prm, stream);
+            }
             const size_t smem = 128 + tile_bytes + red_bytes;
             int per_sm = int((220 * 1024) / (smem + 1024));
             if (per_sm > 8) per_sm = 8;
@@ -2394,6 +2538,13 @@ int backward(const char *who, const void *logits, const int64_t *labels, const v
 // The fused training step runs in the TMA tile kernel and in the whole-row kernel: both keep all
 // channels of a pixel (a row) resident in shared memory, so one read of the logits serves the
 // loss and the gradient.
+// M > 1: the layouts the TMA tile pipeline takes (16-byte aligned rows and pointers).
+inline bool tile_pipeline_eligible(size_t es, const void *logits, const void *grads, const void *labels, int64_t N,
+                                   int64_t C, int64_t M) {
+    return N >= 1 && M > 1 && size_t(C) * 32 * es + 8192 <= kSmemLimit && (M * es) % 16 == 0 && aligned16(logits) &&
+           aligned16(grads) && aligned16(labels) && M < (int64_t(1) << 31) && N < (int64_t(1) << 31);
+}
+
 inline bool fused_step_eligible(size_t es, const void *logits, const void *grads, const void *labels, int64_t N,
                                 int64_t C, int64_t M) {
     if (N < 1 || M < 1) return false;
@@ -2402,8 +2553,8 @@ inline bool fused_step_eligible(size_t es, const void *logits, const void *grads
         return size_t(C) * es + 1024 <= kSmemLimit && (size_t(C) * es) % 16 == 0 && aligned16(logits) && aligned16(grads);
     }
     if (size_t(C) * 32 * es + 8192 > kSmemLimit) return false;
-    return (M * es) % 16 == 0 && aligned16(logits) && aligned16(grads) && aligned16(labels) &&
-           M < (int64_t(1) << 31) && N < (int64_t(1) << 31);
+    if (es == 4 && C <= 320 && C * M < (int64_t(1) << 31)) return true;      // any alignment: the tile pipeline or spatial_any_kernel
+    return tile_pipeline_eligible(es, logits, grads, labels, N, C, M);
 }
 
 // Label-smooth training step for few channels (C <= CMAX, float32, M even, 8-byte aligned
@@ -2533,9 +2684,10 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
         return B200_ERR_ARG;
     }
     const size_t es = dtype_size(dtype);
-    const bool pipeline_ok = fused_step_eligible(es, logits, grad_logits, labels, N, C, M);
+    const bool any_ok = fused_step_eligible(es, logits, grad_logits, labels, N, C, M);
+    const bool pipeline_ok = M == 1 ? any_ok : tile_pipeline_eligible(es, logits, grad_logits, labels, N, C, M);
     const bool resident = resident_step_eligible(KIND, dtype, logits, grad_logits, labels, N, C, M, pipeline_ok);
-    if (!resident && !pipeline_ok) {
+    if (!resident && !any_ok) {
         set_error("%s: this layout has no fused step (ask b200_softmax_fused_step_path first)", who);
         return B200_ERR_UNSUPPORTED;
     }
@@ -2563,7 +2715,7 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
 inline bool pc_step_eligible(int dtype, const void *logits, const void *grads, const void *labels, int64_t N,
                              int64_t C, int64_t M) {
     return dtype_known(dtype) && dtype != B200_F64 && M > 1 && C >= 1 && C <= kPcMaxC &&
-           fused_step_eligible(dtype_size(dtype), logits, grads, labels, N, C, M);
+           tile_pipeline_eligible(dtype_size(dtype), logits, grads, labels, N, C, M);
 }
 
 // Number of labels != ignore, 16-byte loads, four in flight per thread.
