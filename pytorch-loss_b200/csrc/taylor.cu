@@ -12,7 +12,8 @@
 // log form takes the hardware logarithm (lg2.approx, a few ulp) per element and the library
 // one per position for log S.
 //   M > 1   few channels (<= 32 forward, <= 20 backward, float32): a thread owns 2 adjacent
-//           positions and keeps all their channels in registers -- one read, one write;
+//           positions (1 when M is odd or the pointers are not 8-byte aligned) and keeps all their
+//           channels in registers -- one read, one write;
 //           33..320 channels (float32): channel slices over the threads of a block, each thread's
 //           share in registers, partial sums through shared memory -- again one read, one write;
 //           otherwise a thread owns 4 adjacent positions along M (16-byte accesses when the layout
@@ -130,69 +131,80 @@ taylor_spatial_kernel(const TaylorParams p) {
     }
 }
 
-// M > 1, few channels (C <= CMAX), float32: a thread owns 2 adjacent positions and keeps all their
-// channels in registers, so x (and g) are read once: 8-byte accesses, 256 B per warp and channel.
-template <bool BWD, bool LOG, int ORDER, int CMAX>
-__global__ void __launch_bounds__(kTaylorThreads, (!BWD && CMAX <= 20) ? 3 : 2)
+// M > 1, few channels (C <= CMAX), float32: a thread owns VEC adjacent positions (2: 8-byte
+// accesses, 256 B per warp and channel, M even and 8-byte aligned pointers; 1: any M, any
+// alignment) and keeps all their channels in registers, so x (and g) are read once.
+template <bool BWD, bool LOG, int ORDER, int CMAX, int VEC>
+__global__ void __launch_bounds__(kTaylorThreads, (!BWD && CMAX <= 20) || VEC == 1 ? 3 : 2)
 taylor_resident_kernel(const TaylorParams p) {
     const float *x = static_cast<const float *>(p.x);
     const float *g = static_cast<const float *>(p.g);
     float *out = static_cast<float *>(p.out);
     const int C = int(p.C);
-    const int64_t groups_per_row = p.M / 2;
+    const int64_t groups_per_row = p.M / VEC;
     const int64_t groups = p.N * groups_per_row;
     const int64_t stride = int64_t(gridDim.x) * kTaylorThreads;
+    struct Vals { float v[VEC]; };
+    auto load = [](const float *q) {
+        Vals r;
+        if constexpr (VEC == 2) {
+            const float2 f = __ldcs(reinterpret_cast<const float2 *>(q));
+            r.v[0] = f.x;
+            r.v[1] = f.y;
+        } else {
+            r.v[0] = __ldcs(q);
+        }
+        return r;
+    };
     for (int64_t gi = int64_t(blockIdx.x) * kTaylorThreads + threadIdx.x; gi < groups; gi += stride) {
-        const int64_t n = gi / groups_per_row, m0 = (gi % groups_per_row) * 2;
+        const int64_t n = gi / groups_per_row, m0 = (gi % groups_per_row) * VEC;
         const int64_t base = n * p.C * p.M + m0;
-        float2 xv[CMAX], gv[BWD ? CMAX : 1];
+        Vals xv[CMAX], gv[BWD ? CMAX : 1];
 #pragma unroll
         for (int j = 0; j < CMAX; ++j) {
             if (j < C) {
-                xv[j] = __ldcs(reinterpret_cast<const float2 *>(x + base + j * p.M));
-                if (BWD) gv[j] = __ldcs(reinterpret_cast<const float2 *>(g + base + j * p.M));
+                xv[j] = load(x + base + j * p.M);
+                if (BWD) gv[j] = load(g + base + j * p.M);
             }
         }
-        float2 S = make_float2(0.f, 0.f), A = make_float2(0.f, 0.f);
+        float S[VEC], A[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) S[v] = A[v] = 0.f;
 #pragma unroll
         for (int j = 0; j < CMAX; ++j) {
             if (j < C) {
-                float d;
-                float2 f;
-                taylor_poly<ORDER, false>(xv[j].x, p, f.x, d);
-                taylor_poly<ORDER, false>(xv[j].y, p, f.y, d);
-                S.x += f.x;
-                S.y += f.y;
-                if (BWD) {
-                    A.x += LOG ? gv[j].x : gv[j].x * f.x;
-                    A.y += LOG ? gv[j].y : gv[j].y * f.y;
-                } else {
-                    xv[j] = f;            // forward: f(x) takes x's place; backward recomputes it with f'
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    float f, d;
+                    taylor_poly<ORDER, false>(xv[j].v[v], p, f, d);
+                    S[v] += f;
+                    if (BWD) A[v] += LOG ? gv[j].v[v] : gv[j].v[v] * f;
+                    else xv[j].v[v] = f;          // forward: f(x) takes x's place; backward recomputes it with f'
                 }
             }
         }
-        const float2 invS = make_float2(1.f / S.x, 1.f / S.y);
-        const float2 logS = LOG && !BWD ? make_float2(logf(S.x), logf(S.y)) : make_float2(0.f, 0.f);
+        float invS[VEC], logS[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            invS[v] = 1.f / S[v];
+            logS[v] = LOG && !BWD ? logf(S[v]) : 0.f;
+        }
 #pragma unroll
         for (int j = 0; j < CMAX; ++j) {
             if (j < C) {
-                float2 o;
-                if constexpr (!BWD) {
-                    o.x = LOG ? __logf(xv[j].x) - logS.x : xv[j].x * invS.x;
-                    o.y = LOG ? __logf(xv[j].y) - logS.y : xv[j].y * invS.y;
-                } else {
-                    float fx, fy, dx, dy;
-                    taylor_poly<ORDER, true>(xv[j].x, p, fx, dx);
-                    taylor_poly<ORDER, true>(xv[j].y, p, fy, dy);
-                    if (LOG) {
-                        o.x = dx * (gv[j].x / fx - A.x * invS.x);
-                        o.y = dy * (gv[j].y / fy - A.y * invS.y);
+                float o[VEC];
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    if constexpr (!BWD) {
+                        o[v] = LOG ? __logf(xv[j].v[v]) - logS[v] : xv[j].v[v] * invS[v];
                     } else {
-                        o.x = dx * invS.x * (gv[j].x - A.x * invS.x);
-                        o.y = dy * invS.y * (gv[j].y - A.y * invS.y);
+                        float f, d;
+                        taylor_poly<ORDER, true>(xv[j].v[v], p, f, d);
+                        o[v] = LOG ? d * (gv[j].v[v] / f - A[v] * invS[v]) : d * invS[v] * (gv[j].v[v] - A[v] * invS[v]);
                     }
                 }
-                __stcs(reinterpret_cast<float2 *>(out + base + j * p.M), o);
+                if constexpr (VEC == 2) __stcs(reinterpret_cast<float2 *>(out + base + j * p.M), make_float2(o[0], o[1]));
+                else __stcs(out + base + j * p.M, o[0]);
             }
         }
     }
@@ -352,14 +364,21 @@ int launch_taylor(const TaylorParams &p, cudaStream_t stream) {
         const bool al8 = ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.out) |
                            (BWD ? reinterpret_cast<uintptr_t>(p.g) : 0)) & 7u) == 0;
         constexpr int kSmall = BWD ? 20 : 32;
-        if (p.M % 2 == 0 && al8 && p.C <= kSmall) {
-            const int64_t groups2 = p.N * (p.M / 2);
+        if (p.C <= kSmall) {
+            const bool pairs = p.M % 2 == 0 && al8;        // else one position per thread: any M, any alignment
+            const int64_t groups2 = p.N * (pairs ? p.M / 2 : p.M);
             int64_t grid2 = (groups2 + kTaylorThreads - 1) / kTaylorThreads;
             const int64_t cap2 = int64_t(sm_count()) * 2 * 8;
             if (grid2 > cap2) grid2 = cap2;
-            if (p.C <= 8) taylor_resident_kernel<BWD, LOG, ORDER, 8><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
-            else if (!BWD && p.C <= 20) taylor_resident_kernel<false, LOG, ORDER, 20><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
-            else taylor_resident_kernel<BWD, LOG, ORDER, kSmall><<<unsigned(grid2), kTaylorThreads, 0, stream>>>(p);
+            const unsigned g2 = unsigned(grid2);
+            if (pairs) {
+                if (p.C <= 8) taylor_resident_kernel<BWD, LOG, ORDER, 8, 2><<<g2, kTaylorThreads, 0, stream>>>(p);
+                else if (!BWD && p.C <= 20) taylor_resident_kernel<false, LOG, ORDER, 20, 2><<<g2, kTaylorThreads, 0, stream>>>(p);
+                else taylor_resident_kernel<BWD, LOG, ORDER, kSmall, 2><<<g2, kTaylorThreads, 0, stream>>>(p);
+            } else {
+                if (p.C <= 8) taylor_resident_kernel<BWD, LOG, ORDER, 8, 1><<<g2, kTaylorThreads, 0, stream>>>(p);
+                else taylor_resident_kernel<BWD, LOG, ORDER, kSmall, 1><<<g2, kTaylorThreads, 0, stream>>>(p);
+            }
             return launch_status("taylor softmax resident kernel launch");
         }
     }
