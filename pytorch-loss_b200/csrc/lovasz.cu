@@ -355,6 +355,92 @@ lovasz_tile_kernel(const TileArgs a, const __grid_constant__ CUtensorMap map_log
     if (TMA && tid == 0) bulk_wait_all();
 }
 
+// ------------------------------------------------- keys / backward for unaligned layouts
+//
+// Images whose pixel count is not a multiple of 4 (769 x 769 crops), or unaligned pointers: no
+// tensor map.  Up to CMAX classes: a thread owns ONE pixel and keeps all its channels in
+// registers (4-byte accesses, 128 contiguous bytes per warp and channel, every load of a thread
+// in flight together); a block walks groups of 256 adjacent pixels of one image, so a warp never
+// spans two images.  Same arithmetic as lovasz_tile_kernel.
+constexpr int kAnyThreads = 256;
+template <bool BWD, int CMAX>
+__global__ void __launch_bounds__(kAnyThreads, BWD ? 2 : 3)
+lovasz_any_kernel(const TileArgs a) {
+    const LovaszGeom &g = a.g;
+    const int C = int(g.C);
+    const int lane = threadIdx.x & 31;
+    const int64_t groups_per_image = (g.M + kAnyThreads - 1) / kAnyThreads;
+    const int64_t groups = g.N * groups_per_image;
+    for (int64_t gi = blockIdx.x; gi < groups; gi += gridDim.x) {
+        const int64_t n = gi / groups_per_image, grp = gi % groups_per_image;
+        const int64_t pix = grp * kAnyThreads + threadIdx.x;
+        const bool inb = pix < g.M;
+        const int64_t img_base = n * g.C * g.M + (inb ? pix : 0);
+        float xv[CMAX], jv[BWD ? CMAX : 1];
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j) {
+            if (j < C) {
+                xv[j] = inb ? __ldcs(a.logits + img_base + int64_t(j) * g.M) : 0.f;
+                if (BWD) jv[j] = inb ? __ldcs(a.jacc + seg_offset(g, n, j, pix)) : 0.f;
+            }
+        }
+        const int64_t lb = inb ? a.labels[n * g.M + pix] : a.ignore;
+        const bool valid = inb && lb != a.ignore;
+        float m = -3.402823466e38f;
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j)
+            if (j < C) m = fmaxf(m, xv[j]);
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < CMAX; ++j)
+            if (j < C) {
+                xv[j] = exp_fast(xv[j] - m);              // e^{x-m} takes x's place
+                s += xv[j];
+            }
+        const float inv_s = 1.f / s;
+        if (!BWD) {
+            const int64_t seg0 = g.per_image ? n * g.C : 0;
+            const bool sample = grp % (2 * kSampleEvery) == 0;    // (256-pixel groups: half a 512-pixel tile)
+            uint32_t kfg = 0;
+#pragma unroll
+            for (int j = 0; j < CMAX; ++j) {
+                if (j < C) {
+                    uint32_t key = kKeyIgnored;
+                    if (valid) {
+                        const float pr = xv[j] * inv_s;
+                        const bool fg = (j == lb);
+                        const float err = fg ? 1.f - pr : pr;
+                        uint32_t eb = __float_as_uint(fmaxf(err, 0.f));
+                        eb = eb > kOneBits ? kOneBits : eb;
+                        key = ((kOneBits - eb) << 1) | (fg ? 1u : 0u);
+                        if (fg) kfg = key;
+                    }
+                    if (inb) a.keys[seg_offset(g, n, j, pix)] = key;
+                    if (sample) {        // every lane of the warp is at the same j
+                        const uint32_t v = __reduce_min_sync(0xffffffffu, key);
+                        if (lane == 0 && v != kKeyIgnored) atomicMin(a.minkey + seg0 + j, v);
+                    }
+                }
+            }
+            track_fg(a.maxfg + seg0, kfg ? int(lb) : -1, kfg, lane);
+        } else {
+            const int64_t gseg = g.per_image ? n * g.C : 0;
+            float dot = 0.f;
+#pragma unroll
+            for (int j = 0; j < CMAX; ++j)
+                if (j < C) {
+                    jv[j] = (j == lb ? -jv[j] : jv[j]) * __ldg(a.seg_grad + gseg + j);    // gp
+                    dot += xv[j] * inv_s * jv[j];
+                }
+            if (inb) {
+#pragma unroll
+                for (int j = 0; j < CMAX; ++j)
+                    if (j < C) __stcs(a.grads + img_base + int64_t(j) * g.M, valid ? xv[j] * inv_s * (jv[j] - dot) : 0.f);
+            }
+        }
+    }
+}
+
 // -------------------------------------------- pipelined pair-per-thread tile kernels
 //
 // The production form of the keys and backward kernels for few classes (a tile of all C
@@ -1490,6 +1576,15 @@ int launch_tile(const TileArgs &a, cudaStream_t stream) {
         kern<<<dim3(unsigned(grid)), kTileThreads, smem, stream>>>(a, m_logits, m_seg, m_grads);
         return launch_status(BWD ? "lovasz backward kernel launch" : "lovasz keys kernel launch");
     };
+    if (!tma_ok && g.C <= 40) {
+        // unaligned, few classes: a pixel's channels in one thread's registers
+        const int64_t groups = g.N * ((g.M + kAnyThreads - 1) / kAnyThreads);
+        int64_t agrid = int64_t(sm_count()) * (BWD ? 2 : 3) * 4;
+        if (agrid > groups) agrid = groups;
+        if (g.C <= 20) lovasz_any_kernel<BWD, 20><<<dim3(unsigned(agrid)), kAnyThreads, 0, stream>>>(a);
+        else lovasz_any_kernel<BWD, 40><<<dim3(unsigned(agrid)), kAnyThreads, 0, stream>>>(a);
+        return launch_status(BWD ? "lovasz backward kernel launch" : "lovasz keys kernel launch");
+    }
     return tma_ok ? launch(lovasz_tile_kernel<BWD, true>) : launch(lovasz_tile_kernel<BWD, false>);
 }
 

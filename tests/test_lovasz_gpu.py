@@ -22,7 +22,10 @@ def _blocky_labels(gen, n, c, h, w, cell, ignore, frac):
 SHAPES = [(2, 5, 12, 11), (1, 19, 16, 16), (3, 4, 9, 7), (2, 7, 40, 52), (1, 3, 130, 127),
           (2, 19, 96, 96), (1, 2, 8, 8), (2, 40, 33, 20), (1, 300, 12, 12),
           # 512-pixel pipelined tiles: ragged second box, widest backward / forward class counts
-          (2, 19, 26, 30), (1, 26, 24, 37), (1, 40, 30, 28)]
+          (2, 19, 26, 30), (1, 26, 24, 37), (1, 40, 30, 28),
+          # odd pixel counts (no 16-byte aligned channel rows): a pixel's channels in one thread's registers
+          # up to 40 classes (several 256-pixel groups per image), the tile kernel without TMA beyond
+          (2, 19, 37, 41), (1, 33, 9, 31), (1, 41, 9, 31)]
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
