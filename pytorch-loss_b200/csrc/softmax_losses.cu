@@ -1961,6 +1961,75 @@ rows_multi_kernel(const SoftmaxParams prm) {
                     if (lbi >= 0 && (lbi >> 1) % TPR == t)
                         rp[lbi] = from_f32<T>(to_f32(rp[lbi]) - (kc.lb_pos - kc.lb_neg) * psc);
                 }
+            } else if (KIND == kLMargin && valid && lbi >= 0 && (C & 1) == 0) {
+                // Large margin, even C: channel pairs and packed arithmetic as above, the target
+                // handled as in tile_pair_kernel: its logit is parked at -FLT_MAX for the maximum
+                // sweep and at min(x_lb, m') for the sum sweep, its terms are then taken back out of
+                // the sums (s' >= 1 >= e^{min(x_lb - m', 0)}: nothing cancels), and its gradient
+                // overwrites what the sweep left there.
+                const int npair = C >> 1;
+                const float xl = to_f32(rp[lbi]);
+                __syncwarp(row_mask);                          // all of the row's lanes hold x_lb before it is parked
+                const bool owner = (lbi >> 1) % TPR == t;      // my walk visits the label's pair
+                if (owner) rp[lbi] = from_f32<T>(sizeof(T) == 2 ? -65504.f : kNegInf);
+                float2 m2 = splat2(kNegInf);
+                walk_units(npair, chunks_p, rot_p, [&](int q) { m2 = max2(m2, ld_pair(rp + 2 * q)); });
+                float m = fmaxf(m2.x, m2.y);
+                for (int o = TPR >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(row_mask, m, o));
+                const float cl = fminf(xl, m);
+                if (owner) rp[lbi] = from_f32<T>(cl);
+                const pk_t pnegm = psplat(-m), l2e = psplat(kLog2e);
+                pk_t psum = psplat(0.f), psde = psplat(0.f), psx = psplat(0.f);
+                walk_units(npair, chunks_p, rot_p, [&](int q) {
+                    const pk_t x = ld_pk(rp + 2 * q);
+                    const pk_t d = padd(x, pnegm);
+                    const pk_t e = pex2(pmul(d, l2e));
+                    psum = padd(psum, e);
+                    psde = pfma(d, e, psde);
+                    psx = padd(psx, x);
+                });
+                const float2 v1 = upk2(psum), v2 = upk2(psde), v3 = upk2(psx);
+                float sum = v1.x + v1.y, sde = v2.x + v2.y, sx = v3.x + v3.y;
+                for (int o = TPR >> 1; o > 0; o >>= 1) {
+                    sum += __shfl_xor_sync(row_mask, sum, o);
+                    sde += __shfl_xor_sync(row_mask, sde, o);
+                    sx += __shfl_xor_sync(row_mask, sx, o);
+                }
+                // (half tiles hold the parked value rounded to T: use what the sweep read)
+                const float clr = to_f32(from_f32<T>(cl));
+                const float dc = clr - m;
+                const float ec = ex2f(dc * kLog2e);
+                const float s_no = sum - ec;
+                const float sde_no = sde - dc * ec;
+                const float sd = (sx - clr) - float(C - 1) * m;
+                const float inv_s = __fdividef(1.f, s_no);
+                const float sqx = sde_no * inv_s;
+                const float mm = fmaxf(m, xl);
+                const float e_no = s_no * ex2f((m - mm) * kLog2e);
+                const float e_lb = ex2f((xl - mm) * kLog2e);
+                const float s_all = e_no + e_lb;
+                const float rr = __fdividef(e_no, s_all);
+                const float loss = (mm + __logf(s_all)) - xl + kc.half_lam * (sqx - kc.a * sd);
+                if (t == 0) {
+                    if (!BWD && losses) losses[row] = from_f32<T>(loss);
+                    if (REDUCE) {
+                        acc_loss += double(loss);
+                        acc_cnt += 1.0;
+                    }
+                }
+                if (BWD) {
+                    float psc = gscale;
+                    if (prm.grad_mode == 2) psc *= to_f32(gout[row]);
+                    // g_j = scale (r q + lam/2 (q (d + 1 - sqx) - a)) = q (A + B d) + Cc,  q = e^d / s'
+                    const pk_t pqa = psplat((rr + kc.half_lam * (1.f - sqx)) * psc), pqb = psplat(kc.half_lam * psc);
+                    const pk_t pcc = psplat(-kc.half_lam * kc.a * psc), pqs = psplat(inv_s);
+                    walk_units(npair, chunks_p, rot_p, [&](int q) {
+                        const pk_t d = padd(ld_pk(rp + 2 * q), pnegm);
+                        const pk_t qq = pmul(pex2(pmul(d, l2e)), pqs);
+                        st_pk(rp + 2 * q, pfma(qq, pfma(pqb, d, pqa), pcc));
+                    });
+                    if (owner) rp[lbi] = from_f32<T>(-rr * psc);
+                }
             } else if (valid) {
                 Stat1<KIND> s1;
                 s1.init();
