@@ -19,7 +19,8 @@
 //           otherwise a thread owns 4 adjacent positions along M (16-byte accesses when the layout
 //           allows, else one position) and walks the C channels twice: sums first, outputs
 //           second; the second walk finds its lines in L1/L2 (a block's working set is C x 4 KB).
-//   M == 1  a warp owns a row: lanes stride over the channels, warp-shuffle sums.
+//   M == 1  a warp owns a row: lanes stride over the channels, warp-shuffle sums; rows of 64..1024
+//           floats stay in the warp's registers between the sum and the output (one read).
 #include "common.cuh"
 
 namespace b200 {
@@ -348,6 +349,77 @@ taylor_rows_kernel(const TaylorParams p) {
     }
 }
 
+// M == 1, rows of up to 32 * NV * 4 floats (float32, C a multiple of 4, 16-byte aligned pointers):
+// a warp owns a row and keeps it in registers -- NV 16-byte vectors per lane, all loads of a lane
+// in flight together -- so x (and g) are read once; sums by warp shuffles.
+template <bool BWD, bool LOG, int ORDER, int NV>
+__global__ void __launch_bounds__(kTaylorThreads, BWD ? 2 : 3)
+taylor_rows_resident_kernel(const TaylorParams p) {
+    const float4 *x = static_cast<const float4 *>(p.x);
+    const float4 *g = static_cast<const float4 *>(p.g);
+    float4 *out = static_cast<float4 *>(p.out);
+    const int lane = threadIdx.x & 31;
+    const int nvec = int(p.C) >> 2;                     // 16-byte vectors per row
+    const int64_t warps = int64_t(gridDim.x) * (kTaylorThreads / 32);
+    for (int64_t r = int64_t(blockIdx.x) * (kTaylorThreads / 32) + (threadIdx.x >> 5); r < p.N; r += warps) {
+        const float4 *xr = x + r * nvec;
+        const float4 *gr = BWD ? g + r * nvec : nullptr;
+        float4 xv[NV], gv[BWD ? NV : 1];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                xv[i] = __ldcs(xr + v);
+                if (BWD) gv[i] = __ldcs(gr + v);
+            }
+        }
+        float S = 0.f, A = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (lane + 32 * i < nvec) {
+                float *xe = reinterpret_cast<float *>(&xv[i]);
+                const float *ge = reinterpret_cast<const float *>(&gv[BWD ? i : 0]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float f, d;
+                    taylor_poly<ORDER, false>(xe[e], p, f, d);
+                    S += f;
+                    if (BWD) A += LOG ? ge[e] : ge[e] * f;
+                    else xe[e] = f;                     // forward: f(x) takes x's place
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            S += __shfl_xor_sync(0xffffffffu, S, o);
+            if (BWD) A += __shfl_xor_sync(0xffffffffu, A, o);
+        }
+        const float invS = 1.f / S, logS = LOG && !BWD ? logf(S) : 0.f;
+        float4 *orow = out + r * nvec;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) {
+                float4 o4;
+                float *oe = reinterpret_cast<float *>(&o4);
+                const float *xe = reinterpret_cast<const float *>(&xv[i]);
+                const float *ge = reinterpret_cast<const float *>(&gv[BWD ? i : 0]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if constexpr (!BWD) {
+                        oe[e] = LOG ? __logf(xe[e]) - logS : xe[e] * invS;
+                    } else {
+                        float f, d;
+                        taylor_poly<ORDER, true>(xe[e], p, f, d);
+                        oe[e] = LOG ? d * (ge[e] / f - A * invS) : d * invS * (ge[e] - A * invS);
+                    }
+                }
+                __stcs(orow + v, o4);
+            }
+        }
+    }
+}
+
 inline bool aligned16(const void *q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; }
 
 template <typename T, bool BWD, bool LOG, int ORDER>
@@ -356,6 +428,16 @@ int launch_taylor(const TaylorParams &p, cudaStream_t stream) {
         int64_t grid = (p.N + kTaylorThreads / 32 - 1) / (kTaylorThreads / 32);
         const int64_t cap = int64_t(sm_count()) * 8;
         if (grid > cap) grid = cap;
+        if constexpr (sizeof(T) == 4 && ORDER > 0) {
+            // classification-sized rows: the row stays in the warp's registers (one read)
+            if (p.C % 4 == 0 && p.C >= 64 && p.C <= 1024 && aligned16(p.x) && aligned16(p.out) && (!BWD || aligned16(p.g))) {
+                if (p.C <= 256)
+                    taylor_rows_resident_kernel<BWD, LOG, ORDER, 2><<<unsigned(grid), kTaylorThreads, 0, stream>>>(p);
+                else
+                    taylor_rows_resident_kernel<BWD, LOG, ORDER, 8><<<unsigned(grid), kTaylorThreads, 0, stream>>>(p);
+                return launch_status("taylor softmax resident rows kernel launch");
+            }
+        }
         taylor_rows_kernel<T, BWD, LOG, ORDER><<<unsigned(grid), kTaylorThreads, 0, stream>>>(p);
         return launch_status("taylor softmax rows kernel launch");
     }

@@ -15,7 +15,9 @@ CASES = [((2, 19, 16, 24), 1), ((3, 7, 5, 7), 1), ((6, 33), 1), ((64, 1000), -1)
          ((2, 3, 4, 40), 2), ((2, 150, 12, 12), 1), ((1, 2, 1, 1), 1),
          # 33..320 channels: channel slices over the threads of a block (4 slices to 160, 8 beyond), ragged ends
          ((1, 33, 5, 9), 1), ((2, 33, 6, 12), 1), ((3, 40, 70), 1), ((2, 161, 4, 10), 1), ((1, 161, 10, 10), 1),
-         ((1, 320, 8, 8), 1), ((1, 321, 8, 8), 1)]
+         ((1, 320, 8, 8), 1), ((1, 321, 8, 8), 1),
+         # rows of 64..1024 floats stay in a warp's registers (2 or 8 vectors per lane); 1028 does not
+         ((40, 64), 1), ((33, 256), -1), ((9, 260), 1), ((17, 1024), 1), ((5, 1028), 1)]
 
 
 @pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[0])) + "_d%d" % c[1])
