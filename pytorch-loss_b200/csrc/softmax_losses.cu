@@ -2706,6 +2706,109 @@ lsr_resident_step_kernel(const SoftmaxParams prm) {
     grid_reduce_finish(double(acc), double(cnt), prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
 }
 
+// Label-smooth training step over classification rows (M == 1, float32, C a multiple of 4 between
+// 64 and 1024, 16-byte aligned pointers): a warp owns a row and keeps it in registers -- NV 16-byte
+// vectors per lane, all of a lane's loads in flight together -- so the logits are read once and the
+// gradient is written once, with no shared memory and no barrier before the final reduction.  The
+// target's logit is fetched again (one 4-byte load per row) and its gradient is a 4-byte store by
+// the lane that wrote the vector around it.
+template <int NV>
+__global__ void __launch_bounds__(kResidentThreads, 3)
+lsr_rows_resident_step_kernel(const SoftmaxParams prm) {
+    __shared__ double sh_red[64];
+    const float4 *x = static_cast<const float4 *>(prm.logits);
+    float4 *grads = static_cast<float4 *>(prm.grads);
+    const int lane = threadIdx.x & 31;
+    const int C = prm.k.C, nvec = C >> 2;
+    const int64_t warps = int64_t(gridDim.x) * (kResidentThreads / 32);
+    pdl_wait();                                    // the divisor comes from the label count in front
+    const float gs = uniform_grad_scale(nullptr, 0, prm.denom);
+    const float dpn = prm.k.lb_pos - prm.k.lb_neg;
+    float acc = 0.f, cnt = 0.f;
+    for (int64_t r = int64_t(blockIdx.x) * (kResidentThreads / 32) + (threadIdx.x >> 5); r < prm.N; r += warps) {
+        const float4 *xr = x + r * nvec;
+        float4 xv[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec) xv[i] = __ldcs(xr + v);
+        }
+        const int64_t lb = __ldg(prm.labels + r);
+        const bool valid = lb != prm.ignore;
+        // (a label outside [0, C) that is not the ignore value is undefined in the reference: no target term here)
+        const int lbi = (valid && lb >= 0 && lb < C) ? int(lb) : -1;
+        const float xl = lbi >= 0 ? __ldg(static_cast<const float *>(prm.logits) + r * C + lbi) : 0.f;
+        float4 *grow = grads + r * nvec;
+        if (!valid) {                              // (uniform over the warp)
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int v = lane + 32 * i;
+                if (v < nvec) __stcs(grow + v, make_float4(0.f, 0.f, 0.f, 0.f));
+            }
+            continue;
+        }
+        float m = kNegInf, sx = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (lane + 32 * i < nvec) {
+                m = fmaxf(fmaxf(m, fmaxf(xv[i].x, xv[i].y)), fmaxf(xv[i].z, xv[i].w));
+                sx += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float nm2 = -m * kLog2e;
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (lane + 32 * i < nvec) {
+                xv[i].x = ex2f(fmaf(xv[i].x, kLog2e, nm2));         // e^{x-m} takes x's place
+                xv[i].y = ex2f(fmaf(xv[i].y, kLog2e, nm2));
+                xv[i].z = ex2f(fmaf(xv[i].z, kLog2e, nm2));
+                xv[i].w = ex2f(fmaf(xv[i].w, kLog2e, nm2));
+                s += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            s += __shfl_xor_sync(0xffffffffu, s, o);
+            sx += __shfl_xor_sync(0xffffffffu, sx, o);
+        }
+        if (lane == 0) {
+            acc += prm.k.sumy * (m + __log2f(s) * kLn2) - prm.k.lb_neg * sx - dpn * xl;
+            cnt += 1.f;
+        }
+        const float a = prm.k.sumy * __fdividef(gs, s), b = -prm.k.lb_neg * gs;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int v = lane + 32 * i;
+            if (v < nvec)
+                __stcs(grow + v, make_float4(fmaf(xv[i].x, a, b), fmaf(xv[i].y, a, b), fmaf(xv[i].z, a, b), fmaf(xv[i].w, a, b)));
+        }
+        // target: (sumy e_l / s - lb_pos) gs, by the lane whose vector store covers it (program order)
+        if (lbi >= 0 && ((lbi >> 2) & 31) == lane)
+            reinterpret_cast<float *>(grow)[lbi] = fmaf(ex2f(fmaf(xl, kLog2e, nm2)), a, -prm.k.lb_pos * gs);
+    }
+    grid_reduce_finish(double(acc), double(cnt), prm.workspace, prm.out, sh_red, kTagSum, prm.defer != 0);
+}
+
+inline bool rows_resident_step_eligible(int kind, int dtype, const void *logits, const void *grads, const void *labels,
+                                        int64_t N, int64_t C, int64_t M) {
+    return kind == kLSR && dtype == B200_F32 && M == 1 && N >= 1 && C % 4 == 0 && C >= 64 && C <= 1024 &&
+           aligned16(logits) && aligned16(grads) && labels != nullptr;
+}
+
+int launch_rows_resident_step(const SoftmaxParams &prm, cudaStream_t stream) {
+    int64_t grid = (prm.N + kResidentThreads / 32 - 1) / (kResidentThreads / 32);
+    const int64_t cap = int64_t(sm_count()) * 3;           // all blocks resident: one reduction barrier per block
+    if (grid > cap) grid = cap;
+    const dim3 gd{unsigned(grid)}, bd(kResidentThreads);
+    const bool dep = prm.after_count != 0;
+    if (prm.C <= 256) launch_kernel(lsr_rows_resident_step_kernel<2>, gd, bd, 0, stream, dep, prm);
+    else launch_kernel(lsr_rows_resident_step_kernel<8>, gd, bd, 0, stream, dep, prm);
+    return launch_status("label-smooth resident rows step launch");
+}
+
 inline bool aligned8(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
 
 // The layouts lsr_resident_step_kernel takes, and the sizes it wins at: up to ~40 M elements its
@@ -2775,6 +2878,8 @@ int fused_step(const char *who, const void *logits, const int64_t *labels, void 
     prm.defer = defer & B200_STEP_DEFER;
     prm.after_count = (denom != nullptr && (defer & B200_STEP_AFTER_COUNT)) ? 1 : 0;
     if (resident) return launch_resident_step(prm, static_cast<cudaStream_t>(stream));
+    if (rows_resident_step_eligible(KIND, dtype, logits, grad_logits, labels, N, C, M))
+        return launch_rows_resident_step(prm, static_cast<cudaStream_t>(stream));
     return dispatch<KIND, true>(prm, dtype, true, static_cast<cudaStream_t>(stream));
 }
 
