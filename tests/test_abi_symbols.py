@@ -60,3 +60,32 @@ def test_missing_library_fails_loudly(tmp_path):
     from pytorch_loss import _cabi
     with pytest.raises(RuntimeError, match="no fallback"):
         _cabi.load_library(str(tmp_path / "libb200loss.so"))
+
+
+def test_fused_step_path_queries(lib):
+    """Which layouts have a one-pass training step: pure pointer/shape arithmetic, no device needed.
+    Addresses are made up (never dereferenced by the queries)."""
+    A, U = 0x7f0000001000, 0x7f0000001004            # 16-byte aligned / only 4-byte aligned
+    F32, F16 = 0, 1
+    q = lambda x, y, g, n, c, m, dt: lib.b200_softmax_fused_step_path(
+        ctypes.c_void_p(x), ctypes.c_void_p(y), ctypes.c_void_p(g), n, c, m, dt)
+    # images: the tile pipeline (aligned rows), the any-alignment kernel (float32, <= 320 classes)
+    assert q(A, A, A, 2, 19, 1024, F32) == 1
+    assert q(A, A, A, 2, 19, 769 * 769, F32) == 1          # odd pixel count
+    assert q(U, A, U, 2, 150, 1024, F32) == 1              # unaligned pointers
+    assert q(A, A, A, 2, 19, 769 * 769, F16) == 0          # half logits need 16-byte aligned rows
+    assert q(A, A, A, 2, 19, 1024, F16) == 1
+    assert q(A, A, A, 2, 400, 1023, F32) == 0              # too many classes for the unaligned kernel
+    # rows (M == 1): short rows up to 2048 classes, whole rows in shared memory beyond (16-byte rows)
+    assert q(A, A, A, 4096, 1000, 1, F32) == 1
+    assert q(A, A, A, 4096, 19, 1, F32) == 1
+    assert q(A, A, A, 256, 32768, 1, F16) == 1
+    assert q(A, A, A, 256, 4099, 1, F32) == 0              # 16 396-byte rows: no bulk copy
+    assert q(A, A, A, 0, 19, 1024, F32) == 0               # empty batch
+    p = lambda x, y, g, n, c, m, dt: lib.b200_pc_softmax_step_path(
+        ctypes.c_void_p(x), ctypes.c_void_p(y), ctypes.c_void_p(g), n, c, m, dt)
+    assert p(A, A, A, 2, 19, 1024, F32) == 1
+    assert p(A, A, A, 2, 256, 1024, F16) == 1
+    assert p(A, A, A, 2, 257, 1024, F32) == 0              # class weights for at most 256 classes
+    assert p(A, A, A, 2, 19, 1023, F32) == 0               # the tile pipeline only
+    assert p(A, A, A, 64, 19, 1, F32) == 0
