@@ -2707,13 +2707,13 @@ lsr_resident_step_kernel(const SoftmaxParams prm) {
 }
 
 // Label-smooth training step over classification rows (M == 1, float32, C a multiple of 4 between
-// 64 and 1024, 16-byte aligned pointers): a warp owns a row and keeps it in registers -- NV 16-byte
+// 64 and 2048, 16-byte aligned pointers): a warp owns a row and keeps it in registers -- NV 16-byte
 // vectors per lane, all of a lane's loads in flight together -- so the logits are read once and the
 // gradient is written once, with no shared memory and no barrier before the final reduction.  The
 // target's logit is fetched again (one 4-byte load per row) and its gradient is a 4-byte store by
 // the lane that wrote the vector around it.
 template <int NV>
-__global__ void __launch_bounds__(kResidentThreads, 3)
+__global__ void __launch_bounds__(kResidentThreads, NV <= 8 ? 3 : 2)
 lsr_rows_resident_step_kernel(const SoftmaxParams prm) {
     __shared__ double sh_red[64];
     const float4 *x = static_cast<const float4 *>(prm.logits);
@@ -2794,18 +2794,19 @@ lsr_rows_resident_step_kernel(const SoftmaxParams prm) {
 
 inline bool rows_resident_step_eligible(int kind, int dtype, const void *logits, const void *grads, const void *labels,
                                         int64_t N, int64_t C, int64_t M) {
-    return kind == kLSR && dtype == B200_F32 && M == 1 && N >= 1 && C % 4 == 0 && C >= 64 && C <= 1024 &&
+    return kind == kLSR && dtype == B200_F32 && M == 1 && N >= 1 && C % 4 == 0 && C >= 64 && C <= 2048 &&
            aligned16(logits) && aligned16(grads) && labels != nullptr;
 }
 
 int launch_rows_resident_step(const SoftmaxParams &prm, cudaStream_t stream) {
     int64_t grid = (prm.N + kResidentThreads / 32 - 1) / (kResidentThreads / 32);
-    const int64_t cap = int64_t(sm_count()) * 3;           // all blocks resident: one reduction barrier per block
+    const int64_t cap = int64_t(sm_count()) * (prm.C <= 1024 ? 3 : 2);   // all blocks resident: one reduction barrier per block
     if (grid > cap) grid = cap;
     const dim3 gd{unsigned(grid)}, bd(kResidentThreads);
     const bool dep = prm.after_count != 0;
     if (prm.C <= 256) launch_kernel(lsr_rows_resident_step_kernel<2>, gd, bd, 0, stream, dep, prm);
-    else launch_kernel(lsr_rows_resident_step_kernel<8>, gd, bd, 0, stream, dep, prm);
+    else if (prm.C <= 1024) launch_kernel(lsr_rows_resident_step_kernel<8>, gd, bd, 0, stream, dep, prm);
+    else launch_kernel(lsr_rows_resident_step_kernel<16>, gd, bd, 0, stream, dep, prm);
     return launch_status("label-smooth resident rows step launch");
 }
 
